@@ -1,0 +1,66 @@
+/* Shared device helpers: exact conversions and the reduction trees whose
+ * pairing order the reference's kernels fix.
+ *
+ * Bit-exactness notes.  Floating-point addition and max are commutative, so a
+ * reduction is determined by WHICH partial results are paired at each level,
+ * not by which thread does it.  The reference reduces with halving trees
+ * (value t is combined with value t+off for off = T/2 ... 1).  An xor
+ * butterfly over the same off sequence forms exactly the same pairs and leaves
+ * the (identical) result in every lane, which is what the helpers here use. */
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define S2P_FULL_MASK 0xffffffffu
+
+__device__ __forceinline__ float bf_bits_to_f32(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
+__device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ __nv_bfloat16 f2bf(float v) { return __float2bfloat16(v); } /* RNE */
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
+
+/* Warp-level tree over lane values, off = 16,8,4,2,1; result in every lane. */
+__device__ __forceinline__ float warp_tree_sum(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(S2P_FULL_MASK, v, off);
+    return v;
+}
+__device__ __forceinline__ float warp_tree_max(float v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(S2P_FULL_MASK, v, off));
+    return v;
+}
+
+/* Halving tree over T values (thread t < T contributes v; T a power of two,
+ * T >= 32, T <= blockDim.x).  Levels off >= 32 go through shared memory, the
+ * last five through shuffles in warp 0.  `red` needs T floats.  Returns the
+ * total in every thread.  All threads of the block must call it. */
+template <int T, bool IS_MAX>
+__device__ __forceinline__ float block_tree(float v, float* red) {
+    const int t = threadIdx.x;
+    if (t < T) red[t] = v;
+    __syncthreads();
+#pragma unroll
+    for (int off = T >> 1; off >= 32; off >>= 1) {
+        if (t < off) red[t] = IS_MAX ? fmaxf(red[t], red[t + off]) : red[t] + red[t + off];
+        __syncthreads();
+    }
+    if (t < 32) {
+        float r = red[t];
+        r = IS_MAX ? warp_tree_max(r) : warp_tree_sum(r);
+        if (t == 0) red[0] = r;
+    }
+    __syncthreads();
+    const float out = red[0];
+    __syncthreads(); /* red may be reused by the caller right away */
+    return out;
+}
+
+/* Bytes of an int8x4 word (biased by 128) or nibbles of an int4x8 word (biased
+ * by 8) to exact f32: the byte is planted in the mantissa of 2^23 and the bias
+ * is removed by one exact subtraction. */
+__device__ __forceinline__ float biased_byte_to_f32(uint32_t word, int byte_idx, float magic_minus) {
+    const uint32_t bits = __byte_perm(word, 0x4B000000u, 0x7540u | (uint32_t)byte_idx);
+    return __uint_as_float(bits) - magic_minus;
+}
