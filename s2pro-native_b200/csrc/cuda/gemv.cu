@@ -40,15 +40,27 @@ int gemv_rows_per_pass(int wk, int rows_per_cta, int K, int gshift, int swiglu, 
     return r < 1 ? 1 : r;
 }
 
+constexpr size_t GEMV_SMEM_BUDGET = 200 * 1024;
+
+/* Opt the kernel in to large dynamic shared memory, once per device. */
+template <int WK, int PRO, int EPI>
+cudaError_t gemv_stage_setup() {
+    static int done_mask = 0; /* bit per device ordinal */
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (done_mask & (1 << (dev & 31))) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(k_gemv_stage<WK, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)GEMV_SMEM_BUDGET);
+    if (e == cudaSuccess) done_mask |= 1 << (dev & 31);
+    return e;
+}
+
 template <int WK, int PRO, int EPI>
 cudaError_t launch_gemv_stage(GemvStage g, cudaStream_t stream) {
-    static bool attr_done = false;
-    const size_t budget = 200 * 1024;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemv_stage<WK, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)budget);
+    const size_t budget = GEMV_SMEM_BUDGET;
+    {
+        const cudaError_t e = gemv_stage_setup<WK, PRO, EPI>();
         if (e != cudaSuccess) return e;
-        attr_done = true;
     }
     const int units = (EPI == EPI_SWIGLU) ? (g.N >> 1) : g.N;
     int grid = device_sm_count();
@@ -73,6 +85,25 @@ S2P_INST(WK_INT8_CH)
 S2P_INST(WK_INT8_GRP)
 S2P_INST(WK_INT4_PACK)
 #undef S2P_INST
+
+/* Attribute set-up for every instantiation, to be called once before any stream
+ * capture (function attributes are not stream operations). */
+extern "C" cudaError_t gemv_setup_all(void) {
+    cudaError_t e = cudaSuccess;
+#define S2P_SETUP(WK, PRO, EPI) if (e == cudaSuccess) e = gemv_stage_setup<WK, PRO, EPI>();
+#define S2P_SETUP_WK(WK)               \
+    S2P_SETUP(WK, PRO_VEC, EPI_STORE)  \
+    S2P_SETUP(WK, PRO_NORM, EPI_STORE) \
+    S2P_SETUP(WK, PRO_VEC, EPI_RESID)  \
+    S2P_SETUP(WK, PRO_NORM, EPI_SWIGLU) \
+    S2P_SETUP(WK, PRO_NORM, EPI_ARGMAX)
+    S2P_SETUP_WK(WK_INT8_CH)
+    S2P_SETUP_WK(WK_INT8_GRP)
+    S2P_SETUP_WK(WK_INT4_PACK)
+#undef S2P_SETUP_WK
+#undef S2P_SETUP
+    return e;
+}
 
 /* ---- exact-order small batch (2 <= M <= 16) -------------------------------
  * One warp per output row; lane l owns k = 512 i + 16 l .. +15.  The 16 codes

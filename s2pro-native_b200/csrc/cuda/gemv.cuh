@@ -45,14 +45,16 @@ struct GemvStage {
     const void* scales;  /* f32 [N] (WK_INT8_CH) or f16 [N, K>>gshift] */
     int N, K, gshift;
     /* input */
-    const __nv_bfloat16* x;       /* [K]; with x_index: row *x_index of a [*,K] table */
+    const __nv_bfloat16* x;       /* [K]; with x_index / x_key: a row of a [*,K] table */
     const int32_t* x_index;       /* optional device index selecting the input row */
+    const unsigned long long* x_key; /* optional packed arg-max key selecting the input row */
     const __nv_bfloat16* norm_w;  /* PRO_NORM gain [K] */
     float eps;
     /* output */
     __nv_bfloat16* y;                 /* EPI_STORE/ARGMAX: [N]; EPI_SWIGLU: [N/2]; EPI_RESID: destination [N] */
     const __nv_bfloat16* resid_src;   /* EPI_RESID: vector the product is added to */
     const int32_t* resid_index;       /* optional device index: resid_src is row *resid_index of a [*,N] table */
+    const unsigned long long* resid_key; /* same, from a packed arg-max key */
     unsigned long long* argmax_key;   /* EPI_ARGMAX */
     int rows_per_pass;                /* rows (row pairs for EPI_SWIGLU) the shared partial buffer holds */
 };
@@ -78,6 +80,9 @@ __device__ __forceinline__ int xs_slot(int k) {
     const int i = k >> 9, l = (k >> 4) & 31, j = k & 15;
     return (((i * 8 + (j >> 1)) * 32 + l) << 2) + ((j & 1) << 1);
 }
+
+/* index held in a packed arg-max key (see EPI_ARGMAX) */
+__device__ __forceinline__ uint32_t key_index(unsigned long long key) { return 0xFFFFFFFFu - (uint32_t)key; }
 
 __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
 
@@ -148,6 +153,7 @@ __device__ __forceinline__ void stage_activation(const GemvStage& g, float* xs, 
     const int K = g.K;
     const __nv_bfloat16* x = g.x;
     if (g.x_index) x += (size_t)(*g.x_index) * K;
+    else if (g.x_key) x += (size_t)key_index(*g.x_key) * K;
     if (PRO == PRO_VEC) {
         for (int k = threadIdx.x; k < K; k += blockDim.x) {
             const float v = bf2f(x[k]);
@@ -295,6 +301,7 @@ __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsi
                     if (EPI == EPI_RESID) {
                         const __nv_bfloat16* src = g.resid_src;
                         if (g.resid_index) src += (size_t)(*g.resid_index) * g.N;
+                        else if (g.resid_key) src += (size_t)key_index(*g.resid_key) * g.N;
                         g.y[n] = f2bf(__fadd_rn(bf2f(src[n]), bf2f(yb)));
                     } else {
                         g.y[n] = yb;

@@ -1,0 +1,150 @@
+/* Internal launch interface between the CUDA translation units and the C11
+ * host code.  Everything here is extern "C" with plain pointers so model.c /
+ * session.c can call it; none of it is exported from the shared library. */
+#ifndef S2P_OPS_H
+#define S2P_OPS_H
+
+#include <stdint.h>
+#include <cuda_runtime.h>
+
+#ifdef __cplusplus
+#include <cuda_bf16.h>
+namespace s2p {
+extern "C" {
+typedef __nv_bfloat16 s2p_dev_bf16;
+#else
+typedef uint16_t s2p_dev_bf16;
+#endif
+
+/* Where the KV planes of row r live.  Payload base of row r is
+ * (bases ? bases[r] : base0 + r * row_stride); the K plane [kv_heads, max_seq,
+ * 128] starts k_off bytes in, the V plane v_off bytes in.  With an INT8 cache
+ * the f16 scale planes [kv_heads, max_seq, 4] are addressed the same way from
+ * sbases / sbase0 with ks_off / vs_off. */
+typedef struct {
+    void* base0; void* const* bases; size_t row_stride, k_off, v_off;
+    void* sbase0; void* const* sbases; size_t srow_stride, ks_off, vs_off;
+} KvRef;
+
+/* qkv post-processing (see k_qkv_post): per-row cache pointers (decode) or one
+ * base pointer + consecutive positions (prefill). */
+typedef struct {
+    const s2p_dev_bf16* qkv; /* [rows, (q_heads + 2 kv_heads) * 128] */
+    s2p_dev_bf16* q;         /* [rows, q_heads * 128] */
+    const s2p_dev_bf16* q_norm; /* [128] or NULL (fast-AR) */
+    const s2p_dev_bf16* k_norm;
+    float eps, rope_base;
+    int q_heads, kv_heads, max_seq, kv8;
+    int pos0, pos_row_step;
+    const int32_t* pos_arr; /* per-row positions, or NULL -> pos0 + row * pos_row_step */
+    KvRef kv;
+} QkvPostArgs;
+
+typedef struct {
+    const s2p_dev_bf16* q; /* [rows, q_heads*128], post norm/rope */
+    s2p_dev_bf16* out;
+    int q_heads, kv_heads, max_seq, kv8;
+    int pos0, pos_row_step;
+    const int32_t* pos_arr;
+    KvRef kv;
+    /* split-K decode only */
+    float* part;            /* [rows][q_heads][n_split_slots][130] */
+    unsigned int* counters; /* [rows][kv_heads], zero between launches */
+    int n_split_slots;      /* ceil(ctx_len / 64) */
+    int workers;            /* CTAs per (row, kv head) */
+    /* Always 128, but passed at run time: the single-pass kernel derives its query
+     * scale as rsqrtf((float)head_dim) on the device, as the reference's does
+     * (src/slowar/kernels.cu:258); a compile-time 128 would be folded to the
+     * correctly rounded constant, which differs from the device result in the last bit. */
+    int head_dim;
+} AttnArgs;
+
+/* device-resident sampler state; layout of the reference's s2ps_dev_state
+ * (src/slowar/slowar_kernels.h:134-142) */
+typedef struct {
+    int64_t prev[64];
+    uint64_t count;
+    uint64_t rng[4];
+    float temperature, top_p, rep_penalty;
+    int32_t window, seeded;
+    uint32_t seed31;
+    uint32_t pad_;
+} SamplerState;
+
+/* A quantised linear as the fused stage kernels see it. */
+typedef struct {
+    int kind;           /* 0 per-channel INT8, 1 group scale on int8 codes, 2 packed INT4 */
+    const void* w;      /* int8 [N,K] or nibbles [N,K/2] */
+    const void* scales; /* f32 [N] or f16 [N, K/G] */
+    int N, K, gshift;
+} LinRef;
+
+/* Where a [K] activation (or residual) vector comes from: a plain vector, or a
+ * row of a table selected on the device by an int32 index or by the low word
+ * of a packed arg-max key (index = 0xFFFFFFFF - low32). */
+typedef struct {
+    const s2p_dev_bf16* base;
+    const int32_t* index;
+    const unsigned long long* key;
+} VecRef;
+
+/* fused batch-1 decode stages (tick.cu) */
+cudaError_t stage_norm_gemv(const LinRef* lin, const VecRef* x, const s2p_dev_bf16* norm_w, float eps,
+                            s2p_dev_bf16* y, cudaStream_t st);
+cudaError_t stage_gemv_resid(const LinRef* lin, const s2p_dev_bf16* x, const VecRef* resid, s2p_dev_bf16* dst,
+                             cudaStream_t st);
+cudaError_t stage_norm_swiglu(const LinRef* lin, const VecRef* x, const s2p_dev_bf16* norm_w, float eps,
+                              s2p_dev_bf16* h, cudaStream_t st);
+cudaError_t stage_norm_argmax(const LinRef* lin, const s2p_dev_bf16* x, const s2p_dev_bf16* norm_w, float eps,
+                              s2p_dev_bf16* logits, unsigned long long* key, cudaStream_t st);
+/* decode attention that also does q/k norm, RoPE and the KV append from raw qkv */
+cudaError_t stage_attn_decode_prep(const AttnArgs* a, const s2p_dev_bf16* qkv, const s2p_dev_bf16* q_norm,
+                                   const s2p_dev_bf16* k_norm, float eps, float rope_base, int rows,
+                                   cudaStream_t st);
+
+/* Frame start for `rows` decode rows: x[r] = embedding of the fed-back token
+ * (bf16 table, or INT8 sidecar with row scales) plus, where mask[r], the sum of
+ * the 10 codebook embeddings of the previous frame's codes, times f32(1/sqrt 11);
+ * also clears the 9 arg-max keys of every row. */
+typedef struct {
+    const s2p_dev_bf16* embed;  /* bf16 table or NULL */
+    const int8_t* embed_i8; const float* embed_scale;
+    const s2p_dev_bf16* cb_emb; /* [10*4096, 2560] */
+    const int64_t* ids; const int32_t* codes /* [rows][10] */; const uint8_t* mask;
+    s2p_dev_bf16* x;
+    unsigned long long* keys;   /* [rows][9] or NULL */
+} TickBeginArgs;
+cudaError_t tick_begin(const TickBeginArgs* a, int rows, cudaStream_t st);
+/* Frame end: codes[r][1..9] from the arg-max keys (fused path) */
+cudaError_t tick_finish_keys(const unsigned long long* keys, int rows, int32_t* codes, cudaStream_t st);
+
+cudaError_t gemv_setup_all(void); /* once per device, before any stream capture */
+
+cudaError_t qkv_post(const QkvPostArgs* a, int rows, cudaStream_t st);
+cudaError_t attn_single(const AttnArgs* a, int rows, cudaStream_t st);
+cudaError_t attn_decode(const AttnArgs* a, int rows, cudaStream_t st);
+
+cudaError_t rms_norm(const void* x, const void* w, void* y, int rows, int width, float eps, cudaStream_t st);
+cudaError_t silu_mul(const void* gu, void* h, int rows, int ffn, cudaStream_t st);
+cudaError_t add_inplace(void* y, const void* x, int64_t n, cudaStream_t st);
+cudaError_t embed_rows(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t st);
+cudaError_t embed_rows_i8(const void* table, const float* scales, const int64_t* ids, void* out, int rows, int dim,
+                          cudaStream_t st);
+cudaError_t vq_embed_add(const void* cb_table, const int32_t* codes_dev, int T, void* rows, cudaStream_t st);
+cudaError_t scale_div(void* x, int64_t n, float divisor, cudaStream_t st);
+cudaError_t scale_rows_masked(void* x, const uint8_t* mask, int rows, int dim, float scale, cudaStream_t st);
+cudaError_t embed_codes(const void* table, const int32_t* codes, void* out, int rows, cudaStream_t st);
+cudaError_t argmax_rows(const void* logits, int32_t* ids, int rows, int vocab, cudaStream_t st);
+cudaError_t pack_frame(const int32_t* stage, int rows, int32_t* codes, cudaStream_t st);
+
+/* sampler: semantic logits sem_logits[r*stride + i] (i < 4096) and the EOS logit
+ * eos_logits[r*eos_stride]; writes tok/sem/codes[r*10]/eos and updates the states. */
+cudaError_t sample_rows(const void* sem_logits, int64_t stride, const void* eos_logits, int64_t eos_stride,
+                        SamplerState* const* states, int rows, int64_t* out_tok, int32_t* out_sem,
+                        int32_t* out_codes, uint8_t* out_eos, cudaStream_t st);
+
+#ifdef __cplusplus
+}  /* extern "C" */
+}  /* namespace s2p */
+#endif
+#endif

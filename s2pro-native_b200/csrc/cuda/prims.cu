@@ -1,0 +1,506 @@
+/* Transformer primitives with the reference's numerics contract
+ * (src/slowar/kernels.cu:4-17): f32 math on bf16 storage, explicit
+ * round-to-nearest steps where the reference forbids fma contraction, and the
+ * reduction pairings its kernels fix (see common.cuh).
+ *
+ * Exported launchers: the eleven s2pk_* of the primitive contract
+ * (include/s2pro/kernels.h:20-70 of the reference).  The internal launchers in
+ * namespace s2p serve the unfused decode tick and prefill (ops.h).
+ */
+#include <math.h>
+#include "common.cuh"
+#include "headops.cuh"
+#include "ops.h"
+#include "s2p_b200_abi.h"
+
+namespace s2p {
+
+static inline int grid_for(int64_t total, int threads) {
+    int64_t b = (total + threads - 1) / threads;
+    if (b > 148 * 16) b = 148 * 16;
+    return b < 1 ? 1 : (int)b;
+}
+
+/* ---- RMSNorm: 256 strided partials, halving tree (kernels.cu:46-68) -------- */
+__global__ void __launch_bounds__(256) k_rms_norm(const __nv_bfloat16* __restrict__ x,
+                                                  const __nv_bfloat16* __restrict__ w,
+                                                  __nv_bfloat16* __restrict__ y, int width, float eps) {
+    __shared__ float red[256];
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += 256) {
+        const float v = bf2f(x[base + i]);
+        ss = __fmaf_rn(v, v, ss);
+    }
+    const float tot = block_tree<256, false>(ss, red);
+    const float inv = rsqrtf(__fdiv_rn(tot, (float)width) + eps);
+    for (int i = threadIdx.x; i < width; i += 256)
+        y[base + i] = f2bf(__fmul_rn(__fmul_rn(bf2f(x[base + i]), inv), bf2f(w[i])));
+}
+
+/* ---- per-head RMSNorm, 128 partials (kernels.cu:81-101), in place ---------- */
+__device__ __forceinline__ float head_norm_value(float v, float wv, float eps, float* red) {
+    const float tot = block_tree<128, false>(__fmaf_rn(v, v, 0.f), red);
+    const float inv = rsqrtf(__fdiv_rn(tot, 128.0f) + eps);
+    return bf16_round(__fmul_rn(__fmul_rn(v, inv), wv));
+}
+
+__global__ void __launch_bounds__(128) k_head_norm(__nv_bfloat16* __restrict__ qk,
+                                                   const __nv_bfloat16* __restrict__ w, float eps) {
+    __shared__ float red[128];
+    const size_t o = (size_t)blockIdx.x * 128 + threadIdx.x;
+    qk[o] = f2bf(head_norm_value(bf2f(qk[o]), bf2f(w[threadIdx.x]), eps, red));
+}
+
+/* ---- RoPE (kernels.cu:114-139): angle in f32, cos/sin through bf16, no fma - */
+__global__ void __launch_bounds__(256) k_rope(__nv_bfloat16* __restrict__ x, int rows, int heads, int head_dim,
+                                              int pos0, const int32_t* __restrict__ pos_arr, float rope_base) {
+    const int pairs = head_dim >> 1;
+    const int64_t total = (int64_t)rows * heads * pairs;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int i = (int)(idx % pairs);
+        const int64_t rh = idx / pairs;
+        const int r = (int)(rh / heads);
+        const int p = pos_arr ? pos_arr[r] : pos0 + r;
+        const float ex = __fdiv_rn((float)(2 * i), (float)head_dim);
+        const float inv = __fdiv_rn(1.0f, powf(rope_base, ex));
+        const float ang = __fmul_rn((float)p, inv);
+        const float c = bf16_round(cosf(ang)), s = bf16_round(sinf(ang));
+        __nv_bfloat16* px = x + rh * head_dim + 2 * i;
+        const float x0 = bf2f(px[0]), x1 = bf2f(px[1]);
+        px[0] = f2bf(__fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s)));
+        px[1] = f2bf(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s)));
+    }
+}
+
+/* ---- qkv post-processing in one pass --------------------------------------
+ * For every row: q heads -> (qk-norm) -> RoPE -> q buffer; k heads -> (qk-norm)
+ * -> RoPE -> cache at pos (bf16 copy or INT8 quantise); v heads -> cache.
+ * Equals the reference's split + 2 qk_norm + 2 rope + append sequence
+ * (src/slowar/slowar.c:166-243), one bf16 rounding after each of its steps.
+ * grid (rows, q_heads + 2 kv_heads), 128 threads. */
+__global__ void __launch_bounds__(128) k_qkv_post(QkvPostArgs a) {
+    __shared__ float red[128];
+    const int r = blockIdx.x, h = blockIdx.y, t = threadIdx.x;
+    const int QH = a.q_heads, KVH = a.kv_heads;
+    const int width = (QH + 2 * KVH) * 128;
+    const int pos = a.pos_arr ? a.pos_arr[r] : a.pos0 + r * a.pos_row_step;
+    float v = bf2f(a.qkv[(size_t)r * width + (size_t)h * 128 + t]);
+    const bool is_q = h < QH, is_k = !is_q && h < QH + KVH;
+    if (is_q || is_k) {
+        const __nv_bfloat16* nw = is_q ? a.q_norm : a.k_norm;
+        if (nw) v = head_norm_value(v, bf2f(nw[t]), a.eps, red);
+        float c, s;
+        rope_cs(t >> 1, pos, a.rope_base, c, s);
+        const float other = __shfl_xor_sync(S2P_FULL_MASK, v, 1);
+        v = rope_elem(t, v, other, c, s);
+    }
+    if (is_q) {
+        a.q[((size_t)r * QH + h) * 128 + t] = f2bf(v);
+        return;
+    }
+    const int kvh = is_k ? h - QH : h - QH - KVH;
+    const size_t vec = (size_t)kvh * a.max_seq + pos;
+    unsigned char* cache = kv_payload(a.kv, r) + (is_k ? a.kv.k_off : a.kv.v_off);
+    if (!a.kv8) {
+        reinterpret_cast<__nv_bfloat16*>(cache)[vec * 128 + t] = f2bf(v);
+    } else {
+        unsigned char* scales = kv_scales(a.kv, r) + (is_k ? a.kv.ks_off : a.kv.vs_off);
+        __half hsc;
+        const int8_t q8 = kv8_quant(v, hsc);
+        reinterpret_cast<int8_t*>(cache)[vec * 128 + t] = q8;
+        if ((t & 31) == 0) reinterpret_cast<__half*>(scales)[vec * 4 + (t >> 5)] = hsc;
+    }
+}
+
+cudaError_t qkv_post(const QkvPostArgs* a, int rows, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    dim3 grid((unsigned)rows, (unsigned)(a->q_heads + 2 * a->kv_heads));
+    k_qkv_post<<<grid, 128, 0, st>>>(*a);
+    return cudaGetLastError();
+}
+
+/* ---- plain KV append (contract s2pk_kv_append, kernels.cu:172-195) --------- */
+__global__ void __launch_bounds__(256) k_kv_append(const __nv_bfloat16* __restrict__ k,
+                                                   const __nv_bfloat16* __restrict__ v,
+                                                   __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
+                                                   int rows, int kv_heads, int head_dim, int pos0, int max_seq) {
+    const int64_t total = (int64_t)rows * kv_heads * head_dim;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int d = (int)(idx % head_dim);
+        const int64_t rh = idx / head_dim;
+        const int h = (int)(rh % kv_heads), r = (int)(rh / kv_heads);
+        const size_t dst = ((size_t)h * max_seq + pos0 + r) * head_dim + d;
+        kc[dst] = k[idx];
+        vc[dst] = v[idx];
+    }
+}
+
+/* ---- single-pass causal GQA attention, tiles of 128 positions -------------
+ * Arithmetic of kernels.cu:234-309 (bf16 cache) and :625-728 (INT8 cache):
+ * per position one 128-term fma chain (INT8: four 32-term chains folded with
+ * the f16 group scale), tile max/sum by 128-wide trees, running
+ * l = fma(l, corr, tile_sum), acc *= corr, then a sequential fma over the tile.
+ * Here one CTA serves the four q heads of a kv head (512 threads) and stages
+ * the K tile in shared memory with a skewed row stride. */
+template <bool KV8>
+__global__ void __launch_bounds__(512) k_attn_single(AttnArgs a) {
+    constexpr int TS = KV8 ? 132 : 260; /* bytes per staged row: 128 B / 256 B payload + 4 B skew */
+    __shared__ __align__(16) unsigned char tile[128 * TS];
+    __shared__ float sq[4][128];
+    __shared__ float sp[4][128];
+    __shared__ float red[4][128];
+    __shared__ __half ssc[128 * 4];
+    const int row = blockIdx.x, kvh = blockIdx.y;
+    const int g = threadIdx.x >> 7, t = threadIdx.x & 127;
+    const int QH = a.q_heads;
+    const int h = kvh * 4 + g;
+    const int len = (a.pos_arr ? a.pos_arr[row] : a.pos0 + row * a.pos_row_step) + 1;
+    const size_t plane = (size_t)kvh * a.max_seq;
+    const unsigned char* kc = kv_payload(a.kv, row) + a.kv.k_off;
+    const unsigned char* vc = kv_payload(a.kv, row) + a.kv.v_off;
+    const __half* ks = KV8 ? reinterpret_cast<const __half*>(kv_scales(a.kv, row) + a.kv.ks_off) : nullptr;
+    const __half* vs = KV8 ? reinterpret_cast<const __half*>(kv_scales(a.kv, row) + a.kv.vs_off) : nullptr;
+    constexpr int VB = KV8 ? 128 : 256; /* payload bytes per cached vector */
+
+    const float scale = rsqrtf((float)a.head_dim); /* run-time value on purpose, see AttnArgs */
+    sq[g][t] = __fmul_rn(bf2f(a.q[((size_t)row * QH + h) * 128 + t]), scale);
+
+    float m = -INFINITY, l = 0.f, acc = 0.f;
+    for (int t0 = 0; t0 < len; t0 += 128) {
+        const int lim = min(128, len - t0);
+        __syncthreads(); /* previous tile fully consumed; sq visible */
+        /* stage K rows [t0, t0+lim) */
+        for (int i = threadIdx.x; i < lim * (VB / 4); i += 512) {
+            const int rr = i / (VB / 4), cw = i - rr * (VB / 4);
+            *reinterpret_cast<uint32_t*>(tile + rr * TS + cw * 4) =
+                *reinterpret_cast<const uint32_t*>(kc + (plane + t0 + rr) * VB + cw * 4);
+        }
+        if (KV8)
+            for (int i = threadIdx.x; i < lim * 4; i += 512) ssc[i] = ks[(plane + t0) * 4 + i];
+        __syncthreads();
+        float s = -INFINITY;
+        if (t < lim) {
+            float d = 0.f;
+            if (!KV8) {
+                const __nv_bfloat162* kr = reinterpret_cast<const __nv_bfloat162*>(tile + t * TS);
+#pragma unroll 8
+                for (int e = 0; e < 64; e++) {
+                    const float2 kf = __bfloat1622float2(kr[e]);
+                    d = __fmaf_rn(sq[g][2 * e], kf.x, d);
+                    d = __fmaf_rn(sq[g][2 * e + 1], kf.y, d);
+                }
+            } else {
+                const int8_t* kr = reinterpret_cast<const int8_t*>(tile + t * TS);
+#pragma unroll
+                for (int gi = 0; gi < 4; gi++) {
+                    float pp = 0.f;
+#pragma unroll 8
+                    for (int e = 0; e < 32; e++) pp = __fmaf_rn(sq[g][gi * 32 + e], (float)kr[gi * 32 + e], pp);
+                    d = __fmaf_rn(pp, __half2float(ssc[t * 4 + gi]), d);
+                }
+            }
+            s = d;
+        }
+        /* tile max and sum over 128 slots, per head (4 warps per head) */
+        red[g][t] = s;
+        __syncthreads();
+        for (int off = 64; off >= 32; off >>= 1) {
+            if (t < off) red[g][t] = fmaxf(red[g][t], red[g][t + off]);
+            __syncthreads();
+        }
+        float tmax = warp_tree_max(red[g][t & 31]);
+        __syncthreads();
+        const float m_new = fmaxf(m, tmax);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        const float p = (s == -INFINITY) ? 0.f : expf(s - m_new);
+        sp[g][t] = p;
+        red[g][t] = p;
+        __syncthreads();
+        for (int off = 64; off >= 32; off >>= 1) {
+            if (t < off) red[g][t] += red[g][t + off];
+            __syncthreads();
+        }
+        const float tsum = warp_tree_sum(red[g][t & 31]);
+        l = __fmaf_rn(l, corr, tsum);
+        acc = __fmul_rn(acc, corr);
+        __syncthreads(); /* K tile no longer needed: reuse the buffer for V */
+        for (int i = threadIdx.x; i < lim * (VB / 4); i += 512) {
+            const int rr = i / (VB / 4), cw = i - rr * (VB / 4);
+            *reinterpret_cast<uint32_t*>(tile + rr * TS + cw * 4) =
+                *reinterpret_cast<const uint32_t*>(vc + (plane + t0 + rr) * VB + cw * 4);
+        }
+        if (KV8)
+            for (int i = threadIdx.x; i < lim * 4; i += 512) ssc[i] = vs[(plane + t0) * 4 + i];
+        __syncthreads();
+        if (!KV8) {
+            for (int j = 0; j < lim; j++)
+                acc = __fmaf_rn(sp[g][j], bf2f(reinterpret_cast<const __nv_bfloat16*>(tile + j * TS)[t]), acc);
+        } else {
+            for (int j = 0; j < lim; j++)
+                acc = __fmaf_rn(__fmul_rn(sp[g][j], __half2float(ssc[j * 4 + (t >> 5)])),
+                                (float)reinterpret_cast<const int8_t*>(tile + j * TS)[t], acc);
+        }
+        m = m_new;
+    }
+    a.out[((size_t)row * QH + h) * 128 + t] = f2bf(__fdiv_rn(acc, l));
+}
+
+cudaError_t attn_single(const AttnArgs* a, int rows, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    if (a->q_heads != a->kv_heads * 4 || a->head_dim != 128) return cudaErrorInvalidValue;
+    dim3 grid((unsigned)rows, (unsigned)a->kv_heads);
+    if (a->kv8) k_attn_single<true><<<grid, 512, 0, st>>>(*a);
+    else k_attn_single<false><<<grid, 512, 0, st>>>(*a);
+    return cudaGetLastError();
+}
+
+/* ---- SwiGLU (kernels.cu:1216-1229) ---------------------------------------- */
+__global__ void __launch_bounds__(256) k_silu_mul(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h,
+                                                  int64_t total, int ffn) {
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / ffn;
+        const int c = (int)(idx - r * ffn);
+        const float g = bf2f(gu[(size_t)r * 2 * ffn + c]);
+        const float u = bf2f(gu[(size_t)r * 2 * ffn + ffn + c]);
+        const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+        const float sil = bf16_round(__fmul_rn(g, sig));
+        h[idx] = f2bf(__fmul_rn(sil, u));
+    }
+}
+
+/* ---- residual add (kernels.cu:1242-1247) ----------------------------------- */
+__global__ void __launch_bounds__(256) k_add(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = f2bf(__fadd_rn(bf2f(y[i]), bf2f(x[i])));
+}
+
+/* ---- embedding gathers (kernels.cu:1258-1266, 1281-1291) ------------------- */
+__global__ void __launch_bounds__(256) k_embed(const __nv_bfloat16* __restrict__ table, const int64_t* __restrict__ ids,
+                                               __nv_bfloat16* __restrict__ out, int64_t total, int dim) {
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / dim;
+        out[idx] = table[(size_t)ids[r] * dim + (idx - r * dim)];
+    }
+}
+__global__ void __launch_bounds__(256) k_embed_i8(const int8_t* __restrict__ table, const float* __restrict__ scales,
+                                                  const int64_t* __restrict__ ids, __nv_bfloat16* __restrict__ out,
+                                                  int64_t total, int dim) {
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = idx / dim;
+        const int64_t id = ids[r];
+        out[idx] = f2bf(__fmul_rn((float)table[(size_t)id * dim + (idx - r * dim)], scales[id]));
+    }
+}
+
+/* ---- widen / argmax (kernels.cu:1308-1313, 1326-1357) ---------------------- */
+__global__ void __launch_bounds__(256) k_widen(const __nv_bfloat16* __restrict__ in, float* __restrict__ out, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = bf2f(in[i]);
+}
+
+/* "largest value, then lowest index" is a total order, so any reduction shape
+ * returns the reference's answer. */
+__global__ void __launch_bounds__(256) k_argmax(const __nv_bfloat16* __restrict__ logits, int32_t* __restrict__ ids,
+                                                int vocab) {
+    __shared__ float bv_s[8];
+    __shared__ int bi_s[8];
+    const size_t base = (size_t)blockIdx.x * vocab;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += 256) {
+        const float v = bf2f(logits[base + i]);
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(S2P_FULL_MASK, bv, off);
+        const int oi = __shfl_xor_sync(S2P_FULL_MASK, bi, off);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bv_s[threadIdx.x >> 5] = bv; bi_s[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int wv = 1; wv < 8; wv++)
+            if (bv_s[wv] > bv || (bv_s[wv] == bv && bi_s[wv] < bi)) { bv = bv_s[wv]; bi = bi_s[wv]; }
+        ids[blockIdx.x] = bi == 0x7fffffff ? 0 : bi; /* all -inf / NaN rows: index 0, as the reference */
+    }
+}
+
+/* ---- VQ glue (fastar.cu:104-127; kernels.cu:1399-1421) --------------------- */
+__global__ void __launch_bounds__(256) k_vq_embed_add(const __nv_bfloat16* __restrict__ table,
+                                                      const int32_t* __restrict__ codes, int T,
+                                                      __nv_bfloat16* __restrict__ rows, int dim, int ncb, int cbsize) {
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < dim; d += 256) {
+        float acc = 0.f;
+        for (int cb = 0; cb < ncb; cb++) {
+            int c = codes[(size_t)cb * T + t];
+            c = max(0, min(cbsize - 1, c));
+            acc = __fadd_rn(acc, bf2f(table[((size_t)cb * cbsize + c) * dim + d]));
+        }
+        const size_t o = (size_t)t * dim + d;
+        rows[o] = f2bf(__fadd_rn(bf2f(rows[o]), bf16_round(acc)));
+    }
+}
+__global__ void __launch_bounds__(256) k_scale_div(__nv_bfloat16* __restrict__ x, int64_t n, float div) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        x[i] = f2bf(__fdiv_rn(bf2f(x[i]), div));
+}
+__global__ void __launch_bounds__(256) k_scale_rows_masked(__nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ mask,
+                                                           int64_t total, int dim, float scale) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+        if (mask[i / dim]) x[i] = f2bf(__fmul_rn(bf2f(x[i]), scale));
+}
+__global__ void k_embed_codes(const __nv_bfloat16* __restrict__ table, const int32_t* __restrict__ codes,
+                              __nv_bfloat16* __restrict__ out, int rows, int dim, int cbsize) {
+    /* fast-AR step input: row of the 4096-entry table, code clamped (fastar.cu:150-158) */
+    const int r = blockIdx.x;
+    const int c = max(0, min(cbsize - 1, codes[r]));
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) out[(size_t)r * dim + d] = table[(size_t)c * dim + d];
+}
+__global__ void k_pack_frame(const int32_t* __restrict__ stage, int rows, int32_t* __restrict__ codes) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * 9) return;
+    const int cb = i / rows, b = i - cb * rows;
+    codes[(size_t)b * 10 + cb + 1] = stage[i];
+}
+
+/* ---- internal launchers ---------------------------------------------------- */
+cudaError_t rms_norm(const void* x, const void* w, void* y, int rows, int width, float eps, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    k_rms_norm<<<rows, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, width, eps);
+    return cudaGetLastError();
+}
+cudaError_t silu_mul(const void* gu, void* h, int rows, int ffn, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    const int64_t total = (int64_t)rows * ffn;
+    k_silu_mul<<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, total, ffn);
+    return cudaGetLastError();
+}
+cudaError_t add_inplace(void* y, const void* x, int64_t n, cudaStream_t st) {
+    if (n <= 0) return cudaSuccess;
+    k_add<<<grid_for(n, 256), 256, 0, st>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x, n);
+    return cudaGetLastError();
+}
+cudaError_t embed_rows(const void* table, const int64_t* ids, void* out, int rows, int dim, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    const int64_t total = (int64_t)rows * dim;
+    k_embed<<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)table, ids, (__nv_bfloat16*)out, total, dim);
+    return cudaGetLastError();
+}
+cudaError_t embed_rows_i8(const void* table, const float* scales, const int64_t* ids, void* out, int rows, int dim,
+                          cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    const int64_t total = (int64_t)rows * dim;
+    k_embed_i8<<<grid_for(total, 256), 256, 0, st>>>((const int8_t*)table, scales, ids, (__nv_bfloat16*)out, total, dim);
+    return cudaGetLastError();
+}
+cudaError_t vq_embed_add(const void* table, const int32_t* codes_dev, int T, void* rows, cudaStream_t st) {
+    if (T <= 0) return cudaSuccess;
+    k_vq_embed_add<<<T, 256, 0, st>>>((const __nv_bfloat16*)table, codes_dev, T, (__nv_bfloat16*)rows, S2P_DIM,
+                                      S2P_NUM_CODEBOOKS, S2P_CB_SIZE);
+    return cudaGetLastError();
+}
+cudaError_t scale_div(void* x, int64_t n, float divisor, cudaStream_t st) {
+    if (n <= 0) return cudaSuccess;
+    k_scale_div<<<grid_for(n, 256), 256, 0, st>>>((__nv_bfloat16*)x, n, divisor);
+    return cudaGetLastError();
+}
+cudaError_t scale_rows_masked(void* x, const uint8_t* mask, int rows, int dim, float scale, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    const int64_t total = (int64_t)rows * dim;
+    k_scale_rows_masked<<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat16*)x, mask, total, dim, scale);
+    return cudaGetLastError();
+}
+cudaError_t embed_codes(const void* table, const int32_t* codes, void* out, int rows, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    k_embed_codes<<<rows, 256, 0, st>>>((const __nv_bfloat16*)table, codes, (__nv_bfloat16*)out, rows, S2P_DIM, S2P_CB_SIZE);
+    return cudaGetLastError();
+}
+cudaError_t argmax_rows(const void* logits, int32_t* ids, int rows, int vocab, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    k_argmax<<<rows, 256, 0, st>>>((const __nv_bfloat16*)logits, ids, vocab);
+    return cudaGetLastError();
+}
+cudaError_t pack_frame(const int32_t* stage, int rows, int32_t* codes, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    k_pack_frame<<<(rows * 9 + 127) / 128, 128, 0, st>>>(stage, rows, codes);
+    return cudaGetLastError();
+}
+
+}  // namespace s2p
+
+using namespace s2p;
+
+/* ======================= exported primitive contract ======================= */
+extern "C" cudaError_t s2pk_rms_norm(const s2p_bf16* x, const s2p_bf16* w, s2p_bf16* y, int rows, int width,
+                                     float eps, cudaStream_t st) {
+    return rms_norm(x, w, y, rows, width, eps, st);
+}
+
+extern "C" cudaError_t s2pk_qk_norm(s2p_bf16* qk, const s2p_bf16* w, int rows, int heads, int head_dim, float eps,
+                                    cudaStream_t st) {
+    if (rows <= 0 || w == NULL) return cudaSuccess; /* the fast-AR passes no gain: no-op */
+    if (head_dim != 128) return cudaErrorInvalidValue;
+    k_head_norm<<<rows * heads, 128, 0, st>>>((__nv_bfloat16*)qk, (const __nv_bfloat16*)w, eps);
+    return cudaGetLastError();
+}
+
+extern "C" cudaError_t s2pk_rope(s2p_bf16* q, s2p_bf16* k, int rows, int q_heads, int kv_heads, int head_dim,
+                                 int pos, float rope_base, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    k_rope<<<grid_for((int64_t)rows * q_heads * (head_dim / 2), 256), 256, 0, st>>>((__nv_bfloat16*)q, rows, q_heads,
+                                                                                   head_dim, pos, NULL, rope_base);
+    k_rope<<<grid_for((int64_t)rows * kv_heads * (head_dim / 2), 256), 256, 0, st>>>((__nv_bfloat16*)k, rows, kv_heads,
+                                                                                    head_dim, pos, NULL, rope_base);
+    return cudaGetLastError();
+}
+
+extern "C" cudaError_t s2pk_kv_append(const s2p_bf16* k, const s2p_bf16* v, s2p_bf16* k_cache, s2p_bf16* v_cache,
+                                      int rows, int kv_heads, int head_dim, int pos, int max_seq, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    k_kv_append<<<grid_for((int64_t)rows * kv_heads * head_dim, 256), 256, 0, st>>>(
+        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, rows,
+        kv_heads, head_dim, pos, max_seq);
+    return cudaGetLastError();
+}
+
+extern "C" cudaError_t s2pk_attention(const s2p_bf16* q, const s2p_bf16* k_cache, const s2p_bf16* v_cache,
+                                      s2p_bf16* out, int rows, int q_heads, int kv_heads, int head_dim, int pos,
+                                      int max_seq, cudaStream_t st) {
+    if (rows <= 0) return cudaSuccess;
+    if (head_dim != 128) return cudaErrorInvalidValue;
+    AttnArgs a = {};
+    a.q = (const __nv_bfloat16*)q; a.out = (__nv_bfloat16*)out;
+    /* two independent planes: address both from the K plane's base */
+    a.kv.base0 = (void*)k_cache;
+    a.kv.k_off = 0;
+    a.kv.v_off = (size_t)((const char*)v_cache - (const char*)k_cache);
+    a.q_heads = q_heads; a.kv_heads = kv_heads; a.pos0 = pos; a.pos_row_step = 1; a.max_seq = max_seq; a.head_dim = head_dim;
+    return attn_single(&a, rows, st);
+}
+
+extern "C" cudaError_t s2pk_silu_mul(const s2p_bf16* gu, s2p_bf16* h, int rows, int ffn, cudaStream_t st) {
+    return silu_mul(gu, h, rows, ffn, st);
+}
+extern "C" cudaError_t s2pk_add(s2p_bf16* y, const s2p_bf16* x, int64_t n, cudaStream_t st) {
+    return add_inplace(y, x, n, st);
+}
+extern "C" cudaError_t s2pk_embed(const s2p_bf16* table, const int64_t* ids, s2p_bf16* out, int rows, int dim,
+                                  cudaStream_t st) {
+    return embed_rows(table, ids, out, rows, dim, st);
+}
+extern "C" cudaError_t s2pk_sample_prepare(const s2p_bf16* logits, float* scratch, int vocab, cudaStream_t st) {
+    if (vocab <= 0) return cudaSuccess;
+    k_widen<<<grid_for(vocab, 256), 256, 0, st>>>((const __nv_bfloat16*)logits, scratch, vocab);
+    return cudaGetLastError();
+}
+extern "C" cudaError_t s2pk_argmax(const s2p_bf16* logits, int32_t* ids, int rows, int vocab, cudaStream_t st) {
+    return argmax_rows(logits, ids, rows, vocab, st);
+}

@@ -1,0 +1,700 @@
+/* Sessions, prefill, KV-prefix blobs and the lockstep decode tick of the model
+ * contract (include/s2pro/model.h:46-76 of the reference; semantics of
+ * src/slowar/slowar.c:40-117 sessions, :264-379 prefill, :399-449 KV blobs,
+ * :463-606 the device sequence of one tick, :609-826 staging / graph / harvest,
+ * and src/fastar/fastar.cu:726-788 the fast-AR frame).
+ *
+ * Two device sequences produce one frame, with bit-identical results:
+ *   - the general one (any number of rows): one launch per operation group,
+ *     GEMVs in slices of <= 16 rows;
+ *   - the batch-1 one: fused stages (norm -> GEMV, GEMV -> residual,
+ *     norm -> GEMV -> SwiGLU, attention with its prologue, head -> arg-max).
+ * Either is captured once per batch size into a CUDA graph and replayed; all
+ * per-frame variation travels through the pinned upload block.
+ */
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+#include "internal.h"
+
+#define BF(t) ((s2p_dev_bf16*)(t).data)
+#define FA_KVSZ (S2P_SLOW_KV_HEADS * S2P_FAST_SEQ * S2P_HEAD_DIM)
+
+static const double SQRT11 = 3.3166247903554; /* sqrt(num_codebooks + 1) */
+
+static int is_semantic(int64_t tok) { return tok >= S2P_TOK_SEMANTIC_START && tok <= S2P_TOK_SEMANTIC_END; }
+
+/* ---- parity dump hooks: S2P_DUMP_DIR/<name>.f32, raw little-endian f32
+ * (src/slowar/debug_dump.c:15-61) ------------------------------------------ */
+static const char* dump_dir(void) {
+    static int init = 0;
+    static const char* dir = NULL;
+    if (!init) {
+        dir = getenv("S2P_DUMP_DIR");
+        if (dir && !dir[0]) dir = NULL;
+        init = 1;
+    }
+    return dir;
+}
+
+static void dump_bf16(const char* name, const void* dev, int64_t n, cudaStream_t st) {
+    const char* dir = dump_dir();
+    if (!dir) return;
+    uint16_t* h = (uint16_t*)malloc((size_t)n * 2);
+    float* f = (float*)malloc((size_t)n * 4);
+    if (h && f && cudaStreamSynchronize(st) == cudaSuccess &&
+        cudaMemcpy(h, dev, (size_t)n * 2, cudaMemcpyDeviceToHost) == cudaSuccess) {
+        for (int64_t i = 0; i < n; i++) {
+            const uint32_t u = (uint32_t)h[i] << 16;
+            memcpy(&f[i], &u, 4);
+        }
+        char path[1200];
+        snprintf(path, sizeof(path), "%s/%s.f32", dir, name);
+        FILE* fp = fopen(path, "wb");
+        if (fp) {
+            fwrite(f, 4, (size_t)n, fp);
+            fclose(fp);
+        } else {
+            fprintf(stderr, "[s2pro] dump: cannot open %s\n", path);
+        }
+    }
+    free(h);
+    free(f);
+}
+
+/* ---- sessions ---------------------------------------------------------------- */
+s2p_status s2p_session_create(s2p_model* m, const s2p_sampling_cfg* cfg, s2p_session** out) {
+    if (!m || !out) return S2P_ERR_INVALID;
+    *out = NULL;
+    if (m->n_sessions >= m->max_sessions) return S2P_ERR_FULL;
+    s2p_session* s = (s2p_session*)calloc(1, sizeof(*s));
+    if (!s) return S2P_ERR_OOM;
+    s->m = m;
+    s->state = SESS_NEW;
+    const int64_t kv_shape[4] = {m->n_slow, S2P_KV_PLANES_PER_LAYER, m->ctx_len, S2P_HEAD_DIM};
+    s2p_status rc = s2p_tensor_device_alloc(&s->kv, m->kv8 ? S2P_DT_I8 : S2P_DT_BF16, 4, kv_shape);
+    if (rc == S2P_OK && m->kv8) {
+        const int64_t sc_shape[4] = {m->n_slow, S2P_KV_PLANES_PER_LAYER, m->ctx_len, S2P_HEAD_DIM / 32};
+        rc = s2p_tensor_device_alloc(&s->kvs, S2P_DT_F16, 4, sc_shape);
+    }
+    if (rc == S2P_OK) {
+        const int64_t h_shape[1] = {S2P_DIM};
+        rc = s2p_tensor_device_alloc(&s->pending_hidden, S2P_DT_BF16, 1, h_shape);
+    }
+    if (rc == S2P_OK) {
+        struct timespec ts;
+        clock_gettime(CLOCK_MONOTONIC, &ts);
+        const uint64_t entropy = ((uint64_t)ts.tv_sec * 1000000000ULL + (uint64_t)ts.tv_nsec) ^ (uint64_t)(uintptr_t)s;
+        s2p_sampler_init(&s->sampler, cfg, entropy);
+        SamplerState hst;
+        memset(&hst, 0, sizeof(hst));
+        memcpy(hst.rng, s->sampler.rng, sizeof(hst.rng));
+        hst.temperature = s->sampler.temperature;
+        hst.top_p = s->sampler.top_p;
+        hst.rep_penalty = s->sampler.rep_penalty;
+        hst.window = s->sampler.window;
+        hst.seeded = s->sampler.seeded;
+        hst.seed31 = s->sampler.seed31;
+        if (cudaMalloc(&s->dsamp, sizeof(hst)) != cudaSuccess ||
+            cudaMemcpy(s->dsamp, &hst, sizeof(hst), cudaMemcpyHostToDevice) != cudaSuccess)
+            rc = S2P_ERR_CUDA;
+    }
+    if (rc != S2P_OK) {
+        if (s->dsamp) cudaFree(s->dsamp);
+        s2p_tensor_free(&s->kv);
+        s2p_tensor_free(&s->kvs);
+        s2p_tensor_free(&s->pending_hidden);
+        free(s);
+        return rc;
+    }
+    m->n_sessions++;
+    *out = s;
+    return S2P_OK;
+}
+
+void s2p_session_destroy(s2p_session* s) {
+    if (!s) return;
+    if (s->m) {
+        cudaStreamSynchronize(s->m->stream);
+        s->m->n_sessions--;
+    }
+    s2p_tensor_free(&s->kv);
+    s2p_tensor_free(&s->kvs);
+    s2p_tensor_free(&s->pending_hidden);
+    if (s->dsamp) cudaFree(s->dsamp);
+    free(s);
+}
+
+/* ---- one layer, general sequence ---------------------------------------------- */
+typedef struct {
+    int rows;
+    KvRef kv;       /* k_off/v_off/ks_off/vs_off filled per layer by the caller */
+    int max_seq, kv8;
+    int pos0, pos_row_step;
+    const int32_t* pos_arr;
+    int split_k;    /* decode: split-K attention; else the single-pass kernel */
+    int decode;     /* decode-sized rows: GEMV in slices instead of the prefill GEMM */
+} layer_ctx;
+
+static s2p_status lin_apply(s2p_model* m, const s2p_linear* lin, const void* x, void* y, int rows, int decode) {
+    if (decode && m->mode == S2P_GEMM_INT8 && lin->int8_ready) return s2p_linear_gemv_rows(lin, x, y, rows, m->stream);
+    return s2p_linear_forward(lin, x, y, rows, m->mode, m->stream);
+}
+
+static int attn_workers_for(int rows) {
+    int w = 296 / (rows * S2P_SLOW_KV_HEADS);
+    return w < 1 ? 1 : (w > 16 ? 16 : w);
+}
+
+/* x: residual stream [rows, 2560]; scratch tensors: norm/qkv/q/attn/proj/gu/hff */
+static s2p_status layer_general(s2p_model* m, const s2p_layer* L, const layer_ctx* c, s2p_dev_bf16* x,
+                                s2p_dev_bf16* norm, s2p_dev_bf16* qkv, s2p_dev_bf16* q, s2p_dev_bf16* attn,
+                                s2p_dev_bf16* proj, s2p_dev_bf16* gu, s2p_dev_bf16* hff) {
+    cudaStream_t st = m->stream;
+    const int rows = c->rows;
+    S2P_CUDA_TRY(rms_norm(x, L->attn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
+    S2P_TRY(lin_apply(m, &L->wqkv, norm, qkv, rows, c->decode));
+    QkvPostArgs qa;
+    memset(&qa, 0, sizeof(qa));
+    qa.qkv = qkv; qa.q = q;
+    qa.q_norm = (const s2p_dev_bf16*)L->q_norm.data; qa.k_norm = (const s2p_dev_bf16*)L->k_norm.data;
+    qa.eps = S2P_NORM_EPS; qa.rope_base = S2P_ROPE_BASE;
+    qa.q_heads = S2P_SLOW_Q_HEADS; qa.kv_heads = S2P_SLOW_KV_HEADS; qa.max_seq = c->max_seq; qa.kv8 = c->kv8;
+    qa.pos0 = c->pos0; qa.pos_row_step = c->pos_row_step; qa.pos_arr = c->pos_arr; qa.kv = c->kv;
+    S2P_CUDA_TRY(qkv_post(&qa, rows, st));
+    AttnArgs aa;
+    memset(&aa, 0, sizeof(aa));
+    aa.q = q; aa.out = attn;
+    aa.q_heads = S2P_SLOW_Q_HEADS; aa.kv_heads = S2P_SLOW_KV_HEADS; aa.max_seq = c->max_seq; aa.kv8 = c->kv8;
+    aa.pos0 = c->pos0; aa.pos_row_step = c->pos_row_step; aa.pos_arr = c->pos_arr; aa.kv = c->kv;
+    aa.head_dim = S2P_HEAD_DIM;
+    if (c->split_k) {
+        aa.part = (float*)m->attn_part.data; aa.counters = m->attn_ctr;
+        aa.n_split_slots = m->n_split_slots; aa.workers = attn_workers_for(rows);
+        S2P_CUDA_TRY(attn_decode(&aa, rows, st));
+    } else {
+        S2P_CUDA_TRY(attn_single(&aa, rows, st));
+    }
+    S2P_TRY(lin_apply(m, &L->wo, attn, proj, rows, c->decode));
+    S2P_CUDA_TRY(add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
+    S2P_CUDA_TRY(rms_norm(x, L->ffn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
+    S2P_TRY(lin_apply(m, &L->gate_up, norm, gu, rows, c->decode));
+    S2P_CUDA_TRY(silu_mul(gu, hff, rows, S2P_FFN_DIM, st));
+    S2P_TRY(lin_apply(m, &L->w2, hff, proj, rows, c->decode));
+    S2P_CUDA_TRY(add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
+    return S2P_OK;
+}
+
+static void slow_kv_offsets(const s2p_model* m, int layer, KvRef* kv) {
+    const size_t plane = s2p_kv_plane_bytes(m), splane = s2p_kvs_plane_bytes(m);
+    kv->k_off = (size_t)layer * S2P_KV_PLANES_PER_LAYER * plane;
+    kv->v_off = kv->k_off + (size_t)S2P_SLOW_KV_HEADS * plane;
+    kv->ks_off = (size_t)layer * S2P_KV_PLANES_PER_LAYER * splane;
+    kv->vs_off = kv->ks_off + (size_t)S2P_SLOW_KV_HEADS * splane;
+}
+
+static void fast_kv_ref(const s2p_model* m, int layer, KvRef* kv) {
+    memset(kv, 0, sizeof(*kv));
+    kv->base0 = (char*)m->fkv.data + (size_t)layer * m->max_sessions * 2 * FA_KVSZ * 2;
+    kv->row_stride = (size_t)2 * FA_KVSZ * 2;
+    kv->k_off = 0;
+    kv->v_off = (size_t)FA_KVSZ * 2;
+}
+
+/* ---- prefill ------------------------------------------------------------------ */
+s2p_status s2p_session_prefill(s2p_session* s, const int64_t* ids, const uint8_t* vq_mask, int n_ids,
+                               const s2p_vq_part* parts, int n_parts) {
+    if (!s || !ids || n_ids <= 0) return S2P_ERR_INVALID;
+    if (n_parts > 0 && (!parts || !vq_mask)) return S2P_ERR_INVALID;
+    s2p_model* m = s->m;
+    /* NEW, or PREFILLED again: a chunked prompt extends the cache at kv_len and
+     * refreshes the pending hidden state (src/slowar/slowar.c:271-278) */
+    if (s->state != SESS_NEW && s->state != SESS_PREFILLED) return S2P_ERR_STATE;
+    const int pos0 = s->kv_len;
+    if (pos0 + n_ids > m->ctx_len - 1) return S2P_ERR_INVALID; /* at least one decode slot must remain */
+    if (n_ids > m->scratch_rows) {
+        fprintf(stderr, "[s2pro] prefill of %d ids exceeds scratch capacity %d (raise S2P_SCRATCH_ROWS)\n", n_ids,
+                m->scratch_rows);
+        return S2P_ERR_INVALID;
+    }
+    for (int i = 0; i < n_ids; i++)
+        if (ids[i] < 0 || ids[i] >= S2P_TEXT_VOCAB) return S2P_ERR_INVALID;
+    int64_t total_mask = 0, total_t = 0;
+    if (vq_mask)
+        for (int i = 0; i < n_ids; i++) total_mask += vq_mask[i] ? 1 : 0;
+    if (n_parts > 64) return S2P_ERR_INVALID;
+    for (int p = 0; p < n_parts; p++) {
+        if (!parts[p].codes || parts[p].T <= 0) return S2P_ERR_INVALID;
+        for (int64_t j = 0; j < (int64_t)S2P_NUM_CODEBOOKS * parts[p].T; j++)
+            if (parts[p].codes[j] < 0 || parts[p].codes[j] >= S2P_CB_SIZE) return S2P_ERR_INVALID;
+        total_t += parts[p].T;
+    }
+    if (total_mask != total_t) return S2P_ERR_INVALID;
+
+    cudaStream_t st = m->stream;
+    /* caller buffers are pageable: synchronous copies */
+    S2P_CUDA_TRY(cudaMemcpy(m->sids.data, ids, (size_t)n_ids * sizeof(int64_t), cudaMemcpyHostToDevice));
+    int part_start[64];
+    size_t part_off[64];
+    {
+        int cur = 0;
+        size_t off = 0;
+        for (int p = 0; p < n_parts; p++) {
+            while (cur < n_ids && !vq_mask[cur]) cur++;
+            const int T = parts[p].T;
+            if (cur + T > n_ids) return S2P_ERR_INVALID;
+            for (int t = 0; t < T; t++)
+                if (!vq_mask[cur + t]) return S2P_ERR_INVALID; /* a part must cover one unbroken masked run */
+            part_start[p] = cur;
+            part_off[p] = off;
+            S2P_CUDA_TRY(cudaMemcpy((int32_t*)m->svq.data + off, parts[p].codes,
+                                    (size_t)S2P_NUM_CODEBOOKS * T * sizeof(int32_t), cudaMemcpyHostToDevice));
+            off += (size_t)S2P_NUM_CODEBOOKS * T;
+            cur += T;
+        }
+    }
+    if (m->embed_i8_only)
+        S2P_CUDA_TRY(embed_rows_i8(m->embed_i8.data, (const float*)m->embed_scale.data, (const int64_t*)m->sids.data,
+                                   m->sx.data, n_ids, S2P_DIM, st));
+    else
+        S2P_CUDA_TRY(embed_rows(m->embed.data, (const int64_t*)m->sids.data, m->sx.data, n_ids, S2P_DIM, st));
+    for (int p = 0; p < n_parts; p++) {
+        const int T = parts[p].T;
+        s2p_dev_bf16* rows0 = BF(m->sx) + (size_t)part_start[p] * S2P_DIM;
+        S2P_CUDA_TRY(vq_embed_add(m->cb_emb.data, (const int32_t*)m->svq.data + part_off[p], T, rows0, st));
+        /* prefill DIVIDES by sqrt(11); decode multiplies by the reciprocal (slowar.c:350-353) */
+        S2P_CUDA_TRY(scale_div(rows0, (int64_t)T * S2P_DIM, (float)SQRT11, st));
+    }
+
+    layer_ctx c;
+    memset(&c, 0, sizeof(c));
+    c.rows = n_ids;
+    c.kv.base0 = s->kv.data;
+    c.kv.sbase0 = s->kvs.data;
+    c.max_seq = m->ctx_len;
+    c.kv8 = m->kv8;
+    c.pos0 = pos0;
+    c.pos_row_step = 1;
+    for (int l = 0; l < m->n_slow; l++) {
+        slow_kv_offsets(m, l, &c.kv);
+        S2P_TRY(layer_general(m, &m->slow[l], &c, BF(m->sx), BF(m->snorm), BF(m->sqkv), BF(m->sq), BF(m->sattn),
+                              BF(m->sproj), BF(m->sgu), BF(m->sffn)));
+        if (dump_dir()) {
+            char nm[32];
+            snprintf(nm, sizeof(nm), "backbone_layer%02d", l);
+            dump_bf16(nm, BF(m->sx) + (size_t)(n_ids - 1) * S2P_DIM, S2P_DIM, st);
+        }
+    }
+    /* the final-normed LAST hidden is what frame 0 samples from and what primes the fast-AR */
+    S2P_CUDA_TRY(rms_norm(BF(m->sx) + (size_t)(n_ids - 1) * S2P_DIM, m->final_norm.data, s->pending_hidden.data, 1,
+                          S2P_DIM, S2P_NORM_EPS, st));
+    dump_bf16("backbone_final_norm", s->pending_hidden.data, S2P_DIM, st);
+    S2P_CUDA_TRY(cudaStreamSynchronize(st));
+    s->kv_len = pos0 + n_ids;
+    s->state = SESS_PREFILLED;
+    return S2P_OK;
+}
+
+/* ---- KV prefix blobs: the session's plane order at n_tokens depth, payload
+ * planes first, then (INT8 KV) the scale planes -------------------------------- */
+size_t s2p_session_kv_bytes(const s2p_model* m, int n_tokens) {
+    if (!m || n_tokens <= 0) return 0;
+    const size_t planes = (size_t)m->n_slow * S2P_KV_PLANES_PER_LAYER;
+    return planes * n_tokens * s2p_kv_vec_bytes(m) + (m->kv8 ? planes * n_tokens * (S2P_HEAD_DIM / 32) * 2 : 0);
+}
+
+static s2p_status kv_blob_copy(s2p_session* s, void* blob, int n_tokens, int save) {
+    s2p_model* m = s->m;
+    const size_t planes = (size_t)m->n_slow * S2P_KV_PLANES_PER_LAYER;
+    const size_t width = (size_t)n_tokens * s2p_kv_vec_bytes(m), pitch = s2p_kv_plane_bytes(m);
+    if (save)
+        S2P_CUDA_TRY(cudaMemcpy2DAsync(blob, width, s->kv.data, pitch, width, planes, cudaMemcpyDeviceToDevice, m->stream));
+    else
+        S2P_CUDA_TRY(cudaMemcpy2DAsync(s->kv.data, pitch, blob, width, width, planes, cudaMemcpyDeviceToDevice, m->stream));
+    if (m->kv8) {
+        char* sblob = (char*)blob + planes * width;
+        const size_t swidth = (size_t)n_tokens * (S2P_HEAD_DIM / 32) * 2, spitch = s2p_kvs_plane_bytes(m);
+        if (save)
+            S2P_CUDA_TRY(cudaMemcpy2DAsync(sblob, swidth, s->kvs.data, spitch, swidth, planes, cudaMemcpyDeviceToDevice,
+                                           m->stream));
+        else
+            S2P_CUDA_TRY(cudaMemcpy2DAsync(s->kvs.data, spitch, sblob, swidth, swidth, planes, cudaMemcpyDeviceToDevice,
+                                           m->stream));
+    }
+    S2P_CUDA_TRY(cudaStreamSynchronize(m->stream));
+    return S2P_OK;
+}
+
+s2p_status s2p_session_kv_save(s2p_session* s, int n_tokens, void* blob_dev) {
+    if (!s || !blob_dev || n_tokens <= 0 || n_tokens > s->kv_len) return S2P_ERR_INVALID;
+    return kv_blob_copy(s, blob_dev, n_tokens, 1);
+}
+
+s2p_status s2p_session_kv_load(s2p_session* s, const void* blob_dev, int n_tokens) {
+    if (!s || !blob_dev || n_tokens <= 0) return S2P_ERR_INVALID;
+    if (s->state != SESS_NEW || s->kv_len != 0) return S2P_ERR_STATE;
+    if (n_tokens > s->m->ctx_len - 1) return S2P_ERR_INVALID;
+    S2P_TRY(kv_blob_copy(s, (void*)blob_dev, n_tokens, 0));
+    s->kv_len = n_tokens;
+    return S2P_OK;
+}
+
+/* ---- the decode tick ------------------------------------------------------------ */
+typedef struct {
+    const int64_t* ids; const int32_t* codes; const int32_t* pos; const uint8_t* mask;
+    void* const* kv_bases; void* const* kvs_bases; SamplerState* const* samp;
+    int64_t* tok; int32_t* sem; int32_t* ocodes; uint8_t* eos;
+} tick_dev;
+
+static void tick_views(const s2p_model* m, tick_dev* d) {
+    char* u = (char*)m->d_up;
+    d->kv_bases = (void* const*)(u + m->off_kvb);
+    d->kvs_bases = (void* const*)(u + m->off_kvsb);
+    d->samp = (SamplerState* const*)(u + m->off_samp);
+    d->ids = (const int64_t*)(u + m->off_ids);
+    d->codes = (const int32_t*)(u + m->off_codes);
+    d->pos = (const int32_t*)(u + m->off_pos);
+    d->mask = (const uint8_t*)(u + m->off_mask);
+    char* o = (char*)m->d_out;
+    d->tok = (int64_t*)o;
+    d->sem = (int32_t*)(o + m->off_sem);
+    d->ocodes = (int32_t*)(o + m->off_ocodes);
+    d->eos = (uint8_t*)(o + m->off_eos);
+}
+
+static s2p_status tick_begin_rows(s2p_model* m, const tick_dev* d, int bd) {
+    TickBeginArgs a;
+    memset(&a, 0, sizeof(a));
+    if (!m->embed_i8_only) a.embed = (const s2p_dev_bf16*)m->embed.data;
+    a.embed_i8 = (const int8_t*)m->embed_i8.data;
+    a.embed_scale = (const float*)m->embed_scale.data;
+    a.cb_emb = (const s2p_dev_bf16*)m->cb_emb.data;
+    a.ids = d->ids; a.codes = d->codes; a.mask = d->mask;
+    a.x = BF(m->sx);
+    a.keys = m->fkeys;
+    S2P_CUDA_TRY(tick_begin(&a, bd, m->stream));
+    return S2P_OK;
+}
+
+/* tied head + sampler on `nact` final-normed rows of shidden */
+static s2p_status head_and_sample(s2p_model* m, const tick_dev* d, int nact, int dump_ok) {
+    cudaStream_t st = m->stream;
+    const int full = m->head_full;
+    if (!full) {
+        /* only the 4096 semantic rows and the EOS row of the sidecar can be sampled
+         * (src/slowar/slowar.c:519-541) */
+        const int8_t* q = (const int8_t*)m->embed_i8.data;
+        const float* sc = (const float*)m->embed_scale.data;
+        for (int m0 = 0; m0 < nact; m0 += S2P_INT8_GEMV_MAX_M) {
+            const int mm = nact - m0 < S2P_INT8_GEMV_MAX_M ? nact - m0 : S2P_INT8_GEMV_MAX_M;
+            const char* hh = (const char*)m->shidden.data + (size_t)m0 * S2P_DIM * 2;
+            S2P_TRY(s2p_int8_gemv((char*)m->slogc.data + (size_t)m0 * 4096 * 2, hh,
+                                  q + (size_t)S2P_TOK_SEMANTIC_START * S2P_DIM, sc + S2P_TOK_SEMANTIC_START, mm, 4096,
+                                  S2P_DIM, st));
+            S2P_TRY(s2p_int8_gemv((char*)m->sloge.data + (size_t)m0 * 2, hh, q + (size_t)S2P_TOK_EOS * S2P_DIM,
+                                  sc + S2P_TOK_EOS, mm, 1, S2P_DIM, st));
+        }
+        S2P_CUDA_TRY(sample_rows(m->slogc.data, 4096, m->sloge.data, 1, d->samp, nact, d->tok, d->sem, d->ocodes,
+                                 d->eos, st));
+        return S2P_OK;
+    }
+    if (m->mode == S2P_GEMM_INT8 && m->embed_i8.data) {
+        for (int m0 = 0; m0 < nact; m0 += S2P_INT8_GEMV_MAX_M) {
+            const int mm = nact - m0 < S2P_INT8_GEMV_MAX_M ? nact - m0 : S2P_INT8_GEMV_MAX_M;
+            S2P_TRY(s2p_int8_gemv((char*)m->slogits.data + (size_t)m0 * S2P_TEXT_VOCAB * 2,
+                                  (const char*)m->shidden.data + (size_t)m0 * S2P_DIM * 2, m->embed_i8.data,
+                                  (const float*)m->embed_scale.data, mm, S2P_TEXT_VOCAB, S2P_DIM, st));
+        }
+    } else {
+        S2P_TRY(s2p_gemm_bf16(m->shidden.data, m->embed.data, m->slogits.data, nact, S2P_TEXT_VOCAB, S2P_DIM, st));
+    }
+    if (dump_ok && dump_dir() && nact == 1) {
+        static int dump_step = 0;
+        if (dump_step < 2) dump_bf16(dump_step == 0 ? "prefill_logits" : "step1_logits", m->slogits.data, S2P_TEXT_VOCAB, st);
+        dump_step++;
+    }
+    S2P_CUDA_TRY(sample_rows((const uint16_t*)m->slogits.data + S2P_TOK_SEMANTIC_START, S2P_TEXT_VOCAB,
+                             (const uint16_t*)m->slogits.data + S2P_TOK_EOS, S2P_TEXT_VOCAB, d->samp, nact, d->tok,
+                             d->sem, d->ocodes, d->eos, st));
+    return S2P_OK;
+}
+
+/* fast-AR frame, general sequence (src/fastar/fastar.cu:726-788) */
+static s2p_status fast_frame_general(s2p_model* m, const tick_dev* d, int nact, int dump_ok) {
+    cudaStream_t st = m->stream;
+    layer_ctx c;
+    memset(&c, 0, sizeof(c));
+    c.rows = nact; c.max_seq = S2P_FAST_SEQ; c.kv8 = 0; c.pos_row_step = 0; c.decode = 1; c.split_k = 0;
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->fx.data, m->shidden.data, (size_t)nact * S2P_DIM * 2, cudaMemcpyDeviceToDevice, st));
+    for (int cb = 0; cb < S2P_NUM_CODEBOOKS; cb++) {
+        c.pos0 = cb;
+        for (int l = 0; l < S2P_FAST_LAYERS; l++) {
+            fast_kv_ref(m, l, &c.kv);
+            S2P_TRY(layer_general(m, &m->fast[l], &c, BF(m->fx), BF(m->ft), BF(m->fqkv), BF(m->fq), BF(m->fattn),
+                                  BF(m->fproj), BF(m->fgu), BF(m->fhff)));
+        }
+        const int32_t* next_codes;
+        if (cb == 0) {
+            next_codes = d->sem; /* the prime pass produces no logits; step 1 is fed embeddings[sem] */
+        } else {
+            S2P_CUDA_TRY(rms_norm(m->fx.data, m->fast_norm.data, m->ft.data, nact, S2P_DIM, S2P_NORM_EPS, st));
+            S2P_TRY(lin_apply(m, &m->fast_out, m->ft.data, m->flogits.data, nact, 1));
+            if (dump_ok && dump_dir() && nact == 1) {
+                static int dump_frame = 0;
+                if (cb == 1) dump_frame++;
+                if (dump_frame == 1) {
+                    char nm[48];
+                    snprintf(nm, sizeof(nm), "fast_ar_step0_cb%d", cb);
+                    dump_bf16(nm, m->flogits.data, S2P_CB_SIZE, st);
+                }
+            }
+            int32_t* dst = m->fstage + (size_t)(cb - 1) * nact;
+            S2P_CUDA_TRY(argmax_rows(m->flogits.data, dst, nact, S2P_CB_SIZE, st));
+            next_codes = dst;
+        }
+        if (cb < S2P_NUM_CODEBOOKS - 1) S2P_CUDA_TRY(embed_codes(m->fast_emb.data, next_codes, m->fx.data, nact, st));
+    }
+    S2P_CUDA_TRY(pack_frame(m->fstage, nact, d->ocodes, st));
+    return S2P_OK;
+}
+
+/* general tick: bd decode rows (rows [0,bd) of the upload block), nact >= bd rows to sample */
+static s2p_status tick_general(s2p_model* m, s2p_session* const* act, int bd, int nact) {
+    cudaStream_t st = m->stream;
+    tick_dev d;
+    tick_views(m, &d);
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->d_up, m->h_up, m->up_bytes, cudaMemcpyHostToDevice, st));
+    if (bd > 0) {
+        S2P_TRY(tick_begin_rows(m, &d, bd));
+        layer_ctx c;
+        memset(&c, 0, sizeof(c));
+        c.rows = bd; c.kv.bases = d.kv_bases; c.kv.sbases = d.kvs_bases;
+        c.max_seq = m->ctx_len; c.kv8 = m->kv8; c.pos_arr = d.pos; c.split_k = 1; c.decode = 1;
+        for (int l = 0; l < m->n_slow; l++) {
+            slow_kv_offsets(m, l, &c.kv);
+            S2P_TRY(layer_general(m, &m->slow[l], &c, BF(m->sx), BF(m->snorm), BF(m->sqkv), BF(m->sq), BF(m->sattn),
+                                  BF(m->sproj), BF(m->sgu), BF(m->sffn)));
+        }
+        S2P_CUDA_TRY(rms_norm(m->sx.data, m->final_norm.data, m->shidden.data, bd, S2P_DIM, S2P_NORM_EPS, st));
+    }
+    for (int b = bd; b < nact; b++) /* freshly prefilled rows sample from their stashed hidden (eager only) */
+        S2P_CUDA_TRY(cudaMemcpyAsync(BF(m->shidden) + (size_t)b * S2P_DIM, act[b]->pending_hidden.data,
+                                     (size_t)S2P_DIM * 2, cudaMemcpyDeviceToDevice, st));
+    S2P_TRY(head_and_sample(m, &d, nact, 1));
+    S2P_TRY(fast_frame_general(m, &d, nact, 1));
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->h_out, m->d_out, m->out_bytes, cudaMemcpyDeviceToHost, st));
+    return S2P_OK;
+}
+
+/* batch-1 tick out of fused stages; `decode` = 0 when the row is freshly prefilled */
+static s2p_status tick_fused_b1(s2p_model* m, s2p_session* const* act, int decode) {
+    cudaStream_t st = m->stream;
+    tick_dev d;
+    tick_views(m, &d);
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->d_up, m->h_up, m->up_bytes, cudaMemcpyHostToDevice, st));
+    LinRef lr;
+    VecRef xr;
+    if (decode) {
+        S2P_TRY(tick_begin_rows(m, &d, 1));
+        AttnArgs aa;
+        memset(&aa, 0, sizeof(aa));
+        aa.out = BF(m->sattn);
+        aa.q_heads = S2P_SLOW_Q_HEADS; aa.kv_heads = S2P_SLOW_KV_HEADS; aa.max_seq = m->ctx_len; aa.kv8 = m->kv8;
+        aa.pos_arr = d.pos; aa.kv.bases = d.kv_bases; aa.kv.sbases = d.kvs_bases;
+        aa.part = (float*)m->attn_part.data; aa.counters = m->attn_ctr;
+        aa.n_split_slots = m->n_split_slots; aa.workers = attn_workers_for(1); aa.head_dim = S2P_HEAD_DIM;
+        memset(&xr, 0, sizeof(xr));
+        xr.base = BF(m->sx);
+        for (int l = 0; l < m->n_slow; l++) {
+            const s2p_layer* L = &m->slow[l];
+            s2p_lin_ref(&L->wqkv, &lr);
+            S2P_CUDA_TRY(stage_norm_gemv(&lr, &xr, L->attn_norm.data, S2P_NORM_EPS, BF(m->sqkv), st));
+            slow_kv_offsets(m, l, &aa.kv);
+            S2P_CUDA_TRY(stage_attn_decode_prep(&aa, BF(m->sqkv), L->q_norm.data, L->k_norm.data, S2P_NORM_EPS,
+                                                S2P_ROPE_BASE, 1, st));
+            s2p_lin_ref(&L->wo, &lr);
+            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->sattn), &xr, BF(m->sx), st));
+            s2p_lin_ref(&L->gate_up, &lr);
+            S2P_CUDA_TRY(stage_norm_swiglu(&lr, &xr, L->ffn_norm.data, S2P_NORM_EPS, BF(m->sffn), st));
+            s2p_lin_ref(&L->w2, &lr);
+            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->sffn), &xr, BF(m->sx), st));
+        }
+        S2P_CUDA_TRY(rms_norm(m->sx.data, m->final_norm.data, m->shidden.data, 1, S2P_DIM, S2P_NORM_EPS, st));
+    } else {
+        S2P_CUDA_TRY(cudaMemcpyAsync(m->shidden.data, act[0]->pending_hidden.data, (size_t)S2P_DIM * 2,
+                                     cudaMemcpyDeviceToDevice, st));
+        S2P_CUDA_TRY(cudaMemsetAsync(m->fkeys, 0, 9 * sizeof(unsigned long long), st));
+    }
+    S2P_TRY(head_and_sample(m, &d, 1, 0));
+
+    /* fast-AR: the input of a pass is a row selected on the device — the slow hidden
+     * (prime), embeddings[sem] (step 1) or embeddings[arg-max of the previous step] */
+    QkvPostArgs qa;
+    memset(&qa, 0, sizeof(qa));
+    qa.qkv = BF(m->fqkv); qa.q = BF(m->fq);
+    qa.eps = S2P_NORM_EPS; qa.rope_base = S2P_ROPE_BASE;
+    qa.q_heads = S2P_SLOW_Q_HEADS; qa.kv_heads = S2P_SLOW_KV_HEADS; qa.max_seq = S2P_FAST_SEQ;
+    AttnArgs fa;
+    memset(&fa, 0, sizeof(fa));
+    fa.q = BF(m->fq); fa.out = BF(m->fattn);
+    fa.q_heads = S2P_SLOW_Q_HEADS; fa.kv_heads = S2P_SLOW_KV_HEADS; fa.max_seq = S2P_FAST_SEQ;
+    fa.head_dim = S2P_HEAD_DIM;
+    for (int cb = 0; cb < S2P_NUM_CODEBOOKS; cb++) {
+        VecRef in; /* input of layer 0 of this pass */
+        memset(&in, 0, sizeof(in));
+        if (cb == 0) in.base = BF(m->shidden);
+        else {
+            in.base = BF(m->fast_emb);
+            if (cb == 1) in.index = d.sem;
+            else in.key = m->fkeys + (cb - 2);
+        }
+        VecRef fx;
+        memset(&fx, 0, sizeof(fx));
+        fx.base = BF(m->fx);
+        qa.pos0 = cb; fa.pos0 = cb;
+        for (int l = 0; l < S2P_FAST_LAYERS; l++) {
+            const s2p_layer* L = &m->fast[l];
+            const VecRef* src = l == 0 ? &in : &fx;
+            s2p_lin_ref(&L->wqkv, &lr);
+            S2P_CUDA_TRY(stage_norm_gemv(&lr, src, L->attn_norm.data, S2P_NORM_EPS, BF(m->fqkv), st));
+            fast_kv_ref(m, l, &qa.kv);
+            fa.kv = qa.kv;
+            S2P_CUDA_TRY(qkv_post(&qa, 1, st));
+            S2P_CUDA_TRY(attn_single(&fa, 1, st));
+            s2p_lin_ref(&L->wo, &lr);
+            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->fattn), src, BF(m->fx), st));
+            s2p_lin_ref(&L->gate_up, &lr);
+            S2P_CUDA_TRY(stage_norm_swiglu(&lr, &fx, L->ffn_norm.data, S2P_NORM_EPS, BF(m->fhff), st));
+            s2p_lin_ref(&L->w2, &lr);
+            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->fhff), &fx, BF(m->fx), st));
+        }
+        if (cb > 0) {
+            s2p_lin_ref(&m->fast_out, &lr);
+            S2P_CUDA_TRY(stage_norm_argmax(&lr, BF(m->fx), m->fast_norm.data, S2P_NORM_EPS, BF(m->flogits),
+                                           m->fkeys + (cb - 1), st));
+        }
+    }
+    S2P_CUDA_TRY(tick_finish_keys(m->fkeys, 1, d.ocodes, st));
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->h_out, m->d_out, m->out_bytes, cudaMemcpyDeviceToHost, st));
+    return S2P_OK;
+}
+
+s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, int32_t* out_codes, int* eos) {
+    if (!m || !sess || !out_codes || !eos || n < 0 || n > m->max_sessions) return S2P_ERR_INVALID;
+    for (int i = 0; i < n; i++) {
+        if (!sess[i] || sess[i]->m != m) return S2P_ERR_INVALID;
+        if (sess[i]->state == SESS_NEW) return S2P_ERR_STATE;
+    }
+    cudaStream_t st = m->stream;
+    memset(out_codes, 0, (size_t)n * S2P_NUM_CODEBOOKS * sizeof(int32_t));
+
+    /* decode rows first (their final norm lands in shidden[0..bd)), then freshly prefilled ones */
+    s2p_session* act[S2P_MAX_BATCH];
+    int act_ix[S2P_MAX_BATCH];
+    int nact = 0;
+    for (int i = 0; i < n; i++) {
+        s2p_session* s = sess[i];
+        eos[i] = s->state == SESS_FINISHED;
+        if (s->state == SESS_DECODING) {
+            if (s->kv_len >= m->ctx_len) { /* context exhausted: forced stop */
+                s->state = SESS_FINISHED;
+                eos[i] = 1;
+                continue;
+            }
+            act[nact] = s;
+            act_ix[nact++] = i;
+        }
+    }
+    const int bd = nact;
+    for (int i = 0; i < n; i++)
+        if (sess[i]->state == SESS_PREFILLED) {
+            act[nact] = sess[i];
+            act_ix[nact++] = i;
+        }
+    if (nact == 0) return S2P_OK;
+
+    /* host staging */
+    {
+        char* h = (char*)m->h_up;
+        void** kvb = (void**)(h + m->off_kvb);
+        void** kvsb = (void**)(h + m->off_kvsb);
+        void** samp = (void**)(h + m->off_samp);
+        int64_t* ids = (int64_t*)(h + m->off_ids);
+        int32_t* codes = (int32_t*)(h + m->off_codes);
+        int32_t* pos = (int32_t*)(h + m->off_pos);
+        uint8_t* mask = (uint8_t*)(h + m->off_mask);
+        for (int b = 0; b < nact; b++) {
+            s2p_session* s = act[b];
+            samp[b] = s->dsamp;
+            kvb[b] = s->kv.data;
+            kvsb[b] = s->kvs.data;
+            if (b < bd) {
+                ids[b] = s->prev_token;
+                pos[b] = s->kv_len;
+                mask[b] = (uint8_t)is_semantic(s->prev_token);
+                memcpy(codes + (size_t)b * S2P_NUM_CODEBOOKS, s->prev_codes, sizeof(s->prev_codes));
+            }
+        }
+    }
+
+    /* the library GEMM of the BF16 mode is kept out of stream capture */
+    const int graphs = !s2p_env_is_one("S2P_NO_GRAPHS") && dump_dir() == NULL && m->mode == S2P_GEMM_INT8;
+    const int fused = m->fused_b1 && nact == 1 && !m->head_full;
+    const int steady = bd == nact && graphs; /* every row decoding: the launch sequence is frame-invariant */
+    s2p_status rc = S2P_OK;
+    if (steady) {
+        if (!m->gready[bd]) {
+            S2P_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            rc = fused ? tick_fused_b1(m, act, 1) : tick_general(m, act, bd, nact);
+            cudaGraph_t g = NULL;
+            const cudaError_t ce = cudaStreamEndCapture(st, &g);
+            if (rc != S2P_OK) {
+                if (g) cudaGraphDestroy(g);
+                return rc;
+            }
+            if (ce != cudaSuccess) {
+                fprintf(stderr, "[s2pro] graph capture failed: %s\n", cudaGetErrorString(ce));
+                return S2P_ERR_CUDA;
+            }
+            const cudaError_t ci = cudaGraphInstantiate(&m->gexec[bd], g, 0);
+            cudaGraphDestroy(g);
+            if (ci != cudaSuccess) {
+                fprintf(stderr, "[s2pro] graph instantiate failed: %s\n", cudaGetErrorString(ci));
+                return S2P_ERR_CUDA;
+            }
+            m->gready[bd] = 1;
+        }
+        S2P_CUDA_TRY(cudaGraphLaunch(m->gexec[bd], st));
+    } else {
+        rc = fused ? tick_fused_b1(m, act, bd == 1) : tick_general(m, act, bd, nact);
+        if (rc != S2P_OK) return rc;
+    }
+    S2P_CUDA_TRY(cudaStreamSynchronize(st));
+    for (int b = 0; b < bd; b++) act[b]->kv_len++;
+    m->frames_decoded += (uint64_t)nact;
+
+    const int64_t* toks = (const int64_t*)m->h_out;
+    const int32_t* codes = (const int32_t*)((char*)m->h_out + m->off_ocodes);
+    const uint8_t* eflag = (const uint8_t*)((char*)m->h_out + m->off_eos);
+    for (int b = 0; b < nact; b++) {
+        s2p_session* s = act[b];
+        const int i = act_ix[b];
+        if (eflag[b]) { /* the EOS frame carries no codes */
+            s->state = SESS_FINISHED;
+            eos[i] = 1;
+            continue;
+        }
+        const int32_t* frame = codes + (size_t)b * S2P_NUM_CODEBOOKS;
+        memcpy(out_codes + (size_t)i * S2P_NUM_CODEBOOKS, frame, S2P_NUM_CODEBOOKS * sizeof(int32_t));
+        s->prev_token = toks[b];
+        memcpy(s->prev_codes, frame, sizeof(s->prev_codes));
+        s->state = SESS_DECODING;
+        eos[i] = 0;
+    }
+    return S2P_OK;
+}
+
+s2p_status s2p_session_next_frame(s2p_session* s, int32_t out_codes[S2P_NUM_CODEBOOKS], int* is_eos) {
+    if (!s || !out_codes || !is_eos) return S2P_ERR_INVALID;
+    return s2p_model_batch_next_frame(s->m, &s, 1, out_codes, is_eos);
+}
