@@ -1,0 +1,397 @@
+#!/usr/bin/env python
+"""Benchmark of the decode tick (slow-AR backbone + fast-AR loop + sampler).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+    torchrun ... bench.py --gpus N ...          (one rank per GPU)
+
+A step is one frame of one lockstep tick: `--batch` sessions (default 1) advance
+one frame through the public C-ABI call s2p_model_batch_next_frame, i.e. host
+staging, the pinned upload, the captured graph, the result download and the
+stream sync — that is the end-to-end number (`e2e`).  `value` is the device time
+of the same tick (CUDA events on the model's stream around the graph launch).
+With N GPUs every rank runs an independent replica on its own sessions (the path
+shards by session, there is no data-path collective): weak scaling.
+
+The workload is BASELINE.json's batch-1 all-INT4 configuration: 36 + 4 layers,
+seeded random-init checkpoint (the real one is gated), 512-token uniform random
+prompt, temperature 0.8 / top-p 0.8 with a fixed seed.
+"""
+import argparse
+import ctypes as C
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# weights one batch-1 frame touches (reference code truth: fast-AR stack 10x, fast head 9x, tied head 4097 rows)
+WEIGHTS_PER_LAYER = 6144 * 2560 + 2560 * 4096 + 19456 * 2560 + 2560 * 9728
+
+
+def algorithmic_bytes_per_frame(mode, n_slow=36):
+    """Quantised weight bytes + scales streamed per frame (no KV, no activations)."""
+    rows_per_layer = 6144 + 2560 + 19456 + 2560
+    if mode == "int4":
+        layer = WEIGHTS_PER_LAYER * 0.5625
+        fast_head = 4096 * 2560 * 0.5625
+    else:
+        layer = WEIGHTS_PER_LAYER + 4 * rows_per_layer
+        fast_head = 4096 * 2560 + 4 * 4096
+    return n_slow * layer + 10 * 4 * layer + 9 * fast_head + 4097 * (2560 + 4)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    def __init__(self, gpu_index):
+        super().__init__(daemon=True)
+        self.rows, self.stop_flag, self.idx = [], False, gpu_index
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.idx), f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.2)
+
+    def summary(self):
+        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows for i in range(4) if len(r) > 2 + i and r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def set_mode_env(mode):
+    os.environ["S2P_INT8"] = "1"
+    os.environ["S2P_QCACHE"] = "0"
+    if mode == "int4":
+        os.environ["S2P_INT4"] = "1"
+        os.environ["S2P_INT4_ALL"] = "1"
+    else:
+        os.environ.pop("S2P_INT4", None)
+        os.environ.pop("S2P_INT4_ALL", None)
+
+
+def checkpoint_dir(n_slow):
+    base = os.environ.get("S2P_BENCH_CKPT_DIR") or ("/dev/shm" if os.path.isdir("/dev/shm") else "/tmp")
+    return os.path.join(base, f"s2p_synth_l{n_slow}")
+
+
+class Engine:
+    """Sessions of one model behind the C ABI (this library or the rebuilt reference)."""
+
+    def __init__(self, lib, capi, ckpt, ctx_len, max_sessions):
+        self.L, self.capi = lib, capi
+        opts = capi.ModelOpts(capi.GEMM_INT8, ctx_len, max_sessions)
+        self.m = C.c_void_p()
+        capi.check(lib.s2p_model_load(ckpt.encode(), C.byref(opts), C.byref(self.m)), "s2p_model_load")
+        self.sessions = []
+
+    def open_sessions(self, prompts, temperature, top_p, seed):
+        for i, ids in enumerate(prompts):
+            cfg = self.L.s2p_sampling_defaults()
+            cfg.temperature, cfg.top_p, cfg.seed = temperature, top_p, seed + i
+            s = C.c_void_p()
+            self.capi.check(self.L.s2p_session_create(self.m, C.byref(cfg), C.byref(s)), "s2p_session_create")
+            for lo in range(0, len(ids), 2048):  # prefill scratch holds 2048 rows per pass
+                chunk = ids[lo:lo + 2048]
+                self.capi.check(self.L.s2p_session_prefill(s, chunk.ctypes.data_as(C.c_void_p), None, len(chunk), None, 0),
+                                "s2p_session_prefill")
+            self.sessions.append(s)
+        n = len(self.sessions)
+        self.arr = (C.c_void_p * n)(*[s.value for s in self.sessions])
+        self.codes = (C.c_int32 * (10 * n))()
+        self.eos = (C.c_int * n)()
+
+    def tick(self):
+        self.capi.check(self.L.s2p_model_batch_next_frame(self.m, self.arr, len(self.sessions), self.codes, self.eos),
+                        "s2p_model_batch_next_frame")
+        return any(self.eos)
+
+    def close(self):
+        for s in self.sessions:
+            self.L.s2p_session_destroy(s)
+        self.sessions = []
+        self.L.s2p_model_free(self.m)
+
+
+def cpu_baseline(mode, seconds=12.0):
+    """CPU port of the hot loop (oracle/, exact reference order) on a bounded sample:
+    the four GEMVs of one backbone-shaped layer at batch 1, scaled to one frame."""
+    import numpy as np
+    from oracle import oracle_api
+    lib = oracle_api.load()
+    rng = np.random.default_rng(0)
+    int4 = mode == "int4"
+    wbytes = 19456 * 2560 // (2 if int4 else 1)
+    w = rng.integers(0, 256, size=wbytes, dtype=np.uint8)
+    sc16 = np.full(19456 * (9728 // 32), 0x2C00, dtype=np.uint16)
+    sc32 = np.full(19456, 1e-3, dtype=np.float32)
+    x = oracle_api.f32_to_bf16(rng.standard_normal(9728).astype(np.float32))
+    y = np.zeros(19456, dtype=np.uint16)
+    lib.s2po_layer_gemv_sample(oracle_api.ptr(w), oracle_api.ptr(sc16), oracle_api.ptr(sc32), oracle_api.ptr(x), oracle_api.ptr(y), int(int4), 1)
+    reps, t0 = 0, time.time()
+    while time.time() - t0 < seconds:
+        lib.s2po_layer_gemv_sample(oracle_api.ptr(w), oracle_api.ptr(sc16), oracle_api.ptr(sc32), oracle_api.ptr(x), oracle_api.ptr(y), int(int4), 1)
+        reps += 1
+    per_layer_ms = (time.time() - t0) / reps * 1e3
+    layers_per_frame = 36 + 40 + (9 * 4096 * 2560 + 4097 * 2560) / WEIGHTS_PER_LAYER
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return {"value": per_layer_ms * layers_per_frame, "unit": "ms/frame", "cores": cores, "kind": "port",
+            "sample": f"{reps} x the 4 GEMVs of one backbone-shaped layer ({'INT4 g32' if int4 else 'INT8'}, batch 1), "
+                      f"OpenMP over rows, scaled by {layers_per_frame:.2f} layer-equivalents per frame; attention, norms and sampler (<1% of the work) left out"}
+
+
+def isolated_gemv_roofline(lib, torch, mode, peak_gbs):
+    """Each GEMV shape of the tick timed alone with CUDA events, weights rotated through
+    > L2-sized storage so every launch streams from HBM."""
+    out = []
+    G = 32
+    for name, N, K in (("wqkv", 6144, 2560), ("wo", 2560, 4096), ("gate_up", 19456, 2560), ("w2", 2560, 9728)):
+        per = N * K // 2 if mode == "int4" else N * K
+        copies = max(3, int(400e6 // per) + 1)
+        w = torch.randint(0, 255, (copies, per), dtype=torch.uint8, device="cuda")
+        if mode == "int4":
+            sc = torch.full((copies, N * (K // G)), 0.001, dtype=torch.float16, device="cuda")
+        else:
+            sc = torch.full((copies, N), 0.001, dtype=torch.float32, device="cuda")
+        x = torch.randn(1, K, device="cuda").to(torch.bfloat16)
+        y = torch.empty(1, N, dtype=torch.bfloat16, device="cuda")
+        st = torch.cuda.Stream()
+        reps = 3 * copies
+
+        def launch(i):
+            wp, sp = C.c_void_p(w[i % copies].data_ptr()), C.c_void_p(sc[i % copies].data_ptr())
+            if mode == "int4":
+                rc = lib.s2p_int4p_gemv(C.c_void_p(y.data_ptr()), C.c_void_p(x.data_ptr()), wp, sp, 1, N, K, G, C.c_void_p(st.cuda_stream))
+            else:
+                rc = lib.s2p_int8_gemv(C.c_void_p(y.data_ptr()), C.c_void_p(x.data_ptr()), wp, sp, 1, N, K, C.c_void_p(st.cuda_stream))
+            assert rc == 0, rc
+        torch.cuda.synchronize()
+        for i in range(copies):  # warm-up (also sets the kernels' shared-memory attribute before capture)
+            launch(i)
+        torch.cuda.synchronize()
+        # capture `reps` launches into one graph so that launch overhead does not gate the timing
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(reps):
+                launch(i)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g.replay(); torch.cuda.synchronize()
+        e0.record(); g.replay(); e1.record(); torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        byts = per + (N * (K // G) * 2 if mode == "int4" else N * 4)
+        out.append({"kernel": f"k_gemv_stage[{name} {N}x{K} {mode}]", "us": round(us, 2), "bytes": byts,
+                    "achieved_gbs": round(byts / us / 1e3, 1), "frac": round(byts / us / 1e3 / peak_gbs, 3)})
+        del w, sc
+    return out
+
+
+def run_ours(args, rank, world):
+    import numpy as np
+    import torch
+    capi = importlib.import_module("s2pro-native_b200.capi")
+    synth = importlib.import_module("s2pro-native_b200.synth")
+    set_mode_env(args.mode)
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    os.environ["S2P_DEVICE"] = str(local)
+    ckpt = checkpoint_dir(args.layers)
+    if local == 0:
+        synth.write_checkpoint(ckpt, n_slow=args.layers, seed=1, generator="auto")
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    lib = capi.load_library()
+    ctx_len = max(4096, ((args.prompt + args.steps + args.warmup + 64 + 63) // 64) * 64)
+    eng, seed_used = None, args.seed
+    for attempt in range(8):  # a sampled EOS would end a session early: move to the next seed
+        eng = Engine(lib, capi, ckpt, ctx_len, max(args.batch, 1))
+        rng = np.random.default_rng(1000 * rank + attempt)
+        lens = [args.prompt] * args.batch if args.batch == 1 else list(rng.integers(256, 2049, size=args.batch))
+        prompts = [synth.random_prompt(int(n), 100 * rank + i) for i, n in enumerate(lens)]
+        eng.open_sessions(prompts, 0.8, 0.8, seed_used + 7919 * rank)
+        hit = eng.tick()  # first frame samples from the prefill state (not graph-captured)
+        for _ in range(args.warmup):
+            hit = hit or eng.tick()
+        if not hit:
+            break
+        eng.close()
+        seed_used += 1
+    stats = capi.Stats()
+    sampler = ClockSampler(local)
+    sampler.start()
+    dev_ms = []
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    eos_in_timed = False
+    for _ in range(args.steps):
+        eos_in_timed = eng.tick() or eos_in_timed
+        lib.s2p_b200_model_stats(eng.m, C.byref(stats))
+        dev_ms.append(stats.last_tick_device_ms)
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    lib.s2p_b200_model_stats(eng.m, C.byref(stats))
+    step_wall = wall_ms / args.steps
+    step_dev = sum(dev_ms) / len(dev_ms)
+    if world > 1:
+        t = torch.tensor([step_wall, step_dev], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_wall, step_dev = float(t[0]), float(t[1])
+    if rank != 0:
+        eng.close()
+        return None
+    peaks, peak_kind = measured_peaks()
+    peak = float(peaks["hbm_gbs"])
+    kv_tokens = sum(int(n) for n in lens) + args.batch * (1 + args.warmup + args.steps // 2)
+    algo = algorithmic_bytes_per_frame(args.mode, args.layers)
+    traffic_model = algo + stats.kv_bytes_per_token * kv_tokens
+    achieved = algo / (step_dev * 1e-3) / 1e9
+    line = {
+        "metric": "decode ms/frame (B=%d)" % args.batch, "value": round(step_dev, 4), "unit": "ms/frame",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_wall, 4),
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": args.mode,
+        "data": "synthetic (seeded random-init checkpoint, uniform random prompt)",
+        "config": {"workload": f"dual-AR decode, all-{args.mode.upper()} weights + INT8 KV, {args.layers}+4 layers, batch {args.batch} per GPU, "
+                               f"{args.prompt}-token prompt, T=0.8 top-p=0.8 seed {seed_used}",
+                   "replicas": world, "ctx_len": ctx_len, "l2": "weights per frame (4.4-7.8 GB) exceed the 126 MB L2: every frame streams from HBM",
+                   "eos_in_timed_region": bool(eos_in_timed)},
+        "frames_per_s": round(world * args.batch * 1e3 / step_wall, 1),
+        "e2e": {"value": round(step_wall, 4), "unit": "ms/frame", "h2d_bytes_per_step": int(stats.upload_bytes),
+                "d2h_bytes_per_step": int(stats.download_bytes)},
+        "gpu_launches": int(stats.last_tick_kernels) * args.steps,
+        "tick": {"kernels": int(stats.last_tick_kernels), "fused": int(stats.last_tick_fused), "graph": int(stats.last_tick_graph),
+                 "device_ms_p50": round(statistics.median(dev_ms), 4), "device_ms_p95": round(sorted(dev_ms)[int(0.95 * (len(dev_ms) - 1))], 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "traffic": None, "peak_source": peak_kind,
+                     "note": "whole tick: algorithmic weight bytes per frame / device time per frame; per-kernel figures under roofline_kernels",
+                     "algorithmic_bytes_per_frame": int(algo), "modelled_bytes_with_kv": int(traffic_model)},
+        "clocks": sampler.summary(),
+    }
+    eng.close()
+    if not args.no_kernel_roofline:
+        line["roofline_kernels"] = isolated_gemv_roofline(lib, torch, args.mode, peak)
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args.mode)
+    return line
+
+
+def run_reference(args, rank, world):
+    """The reference's own implementation of the path.  It has no CPU decode path; its
+    CUDA path rebuilt unchanged for sm_100a (oracle/_ref) is timed through the same public
+    API calls.  Without that build the CPU port of the hot loop stands in."""
+    if rank != 0:
+        return None
+    ref_path = os.path.join(ROOT, "oracle", "_ref", "libs2pref.so" if args.layers == 36 else "libs2pref_l2.so")
+    base = {"impl": "reference", "metric": "decode ms/frame (B=1)", "unit": "ms/frame", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": args.mode,
+            "data": "synthetic (seeded random-init checkpoint, uniform random prompt)"}
+    try:
+        import torch
+        have_gpu = torch.cuda.is_available()
+    except Exception:
+        have_gpu = False
+    if os.path.exists(ref_path) and have_gpu and args.batch <= 16:
+        import numpy as np
+        capi = importlib.import_module("s2pro-native_b200.capi")
+        synth = importlib.import_module("s2pro-native_b200.synth")
+        set_mode_env(args.mode)
+        ckpt = checkpoint_dir(args.layers)
+        synth.write_checkpoint(ckpt, n_slow=args.layers, seed=1, generator="auto")
+        ref = C.CDLL(ref_path)
+        capi.bind(ref, capi.PROTOTYPES, strict=False)
+        seed_used = args.seed
+        for attempt in range(8):
+            eng = Engine(ref, capi, ckpt, 4096, max(args.batch, 1))
+            rng = np.random.default_rng(attempt)
+            lens = [args.prompt] * args.batch if args.batch == 1 else list(rng.integers(256, 2049, size=args.batch))
+            eng.open_sessions([synth.random_prompt(int(n), i) for i, n in enumerate(lens)], 0.8, 0.8, seed_used)
+            hit = eng.tick()
+            for _ in range(args.warmup):
+                hit = hit or eng.tick()
+            if not hit:
+                break
+            eng.close()
+            seed_used += 1
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            eng.tick()
+        torch.cuda.synchronize()
+        step = (time.perf_counter() - t0) * 1e3 / args.steps
+        eng.close()
+        base.update({"value": round(step, 4), "ms_per_step": round(step, 4),
+                     "config": {"workload": f"dual-AR decode, all-{args.mode.upper()} weights + INT8 KV, {args.layers}+4 layers, batch {args.batch}, "
+                                            f"{args.prompt}-token prompt, T=0.8 top-p=0.8 seed {seed_used}",
+                                "arm": "reference CUDA path rebuilt unchanged for sm_100a (oracle/_ref), same GPU, same API calls"},
+                     "cpu_baseline": {"value": round(step, 4), "unit": "ms/frame", "cores": 1, "kind": "reference",
+                                      "sample": "the reference has no CPU decode path; this is its CUDA path on the GPU, one host thread issuing"},
+                     "e2e": {"value": round(step, 4), "unit": "ms/frame", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        return base
+    cb = cpu_baseline(args.mode)
+    base.update({"value": round(cb["value"], 2), "ms_per_step": round(cb["value"], 2),
+                 "config": {"workload": f"dual-AR decode, all-{args.mode.upper()}, batch 1", "arm": "CPU port of the hot loop (oracle/): the reference library is not built here"},
+                 "cpu_baseline": cb,
+                 "e2e": {"value": round(cb["value"], 2), "unit": "ms/frame", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    return base
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="int4", choices=["int4", "int8"])
+    ap.add_argument("--batch", type=int, default=1, help="lockstep sessions per GPU")
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--seed", type=int, default=42)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernel-roofline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and args.impl == "ours":
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dist.init_process_group("nccl")
+    line = (run_ours if args.impl == "ours" else run_reference)(args, rank, world)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1 and args.impl == "ours":
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

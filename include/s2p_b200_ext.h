@@ -15,6 +15,25 @@ extern "C" {
 /* Library identification: "s2pro-b200 <version> sm_100a". */
 const char* s2p_b200_version(void);
 
+/* Measurement hooks (no counterpart in the reference). */
+typedef struct {
+    uint64_t frames_decoded;        /* session-frames produced since load */
+    int n_slow_layers;              /* backbone depth found in the checkpoint */
+    int last_tick_rows;             /* rows of the most recent tick */
+    int last_tick_fused;            /* 1 = batch-1 fused stages, 0 = general sequence */
+    int last_tick_graph;            /* 1 = replayed from a captured CUDA graph */
+    int last_tick_kernels;          /* kernel launches of the most recent tick */
+    float last_tick_device_ms;      /* device time of the most recent tick (events on the model stream) */
+    size_t upload_bytes;            /* host->device bytes per tick */
+    size_t download_bytes;          /* device->host bytes per tick */
+    double weight_bytes_per_frame;  /* quantised weight + scale bytes one batch-1 frame streams */
+    double kv_bytes_per_token;      /* KV bytes one session reads per cached token per frame */
+} s2p_b200_stats;
+
+s2p_status s2p_b200_model_stats(const s2p_model* m, s2p_b200_stats* out);
+/* The stream every tick of this model is issued on (for external event timing). */
+cudaStream_t s2p_b200_model_stream(s2p_model* m);
+
 #pragma GCC visibility pop
 #ifdef __cplusplus
 }

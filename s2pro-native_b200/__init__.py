@@ -8,5 +8,5 @@ loudly when the library has not been built.
 """
 from .capi import (  # noqa: F401
     LIB_PATH, S2PError, check, lib, load_library, Linear, Tensor, ModelOpts, SamplingCfg, VqPart,
-    GEMM_BF16, GEMM_INT8, STATUS_NAMES,
+    GEMM_BF16, GEMM_INT8, STATUS_NAMES, Stats,
 )

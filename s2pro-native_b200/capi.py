@@ -114,8 +114,17 @@ PROTOTYPES = {
 }
 
 # additive entry points of this library only (include/s2p_b200_ext.h)
+class Stats(C.Structure):
+    _fields_ = [("frames_decoded", C.c_uint64), ("n_slow_layers", C.c_int), ("last_tick_rows", C.c_int),
+                ("last_tick_fused", C.c_int), ("last_tick_graph", C.c_int), ("last_tick_kernels", C.c_int),
+                ("last_tick_device_ms", C.c_float), ("upload_bytes", C.c_size_t), ("download_bytes", C.c_size_t),
+                ("weight_bytes_per_frame", C.c_double), ("kv_bytes_per_token", C.c_double)]
+
+
 EXT_PROTOTYPES = {
     "s2p_b200_version": (C.c_char_p, []),
+    "s2p_b200_model_stats": (_I, [_P, C.POINTER(Stats)]),
+    "s2p_b200_model_stream": (C.c_void_p, [_P]),
 }
 
 

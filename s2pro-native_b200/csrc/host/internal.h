@@ -70,6 +70,12 @@ struct s2p_model {
     cudaGraphExec_t gexec[S2P_MAX_BATCH + 1];
     unsigned char gready[S2P_MAX_BATCH + 1];
     uint64_t frames_decoded;
+    /* measurement */
+    cudaEvent_t ev0, ev1;
+    int tick_kernels;                 /* counted while a tick is enqueued or captured */
+    int graph_kernels[S2P_MAX_BATCH + 1];
+    int last_rows, last_fused, last_graph, last_kernels;
+    float last_device_ms;
 };
 
 struct s2p_session {
@@ -90,5 +96,8 @@ size_t s2p_kv_vec_bytes(const s2p_model* m);
 size_t s2p_kv_plane_bytes(const s2p_model* m);  /* one [ctx] plane of payload */
 size_t s2p_kvs_plane_bytes(const s2p_model* m); /* one [ctx] plane of scales */
 void s2p_lin_ref(const s2p_linear* lin, LinRef* out);
+
+/* S2P_CUDA_TRY for a kernel launch of the tick, counted for the statistics */
+#define S2P_LAUNCH(m, expr) do { (m)->tick_kernels++; S2P_CUDA_TRY(expr); } while (0)
 
 #endif

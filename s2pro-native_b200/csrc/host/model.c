@@ -291,6 +291,7 @@ s2p_status s2p_model_load(const char* model_dir, const s2p_model_opts* opts, s2p
         if (rc != S2P_OK) goto fail;
     }
     if ((rc = alloc_workspace(m)) != S2P_OK) goto fail;
+    if (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess) { rc = S2P_ERR_CUDA; goto fail; }
     if (cudaStreamSynchronize(m->stream) != cudaSuccess) { rc = S2P_ERR_CUDA; goto fail; }
     s2p_st_close(st);
     st = NULL;
@@ -338,6 +339,45 @@ void s2p_model_free(s2p_model* m) {
     if (m->h_up) cudaFreeHost(m->h_up);
     if (m->d_out) cudaFree(m->d_out);
     if (m->h_out) cudaFreeHost(m->h_out);
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
     if (m->stream) cudaStreamDestroy(m->stream);
     free(m);
 }
+
+/* ---- measurement hooks (include/s2p_b200_ext.h) ------------------------------ */
+static double linear_bytes(const s2p_linear* lin) {
+    return (double)lin->w_int8.bytes + (double)lin->w_pack.bytes + (double)lin->w_iscale.bytes +
+           (lin->int8_ready ? 0.0 : (double)lin->w_bf16.bytes);
+}
+static double layer_bytes(const s2p_layer* L) {
+    return linear_bytes(&L->wqkv) + linear_bytes(&L->wo) + linear_bytes(&L->gate_up) + linear_bytes(&L->w2);
+}
+
+s2p_status s2p_b200_model_stats(const s2p_model* m, s2p_b200_stats* out) {
+    if (!m || !out) return S2P_ERR_INVALID;
+    memset(out, 0, sizeof(*out));
+    out->frames_decoded = m->frames_decoded;
+    out->n_slow_layers = m->n_slow;
+    out->last_tick_rows = m->last_rows;
+    out->last_tick_fused = m->last_fused;
+    out->last_tick_graph = m->last_graph;
+    out->last_tick_kernels = m->last_kernels;
+    out->last_tick_device_ms = m->last_device_ms;
+    out->upload_bytes = m->up_bytes;
+    out->download_bytes = m->out_bytes;
+    /* one frame reads: every backbone linear once, every fast-AR linear ten times (prime + 9 steps),
+     * the fast head nine times, and the 4096 + 1 sampled rows of the tied head */
+    double w = 0.0;
+    for (int l = 0; l < m->n_slow; l++) w += layer_bytes(&m->slow[l]);
+    for (int l = 0; l < S2P_FAST_LAYERS; l++) w += 10.0 * layer_bytes(&m->fast[l]);
+    w += 9.0 * linear_bytes(&m->fast_out);
+    if (m->mode == S2P_GEMM_INT8 && !m->head_full) w += 4097.0 * (S2P_DIM + 4);
+    else w += (double)S2P_TEXT_VOCAB * S2P_DIM * (m->mode == S2P_GEMM_INT8 ? 1.0 : 2.0);
+    out->weight_bytes_per_frame = w;
+    out->kv_bytes_per_token = (double)m->n_slow * S2P_KV_PLANES_PER_LAYER *
+                              (m->kv8 ? S2P_HEAD_DIM + (S2P_HEAD_DIM / 32) * 2 : S2P_HEAD_DIM * 2);
+    return S2P_OK;
+}
+
+cudaStream_t s2p_b200_model_stream(s2p_model* m) { return m ? m->stream : NULL; }

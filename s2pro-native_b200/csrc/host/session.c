@@ -137,6 +137,7 @@ typedef struct {
 } layer_ctx;
 
 static s2p_status lin_apply(s2p_model* m, const s2p_linear* lin, const void* x, void* y, int rows, int decode) {
+    m->tick_kernels += decode ? (rows + S2P_INT8_GEMV_MAX_M - 1) / S2P_INT8_GEMV_MAX_M : 2;
     if (decode && m->mode == S2P_GEMM_INT8 && lin->int8_ready) return s2p_linear_gemv_rows(lin, x, y, rows, m->stream);
     return s2p_linear_forward(lin, x, y, rows, m->mode, m->stream);
 }
@@ -152,7 +153,7 @@ static s2p_status layer_general(s2p_model* m, const s2p_layer* L, const layer_ct
                                 s2p_dev_bf16* proj, s2p_dev_bf16* gu, s2p_dev_bf16* hff) {
     cudaStream_t st = m->stream;
     const int rows = c->rows;
-    S2P_CUDA_TRY(rms_norm(x, L->attn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
+    S2P_LAUNCH(m, rms_norm(x, L->attn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
     S2P_TRY(lin_apply(m, &L->wqkv, norm, qkv, rows, c->decode));
     QkvPostArgs qa;
     memset(&qa, 0, sizeof(qa));
@@ -161,7 +162,7 @@ static s2p_status layer_general(s2p_model* m, const s2p_layer* L, const layer_ct
     qa.eps = S2P_NORM_EPS; qa.rope_base = S2P_ROPE_BASE;
     qa.q_heads = S2P_SLOW_Q_HEADS; qa.kv_heads = S2P_SLOW_KV_HEADS; qa.max_seq = c->max_seq; qa.kv8 = c->kv8;
     qa.pos0 = c->pos0; qa.pos_row_step = c->pos_row_step; qa.pos_arr = c->pos_arr; qa.kv = c->kv;
-    S2P_CUDA_TRY(qkv_post(&qa, rows, st));
+    S2P_LAUNCH(m, qkv_post(&qa, rows, st));
     AttnArgs aa;
     memset(&aa, 0, sizeof(aa));
     aa.q = q; aa.out = attn;
@@ -171,17 +172,17 @@ static s2p_status layer_general(s2p_model* m, const s2p_layer* L, const layer_ct
     if (c->split_k) {
         aa.part = (float*)m->attn_part.data; aa.counters = m->attn_ctr;
         aa.n_split_slots = m->n_split_slots; aa.workers = attn_workers_for(rows);
-        S2P_CUDA_TRY(attn_decode(&aa, rows, st));
+        S2P_LAUNCH(m, attn_decode(&aa, rows, st));
     } else {
-        S2P_CUDA_TRY(attn_single(&aa, rows, st));
+        S2P_LAUNCH(m, attn_single(&aa, rows, st));
     }
     S2P_TRY(lin_apply(m, &L->wo, attn, proj, rows, c->decode));
-    S2P_CUDA_TRY(add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
-    S2P_CUDA_TRY(rms_norm(x, L->ffn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
+    S2P_LAUNCH(m, add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
+    S2P_LAUNCH(m, rms_norm(x, L->ffn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
     S2P_TRY(lin_apply(m, &L->gate_up, norm, gu, rows, c->decode));
-    S2P_CUDA_TRY(silu_mul(gu, hff, rows, S2P_FFN_DIM, st));
+    S2P_LAUNCH(m, silu_mul(gu, hff, rows, S2P_FFN_DIM, st));
     S2P_TRY(lin_apply(m, &L->w2, hff, proj, rows, c->decode));
-    S2P_CUDA_TRY(add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
+    S2P_LAUNCH(m, add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
     return S2P_OK;
 }
 
@@ -254,16 +255,16 @@ s2p_status s2p_session_prefill(s2p_session* s, const int64_t* ids, const uint8_t
         }
     }
     if (m->embed_i8_only)
-        S2P_CUDA_TRY(embed_rows_i8(m->embed_i8.data, (const float*)m->embed_scale.data, (const int64_t*)m->sids.data,
+        S2P_LAUNCH(m, embed_rows_i8(m->embed_i8.data, (const float*)m->embed_scale.data, (const int64_t*)m->sids.data,
                                    m->sx.data, n_ids, S2P_DIM, st));
     else
-        S2P_CUDA_TRY(embed_rows(m->embed.data, (const int64_t*)m->sids.data, m->sx.data, n_ids, S2P_DIM, st));
+        S2P_LAUNCH(m, embed_rows(m->embed.data, (const int64_t*)m->sids.data, m->sx.data, n_ids, S2P_DIM, st));
     for (int p = 0; p < n_parts; p++) {
         const int T = parts[p].T;
         s2p_dev_bf16* rows0 = BF(m->sx) + (size_t)part_start[p] * S2P_DIM;
-        S2P_CUDA_TRY(vq_embed_add(m->cb_emb.data, (const int32_t*)m->svq.data + part_off[p], T, rows0, st));
+        S2P_LAUNCH(m, vq_embed_add(m->cb_emb.data, (const int32_t*)m->svq.data + part_off[p], T, rows0, st));
         /* prefill DIVIDES by sqrt(11); decode multiplies by the reciprocal (slowar.c:350-353) */
-        S2P_CUDA_TRY(scale_div(rows0, (int64_t)T * S2P_DIM, (float)SQRT11, st));
+        S2P_LAUNCH(m, scale_div(rows0, (int64_t)T * S2P_DIM, (float)SQRT11, st));
     }
 
     layer_ctx c;
@@ -286,7 +287,7 @@ s2p_status s2p_session_prefill(s2p_session* s, const int64_t* ids, const uint8_t
         }
     }
     /* the final-normed LAST hidden is what frame 0 samples from and what primes the fast-AR */
-    S2P_CUDA_TRY(rms_norm(BF(m->sx) + (size_t)(n_ids - 1) * S2P_DIM, m->final_norm.data, s->pending_hidden.data, 1,
+    S2P_LAUNCH(m, rms_norm(BF(m->sx) + (size_t)(n_ids - 1) * S2P_DIM, m->final_norm.data, s->pending_hidden.data, 1,
                           S2P_DIM, S2P_NORM_EPS, st));
     dump_bf16("backbone_final_norm", s->pending_hidden.data, S2P_DIM, st);
     S2P_CUDA_TRY(cudaStreamSynchronize(st));
@@ -372,7 +373,7 @@ static s2p_status tick_begin_rows(s2p_model* m, const tick_dev* d, int bd) {
     a.ids = d->ids; a.codes = d->codes; a.mask = d->mask;
     a.x = BF(m->sx);
     a.keys = m->fkeys;
-    S2P_CUDA_TRY(tick_begin(&a, bd, m->stream));
+    S2P_LAUNCH(m, tick_begin(&a, bd, m->stream));
     return S2P_OK;
 }
 
@@ -388,13 +389,14 @@ static s2p_status head_and_sample(s2p_model* m, const tick_dev* d, int nact, int
         for (int m0 = 0; m0 < nact; m0 += S2P_INT8_GEMV_MAX_M) {
             const int mm = nact - m0 < S2P_INT8_GEMV_MAX_M ? nact - m0 : S2P_INT8_GEMV_MAX_M;
             const char* hh = (const char*)m->shidden.data + (size_t)m0 * S2P_DIM * 2;
+            m->tick_kernels += 2;
             S2P_TRY(s2p_int8_gemv((char*)m->slogc.data + (size_t)m0 * 4096 * 2, hh,
                                   q + (size_t)S2P_TOK_SEMANTIC_START * S2P_DIM, sc + S2P_TOK_SEMANTIC_START, mm, 4096,
                                   S2P_DIM, st));
             S2P_TRY(s2p_int8_gemv((char*)m->sloge.data + (size_t)m0 * 2, hh, q + (size_t)S2P_TOK_EOS * S2P_DIM,
                                   sc + S2P_TOK_EOS, mm, 1, S2P_DIM, st));
         }
-        S2P_CUDA_TRY(sample_rows(m->slogc.data, 4096, m->sloge.data, 1, d->samp, nact, d->tok, d->sem, d->ocodes,
+        S2P_LAUNCH(m, sample_rows(m->slogc.data, 4096, m->sloge.data, 1, d->samp, nact, d->tok, d->sem, d->ocodes,
                                  d->eos, st));
         return S2P_OK;
     }
@@ -413,7 +415,7 @@ static s2p_status head_and_sample(s2p_model* m, const tick_dev* d, int nact, int
         if (dump_step < 2) dump_bf16(dump_step == 0 ? "prefill_logits" : "step1_logits", m->slogits.data, S2P_TEXT_VOCAB, st);
         dump_step++;
     }
-    S2P_CUDA_TRY(sample_rows((const uint16_t*)m->slogits.data + S2P_TOK_SEMANTIC_START, S2P_TEXT_VOCAB,
+    S2P_LAUNCH(m, sample_rows((const uint16_t*)m->slogits.data + S2P_TOK_SEMANTIC_START, S2P_TEXT_VOCAB,
                              (const uint16_t*)m->slogits.data + S2P_TOK_EOS, S2P_TEXT_VOCAB, d->samp, nact, d->tok,
                              d->sem, d->ocodes, d->eos, st));
     return S2P_OK;
@@ -437,7 +439,7 @@ static s2p_status fast_frame_general(s2p_model* m, const tick_dev* d, int nact, 
         if (cb == 0) {
             next_codes = d->sem; /* the prime pass produces no logits; step 1 is fed embeddings[sem] */
         } else {
-            S2P_CUDA_TRY(rms_norm(m->fx.data, m->fast_norm.data, m->ft.data, nact, S2P_DIM, S2P_NORM_EPS, st));
+            S2P_LAUNCH(m, rms_norm(m->fx.data, m->fast_norm.data, m->ft.data, nact, S2P_DIM, S2P_NORM_EPS, st));
             S2P_TRY(lin_apply(m, &m->fast_out, m->ft.data, m->flogits.data, nact, 1));
             if (dump_ok && dump_dir() && nact == 1) {
                 static int dump_frame = 0;
@@ -449,12 +451,12 @@ static s2p_status fast_frame_general(s2p_model* m, const tick_dev* d, int nact, 
                 }
             }
             int32_t* dst = m->fstage + (size_t)(cb - 1) * nact;
-            S2P_CUDA_TRY(argmax_rows(m->flogits.data, dst, nact, S2P_CB_SIZE, st));
+            S2P_LAUNCH(m, argmax_rows(m->flogits.data, dst, nact, S2P_CB_SIZE, st));
             next_codes = dst;
         }
-        if (cb < S2P_NUM_CODEBOOKS - 1) S2P_CUDA_TRY(embed_codes(m->fast_emb.data, next_codes, m->fx.data, nact, st));
+        if (cb < S2P_NUM_CODEBOOKS - 1) S2P_LAUNCH(m, embed_codes(m->fast_emb.data, next_codes, m->fx.data, nact, st));
     }
-    S2P_CUDA_TRY(pack_frame(m->fstage, nact, d->ocodes, st));
+    S2P_LAUNCH(m, pack_frame(m->fstage, nact, d->ocodes, st));
     return S2P_OK;
 }
 
@@ -475,7 +477,7 @@ static s2p_status tick_general(s2p_model* m, s2p_session* const* act, int bd, in
             S2P_TRY(layer_general(m, &m->slow[l], &c, BF(m->sx), BF(m->snorm), BF(m->sqkv), BF(m->sq), BF(m->sattn),
                                   BF(m->sproj), BF(m->sgu), BF(m->sffn)));
         }
-        S2P_CUDA_TRY(rms_norm(m->sx.data, m->final_norm.data, m->shidden.data, bd, S2P_DIM, S2P_NORM_EPS, st));
+        S2P_LAUNCH(m, rms_norm(m->sx.data, m->final_norm.data, m->shidden.data, bd, S2P_DIM, S2P_NORM_EPS, st));
     }
     for (int b = bd; b < nact; b++) /* freshly prefilled rows sample from their stashed hidden (eager only) */
         S2P_CUDA_TRY(cudaMemcpyAsync(BF(m->shidden) + (size_t)b * S2P_DIM, act[b]->pending_hidden.data,
@@ -508,18 +510,18 @@ static s2p_status tick_fused_b1(s2p_model* m, s2p_session* const* act, int decod
         for (int l = 0; l < m->n_slow; l++) {
             const s2p_layer* L = &m->slow[l];
             s2p_lin_ref(&L->wqkv, &lr);
-            S2P_CUDA_TRY(stage_norm_gemv(&lr, &xr, L->attn_norm.data, S2P_NORM_EPS, BF(m->sqkv), st));
+            S2P_LAUNCH(m, stage_norm_gemv(&lr, &xr, L->attn_norm.data, S2P_NORM_EPS, BF(m->sqkv), st));
             slow_kv_offsets(m, l, &aa.kv);
-            S2P_CUDA_TRY(stage_attn_decode_prep(&aa, BF(m->sqkv), L->q_norm.data, L->k_norm.data, S2P_NORM_EPS,
+            S2P_LAUNCH(m, stage_attn_decode_prep(&aa, BF(m->sqkv), L->q_norm.data, L->k_norm.data, S2P_NORM_EPS,
                                                 S2P_ROPE_BASE, 1, st));
             s2p_lin_ref(&L->wo, &lr);
-            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->sattn), &xr, BF(m->sx), st));
+            S2P_LAUNCH(m, stage_gemv_resid(&lr, BF(m->sattn), &xr, BF(m->sx), st));
             s2p_lin_ref(&L->gate_up, &lr);
-            S2P_CUDA_TRY(stage_norm_swiglu(&lr, &xr, L->ffn_norm.data, S2P_NORM_EPS, BF(m->sffn), st));
+            S2P_LAUNCH(m, stage_norm_swiglu(&lr, &xr, L->ffn_norm.data, S2P_NORM_EPS, BF(m->sffn), st));
             s2p_lin_ref(&L->w2, &lr);
-            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->sffn), &xr, BF(m->sx), st));
+            S2P_LAUNCH(m, stage_gemv_resid(&lr, BF(m->sffn), &xr, BF(m->sx), st));
         }
-        S2P_CUDA_TRY(rms_norm(m->sx.data, m->final_norm.data, m->shidden.data, 1, S2P_DIM, S2P_NORM_EPS, st));
+        S2P_LAUNCH(m, rms_norm(m->sx.data, m->final_norm.data, m->shidden.data, 1, S2P_DIM, S2P_NORM_EPS, st));
     } else {
         S2P_CUDA_TRY(cudaMemcpyAsync(m->shidden.data, act[0]->pending_hidden.data, (size_t)S2P_DIM * 2,
                                      cudaMemcpyDeviceToDevice, st));
@@ -556,25 +558,25 @@ static s2p_status tick_fused_b1(s2p_model* m, s2p_session* const* act, int decod
             const s2p_layer* L = &m->fast[l];
             const VecRef* src = l == 0 ? &in : &fx;
             s2p_lin_ref(&L->wqkv, &lr);
-            S2P_CUDA_TRY(stage_norm_gemv(&lr, src, L->attn_norm.data, S2P_NORM_EPS, BF(m->fqkv), st));
+            S2P_LAUNCH(m, stage_norm_gemv(&lr, src, L->attn_norm.data, S2P_NORM_EPS, BF(m->fqkv), st));
             fast_kv_ref(m, l, &qa.kv);
             fa.kv = qa.kv;
-            S2P_CUDA_TRY(qkv_post(&qa, 1, st));
-            S2P_CUDA_TRY(attn_single(&fa, 1, st));
+            S2P_LAUNCH(m, qkv_post(&qa, 1, st));
+            S2P_LAUNCH(m, attn_single(&fa, 1, st));
             s2p_lin_ref(&L->wo, &lr);
-            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->fattn), src, BF(m->fx), st));
+            S2P_LAUNCH(m, stage_gemv_resid(&lr, BF(m->fattn), src, BF(m->fx), st));
             s2p_lin_ref(&L->gate_up, &lr);
-            S2P_CUDA_TRY(stage_norm_swiglu(&lr, &fx, L->ffn_norm.data, S2P_NORM_EPS, BF(m->fhff), st));
+            S2P_LAUNCH(m, stage_norm_swiglu(&lr, &fx, L->ffn_norm.data, S2P_NORM_EPS, BF(m->fhff), st));
             s2p_lin_ref(&L->w2, &lr);
-            S2P_CUDA_TRY(stage_gemv_resid(&lr, BF(m->fhff), &fx, BF(m->fx), st));
+            S2P_LAUNCH(m, stage_gemv_resid(&lr, BF(m->fhff), &fx, BF(m->fx), st));
         }
         if (cb > 0) {
             s2p_lin_ref(&m->fast_out, &lr);
-            S2P_CUDA_TRY(stage_norm_argmax(&lr, BF(m->fx), m->fast_norm.data, S2P_NORM_EPS, BF(m->flogits),
+            S2P_LAUNCH(m, stage_norm_argmax(&lr, BF(m->fx), m->fast_norm.data, S2P_NORM_EPS, BF(m->flogits),
                                            m->fkeys + (cb - 1), st));
         }
     }
-    S2P_CUDA_TRY(tick_finish_keys(m->fkeys, 1, d.ocodes, st));
+    S2P_LAUNCH(m, tick_finish_keys(m->fkeys, 1, d.ocodes, st));
     S2P_CUDA_TRY(cudaMemcpyAsync(m->h_out, m->d_out, m->out_bytes, cudaMemcpyDeviceToHost, st));
     return S2P_OK;
 }
@@ -642,10 +644,12 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
     const int fused = m->fused_b1 && nact == 1 && !m->head_full;
     const int steady = bd == nact && graphs; /* every row decoding: the launch sequence is frame-invariant */
     s2p_status rc = S2P_OK;
+    m->tick_kernels = 0;
     if (steady) {
         if (!m->gready[bd]) {
             S2P_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
             rc = fused ? tick_fused_b1(m, act, 1) : tick_general(m, act, bd, nact);
+            m->graph_kernels[bd] = m->tick_kernels;
             cudaGraph_t g = NULL;
             const cudaError_t ce = cudaStreamEndCapture(st, &g);
             if (rc != S2P_OK) {
@@ -664,12 +668,18 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
             }
             m->gready[bd] = 1;
         }
+        S2P_CUDA_TRY(cudaEventRecord(m->ev0, st));
         S2P_CUDA_TRY(cudaGraphLaunch(m->gexec[bd], st));
+        m->tick_kernels = m->graph_kernels[bd];
     } else {
+        S2P_CUDA_TRY(cudaEventRecord(m->ev0, st));
         rc = fused ? tick_fused_b1(m, act, bd == 1) : tick_general(m, act, bd, nact);
         if (rc != S2P_OK) return rc;
     }
+    S2P_CUDA_TRY(cudaEventRecord(m->ev1, st));
     S2P_CUDA_TRY(cudaStreamSynchronize(st));
+    m->last_rows = nact; m->last_fused = fused; m->last_graph = steady; m->last_kernels = m->tick_kernels;
+    if (cudaEventElapsedTime(&m->last_device_ms, m->ev0, m->ev1) != cudaSuccess) m->last_device_ms = 0.f;
     for (int b = 0; b < bd; b++) act[b]->kv_len++;
     m->frames_decoded += (uint64_t)nact;
 

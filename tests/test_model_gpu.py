@@ -41,3 +41,14 @@ def check(res):
 def test_two_layer_parity_config(mode):
     """64-token prompt, greedy and seeded-sampled decode, 2-layer backbone."""
     check(run_worker(mode, 2, 24))
+
+
+@pytest.mark.parametrize("mode", ["int4", "int8"])
+def test_full_model_200_frames(mode):
+    """BASELINE configurations 2 and 3: 36-layer backbone + 4-layer fast-AR, 512-token prompt,
+    200 frames greedy and 200 frames seeded T=0.8/top-p=0.8; every code of every frame and the
+    KV cache bytes must equal the reference's."""
+    res = run_worker(mode, 36, 200, prompt=512)
+    check(res)
+    for tag, run in res["runs"].items():
+        assert run["frames_ref"] >= 1
