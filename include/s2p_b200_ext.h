@@ -34,6 +34,31 @@ s2p_status s2p_b200_model_stats(const s2p_model* m, s2p_b200_stats* out);
 /* The stream every tick of this model is issued on (for external event timing). */
 cudaStream_t s2p_b200_model_stream(s2p_model* m);
 
+/* Decode attention that never asks the driver for memory.  (No counterpart in the
+ * reference: its split-K attention takes a caller-allocated scratch pointer.)
+ *
+ * Some hosts of this library may not allocate device memory while they run: a
+ * real-time audio worker whose tick must never wait on cudaMalloc / cudaFree (both
+ * serialise against every stream of the device, the vocoder's included), or an
+ * embedding application that gives a plug-in no memory pool of its own.  For them
+ * this entry point computes the split-K GQA decode attention of ONE query row —
+ * 32 query heads over 8 kv heads of width 128, bf16 cache planes
+ * [kv_heads, max_seq, 128], attending positions 0..pos — with its scratch (split
+ * partials and arrival counters) in a fixed ~2.1 MB array built into the library.
+ * The result equals the library's regular split-K decode attention bit for bit.
+ *
+ * Limits and rules:
+ *  - pos + 1 <= 8192 cached positions; anything larger is refused with S2P_ERR_INVALID
+ *    and a message (use the regular path, whose scratch is sized at model load);
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress); make that first call before starting any stream capture;
+ *  - all calls share the one array: calls that can overlap on the GPU (different
+ *    streams, or two host threads) race — issue them on one stream;
+ *  - no cudaMalloc, cudaFree or allocating library routine is called, ever. */
+s2p_status s2p_b200_attention_decode_noalloc(const s2p_bf16* q, const s2p_bf16* k_cache, const s2p_bf16* v_cache,
+                                             s2p_bf16* out, int q_heads, int kv_heads, int head_dim, int pos,
+                                             int max_seq, cudaStream_t stream);
+
 #pragma GCC visibility pop
 #ifdef __cplusplus
 }

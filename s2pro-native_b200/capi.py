@@ -125,6 +125,7 @@ EXT_PROTOTYPES = {
     "s2p_b200_version": (C.c_char_p, []),
     "s2p_b200_model_stats": (_I, [_P, C.POINTER(Stats)]),
     "s2p_b200_model_stream": (C.c_void_p, [_P]),
+    "s2p_b200_attention_decode_noalloc": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _S]),
 }
 
 

@@ -234,4 +234,68 @@ extern "C" cudaError_t attn_decode(const AttnArgs* a, int rows, cudaStream_t st)
     return launch_attn_decode(*a, nullptr, rows, st);
 }
 
+/* ---- allocation-free variant (include/s2p_b200_ext.h) --------------------------
+ * Split-K decode attention for one query row whose scratch (the per-split partials
+ * and the arrival counters) lives in a fixed array inside the library image instead
+ * of memory obtained from the driver.  Every GPU that loads the library carries the
+ * array (about 2.1 MB) until the process exits. */
+constexpr int NOALLOC_MAX_POSITIONS = 8192;                       /* cached positions a call may attend over */
+constexpr int NOALLOC_SLOTS = NOALLOC_MAX_POSITIONS / 64;          /* 64-position splits */
+constexpr size_t NOALLOC_PART_BYTES = (size_t)32 * NOALLOC_SLOTS * 130 * sizeof(float);
+constexpr size_t NOALLOC_CTR_BYTES = 8 * sizeof(unsigned int);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_PART_BYTES + NOALLOC_CTR_BYTES];
+
+}  // namespace s2p
+
+#include <stdio.h>
+#include "s2p_b200_ext.h"
+
+extern "C" s2p_status s2p_b200_attention_decode_noalloc(const s2p_bf16* q, const s2p_bf16* k_cache,
+                                                        const s2p_bf16* v_cache, s2p_bf16* out, int q_heads,
+                                                        int kv_heads, int head_dim, int pos, int max_seq,
+                                                        cudaStream_t stream) {
+    using namespace s2p;
+    if (!q || !k_cache || !v_cache || !out) return S2P_ERR_INVALID;
+    if (q_heads != 32 || kv_heads != 8 || head_dim != 128) {
+        fprintf(stderr, "[s2pro] attention_decode_noalloc: only 32 query / 8 kv heads of width 128 are served\n");
+        return S2P_ERR_INVALID;
+    }
+    if (pos < 0 || pos >= max_seq || pos + 1 > NOALLOC_MAX_POSITIONS) {
+        fprintf(stderr, "[s2pro] attention_decode_noalloc: position %d outside the cache (%d) or beyond the built-in "
+                        "scratch limit of %d positions\n", pos, max_seq, NOALLOC_MAX_POSITIONS);
+        return S2P_ERR_INVALID;
+    }
+    /* The array's name is only a host-side handle; the kernel needs its device address.
+     * It is looked up once per device, with that device current. */
+    static void* dev_addr[64] = {0};
+    int dev = -1;
+    S2P_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return S2P_ERR_UNSUPPORTED;
+    if (!dev_addr[dev]) {
+        void* p = NULL;
+        S2P_CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        dev_addr[dev] = p;
+    }
+    unsigned char* base = static_cast<unsigned char*>(dev_addr[dev]);
+    unsigned int* counters = reinterpret_cast<unsigned int*>(base + NOALLOC_PART_BYTES);
+    /* the array keeps whatever the previous call left: the arrival counters must start at zero */
+    S2P_CUDA_TRY(cudaMemsetAsync(counters, 0, NOALLOC_CTR_BYTES, stream));
+    AttnArgs a = {};
+    a.q = reinterpret_cast<const __nv_bfloat16*>(q);
+    a.out = reinterpret_cast<__nv_bfloat16*>(out);
+    a.q_heads = q_heads; a.kv_heads = kv_heads; a.max_seq = max_seq; a.kv8 = 0; a.head_dim = head_dim;
+    a.pos0 = pos; a.pos_row_step = 0;
+    a.kv.base0 = (void*)k_cache;
+    a.kv.k_off = 0;
+    a.kv.v_off = (size_t)((const char*)v_cache - (const char*)k_cache);
+    a.part = reinterpret_cast<float*>(base);
+    a.counters = counters;
+    a.n_split_slots = NOALLOC_SLOTS;
+    a.workers = 16;
+    S2P_CUDA_TRY(launch_attn_decode(a, nullptr, 1, stream));
+    return S2P_OK;
+}
+
+namespace s2p {
+
 }  // namespace s2p
