@@ -27,10 +27,9 @@ int device_sm_count() {
 template <int WK, int PRO, int EPI>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stage(GemvStage g) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const int units = (EPI == EPI_SWIGLU) ? (g.N >> 1) : g.N;
-    const int row0 = (int)((long long)units * blockIdx.x / gridDim.x);
-    const int row1 = (int)((long long)units * (blockIdx.x + 1) / gridDim.x);
-    gemv_stage_cta<WK, PRO, EPI>(g, row0, row1 - row0, smem);
+    int row0, cnt;
+    gemv_cta_rows<EPI>(g, blockIdx.x, gridDim.x, row0, cnt);
+    gemv_stage_cta<WK, PRO, EPI>(g, row0, cnt, smem);
 }
 
 /* Rows per pass that keep the CTA's shared memory within `budget` bytes. */

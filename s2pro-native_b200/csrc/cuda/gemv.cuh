@@ -1,6 +1,6 @@
 /* Weight-streaming dequant GEMV for batch-1 decode, as a device-side stage
- * that both the stand-alone launchers (gemv.cu) and the fused decode tick
- * (tick.cu) instantiate.
+ * that the stand-alone launchers (gemv.cu), the fused per-stage tick (tick.cu)
+ * and the persistent tick kernel (mega.cu) all instantiate.
  *
  * Arithmetic contract (bit-exact with the reference GEMVs,
  * src/sched/int8_gemv.cu:60-104 per-channel INT8, :197-242 group scale on an
@@ -11,16 +11,27 @@
  * acc = fma(s, group_scale, acc) (INT4); the 32 lane values are merged by the
  * 16/8/4/2/1 tree; INT8 multiplies by the row scale; one bf16 rounding.
  *
- * Mapping to B200 (what is NOT the reference's): the unit of work is a
- * (row-group, K-tile) job, so a 2560-row matrix still offers thousands of
- * independent jobs to the 148 SMs; a CTA owns a contiguous block of rows, i.e.
- * one contiguous span of HBM; every lane keeps two jobs of 8-byte (INT4) or
- * 16-byte (INT8) loads in flight; codes are widened to f32 with one byte-permute
- * and one exact subtraction (no int->float converts); two rows advance per
- * instruction through the packed f32x2 fma of sm_100, each half being its own
- * IEEE fma chain; the activation vector is staged once per CTA in shared
- * memory in the lane order the jobs read it; per-tile partials cross warps
- * through shared memory and one warp per row folds them in the fixed order.
+ * Mapping to B200 (what is NOT the reference's):
+ *  - the unit of work is one (row, K-tile) pair; the units of a CTA's row block
+ *    are laid out tile-major and cut into 16 equal contiguous ranges, one per
+ *    warp, so a 2560-row matrix loads all 148 x 16 warps evenly; per-tile
+ *    partials cross warps through shared memory and one warp per row folds
+ *    them in the fixed order;
+ *  - INT4: a packed word becomes four bf16x2 registers with one shift and one
+ *    logic op each (nibble | 0x4300 = 128 + code) and one packed bf16
+ *    subtraction of 136; the products run on the mixed-precision fma of sm_100
+ *    (fma.rn.f32.bf16: bf16 x bf16 exact product, f32 accumulate), which is
+ *    bit-identical to fmaf((float)w, (float)x, s) because codes and
+ *    activations are exactly representable in bf16.  Measured 3.25
+ *    instructions per weight against 3.9 for byte-permute + packed f32x2 fma
+ *    and 4.7 for the scalar int->float route;
+ *  - INT8: byte-permute into the mantissa of 2^23, one exact subtraction, f32 fma;
+ *  - the activation vector is staged once per CTA in shared memory in the lane
+ *    order the units read it (bf16 pairs for INT4, f32 for INT8);
+ *  - activations, residuals and indices written by other SMs are read with
+ *    L1-bypassing loads, so the same code is correct inside a persistent kernel;
+ *  - a CTA can prefetch its slice of the NEXT stage's weights into L2 while it
+ *    waits at a stage boundary (weight addresses never depend on activations).
  */
 #pragma once
 #include "common.cuh"
@@ -56,160 +67,200 @@ struct GemvStage {
     const int32_t* resid_index;       /* optional device index: resid_src is row *resid_index of a [*,N] table */
     const unsigned long long* resid_key; /* same, from a packed arg-max key */
     unsigned long long* argmax_key;   /* EPI_ARGMAX */
+    __nv_bfloat16* normed_out;        /* PRO_NORM, optional: CTA 0 also writes the normalised vector here */
     int rows_per_pass;                /* rows (row pairs for EPI_SWIGLU) the shared partial buffer holds */
 };
 
 constexpr int GEMV_THREADS = 512;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
+constexpr int GEMV_GROUP = 4; /* units a warp keeps in flight together */
 
-/* rows advanced together by one job */
-template <int WK> struct JobRows { static constexpr int value = (WK == WK_INT4_PACK) ? 8 : 4; };
+__host__ __device__ inline size_t gemv_x_bytes(int wk, int K) { return (size_t)K * (wk == WK_INT4_PACK ? 2 : 4); }
 
-__host__ __device__ inline size_t gemv_smem_bytes(int wk, int rows_per_cta, int K, int gshift) {
+__host__ __device__ inline size_t gemv_smem_bytes(int wk, int rows_local, int K, int gshift) {
     const int T = K / 512;
-    size_t b = (size_t)K * 8;                             /* x, duplicated f32 pairs */
-    b += (size_t)rows_per_cta * T * 32 * sizeof(float);   /* per-tile lane partials */
-    if (wk != WK_INT8_CH) b += ((size_t)rows_per_cta * (K >> gshift) * 2 + 15) & ~(size_t)15;
+    size_t b = gemv_x_bytes(wk, K);
+    b += (size_t)rows_local * T * 32 * sizeof(float);   /* per-tile lane partials */
+    if (wk != WK_INT8_CH) b += ((size_t)rows_local * (K >> gshift) * 2 + 15) & ~(size_t)15;
     return b + 1024 /* reduction scratch */;
-}
-
-/* Shared-memory slot of activation k as a duplicated pair (x_k, x_k).  A lane
- * reads its 16 activations of a tile as eight 16-byte words, consecutive lanes
- * touching consecutive words (no bank conflicts). */
-__device__ __forceinline__ int xs_slot(int k) {
-    const int i = k >> 9, l = (k >> 4) & 31, j = k & 15;
-    return (((i * 8 + (j >> 1)) * 32 + l) << 2) + ((j & 1) << 1);
 }
 
 /* index held in a packed arg-max key (see EPI_ARGMAX) */
 __device__ __forceinline__ uint32_t key_index(unsigned long long key) { return 0xFFFFFFFFu - (uint32_t)key; }
 
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-
-/* 8 nibbles of two rows (same columns) -> 8 steps of the two fma chains. */
-__device__ __forceinline__ void chain_int4_word(uint32_t wa, uint32_t wb, const float4* xq, float2& s) {
-    const uint32_t a = wa ^ 0x88888888u, b = wb ^ 0x88888888u;
-    const uint32_t ae = a & 0x0F0F0F0Fu, ao = (a >> 4) & 0x0F0F0F0Fu;
-    const uint32_t be = b & 0x0F0F0F0Fu, bo = (b >> 4) & 0x0F0F0F0Fu;
-    const float2 bias = make_float2(-8388616.0f, -8388616.0f); /* -(2^23 + 8) */
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-        const float4 xv = xq[t]; /* (x_2t, x_2t, x_2t+1, x_2t+1) */
-        float2 f;
-        f.x = __uint_as_float(__byte_perm(ae, 0x4B000000u, 0x7540u | t));
-        f.y = __uint_as_float(__byte_perm(be, 0x4B000000u, 0x7540u | t));
-        s = ffma2(__fadd2_rn(f, bias), make_float2(xv.x, xv.y), s);
-        f.x = __uint_as_float(__byte_perm(ao, 0x4B000000u, 0x7540u | t));
-        f.y = __uint_as_float(__byte_perm(bo, 0x4B000000u, 0x7540u | t));
-        s = ffma2(__fadd2_rn(f, bias), make_float2(xv.z, xv.w), s);
-    }
+/* L1-bypassing loads for data other SMs may have written during this kernel */
+__device__ __forceinline__ float ldcg_bf16(const __nv_bfloat16* p) {
+    return bf_bits_to_f32(__ldcg(reinterpret_cast<const unsigned short*>(p)));
 }
 
-/* 4 int8 codes of two rows -> 4 steps. xq: two 16-byte words = 4 duplicated pairs. */
-__device__ __forceinline__ void chain_int8_word(uint32_t wa, uint32_t wb, const float4* xq, float2& s) {
-    const uint32_t a = wa ^ 0x80808080u, b = wb ^ 0x80808080u;
-    const float2 bias = make_float2(-8388736.0f, -8388736.0f); /* -(2^23 + 128) */
-#pragma unroll
-    for (int t = 0; t < 2; t++) {
-        const float4 xv = xq[t];
-        float2 f;
-        f.x = __uint_as_float(__byte_perm(a, 0x4B000000u, 0x7540u | (2 * t)));
-        f.y = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7540u | (2 * t)));
-        s = ffma2(__fadd2_rn(f, bias), make_float2(xv.x, xv.y), s);
-        f.x = __uint_as_float(__byte_perm(a, 0x4B000000u, 0x7540u | (2 * t + 1)));
-        f.y = __uint_as_float(__byte_perm(b, 0x4B000000u, 0x7540u | (2 * t + 1)));
-        s = ffma2(__fadd2_rn(f, bias), make_float2(xv.z, xv.w), s);
-    }
+/* mixed-precision fma: s + w * x with bf16 w, x (exact product), f32 s, one rounding */
+__device__ __forceinline__ float fma_bf16(unsigned short w, unsigned short x, float s) {
+    asm("fma.rn.f32.bf16 %0, %1, %2, %0;" : "+f"(s) : "h"(w), "h"(x));
+    return s;
 }
 
-template <int WK> struct LaneTile;  /* the bytes one lane owns of one (row, tile) */
+/* 8 packed nibbles (weights j = 0..7 of a half tile) against 8 bf16 activations */
+__device__ __forceinline__ void chain_int4_word(uint32_t w, const unsigned short* xh, float& s) {
+    const uint32_t a = w ^ 0x88888888u; /* two's complement nibble -> code + 8 */
+    unsigned short lo[4], hi[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        uint32_t m = ((a >> (4 * k)) & 0x000F000Fu) | 0x43004300u; /* bf16x2 (128 + n_k, 128 + n_{k+4}) */
+        __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&m);
+        const uint32_t c = 0x43084308u;                            /* (136, 136) */
+        h = __hsub2(h, *reinterpret_cast<const __nv_bfloat162*>(&c));
+        const uint32_t p = *reinterpret_cast<uint32_t*>(&h);
+        asm("mov.b32 {%0,%1}, %2;" : "=h"(lo[k]), "=h"(hi[k]) : "r"(p));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; j++) s = fma_bf16(lo[j], xh[j], s);
+#pragma unroll
+    for (int j = 0; j < 4; j++) s = fma_bf16(hi[j], xh[4 + j], s);
+}
+
+/* 4 int8 codes (weights j = 0..3 of a quarter tile) against 4 f32 activations */
+__device__ __forceinline__ void chain_int8_word(uint32_t w, const float4& xv, float& s) {
+    const uint32_t a = w ^ 0x80808080u;
+    const float bias = 8388736.0f; /* 2^23 + 128 */
+    s = __fmaf_rn(__uint_as_float(__byte_perm(a, 0x4B000000u, 0x7540u)) - bias, xv.x, s);
+    s = __fmaf_rn(__uint_as_float(__byte_perm(a, 0x4B000000u, 0x7541u)) - bias, xv.y, s);
+    s = __fmaf_rn(__uint_as_float(__byte_perm(a, 0x4B000000u, 0x7542u)) - bias, xv.z, s);
+    s = __fmaf_rn(__uint_as_float(__byte_perm(a, 0x4B000000u, 0x7543u)) - bias, xv.w, s);
+}
+
+template <int WK> struct LaneTile;  /* the bytes one lane owns of one (row, tile) unit */
 template <> struct LaneTile<WK_INT4_PACK> { typedef uint2 type; };
 template <> struct LaneTile<WK_INT8_CH> { typedef uint4 type; };
 template <> struct LaneTile<WK_INT8_GRP> { typedef uint4 type; };
 
+/* The activations one lane needs for one tile, held in registers while the warp
+ * walks the rows of that tile. */
+template <int WK> struct LaneX;
+template <> struct LaneX<WK_INT4_PACK> {
+    unsigned short h[16];
+    __device__ __forceinline__ void load(const unsigned char* xs, int tile, int lane) {
+        const uint4* p = reinterpret_cast<const uint4*>(xs);
+        const uint4 a = p[(tile * 2) * 32 + lane], b = p[(tile * 2 + 1) * 32 + lane];
+        const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) asm("mov.b32 {%0,%1}, %2;" : "=h"(h[2 * i]), "=h"(h[2 * i + 1]) : "r"(w[i]));
+    }
+    __device__ __forceinline__ float unit(const uint2& t) const {
+        float s = 0.f;
+        chain_int4_word(t.x, h, s);
+        chain_int4_word(t.y, h + 8, s);
+        return s;
+    }
+};
+template <> struct LaneX<WK_INT8_CH> {
+    float4 v[4];
+    __device__ __forceinline__ void load(const unsigned char* xs, int tile, int lane) {
+        const float4* p = reinterpret_cast<const float4*>(xs);
+#pragma unroll
+        for (int q = 0; q < 4; q++) v[q] = p[(tile * 4 + q) * 32 + lane];
+    }
+    __device__ __forceinline__ float unit(const uint4& t) const {
+        float s = 0.f;
+        chain_int8_word(t.x, v[0], s);
+        chain_int8_word(t.y, v[1], s);
+        chain_int8_word(t.z, v[2], s);
+        chain_int8_word(t.w, v[3], s);
+        return s;
+    }
+};
+template <> struct LaneX<WK_INT8_GRP> : LaneX<WK_INT8_CH> {};
+
+/* write activation k (already rounded to bf16, given as f32) into the staging area */
 template <int WK>
-__device__ __forceinline__ void chain_tile(const typename LaneTile<WK>::type& a, const typename LaneTile<WK>::type& b,
-                                           const float4* xq, float2& s);
-template <>
-__device__ __forceinline__ void chain_tile<WK_INT4_PACK>(const uint2& a, const uint2& b, const float4* xq, float2& s) {
-    chain_int4_word(a.x, b.x, xq, s);
-    chain_int4_word(a.y, b.y, xq + 4, s);
-}
-template <>
-__device__ __forceinline__ void chain_tile<WK_INT8_CH>(const uint4& a, const uint4& b, const float4* xq, float2& s) {
-    chain_int8_word(a.x, b.x, xq, s);
-    chain_int8_word(a.y, b.y, xq + 2, s);
-    chain_int8_word(a.z, b.z, xq + 4, s);
-    chain_int8_word(a.w, b.w, xq + 6, s);
-}
-template <>
-__device__ __forceinline__ void chain_tile<WK_INT8_GRP>(const uint4& a, const uint4& b, const float4* xq, float2& s) {
-    chain_tile<WK_INT8_CH>(a, b, xq, s);
+__device__ __forceinline__ void xs_store(unsigned char* xs, int k, float v) {
+    const int i = k >> 9, l = (k >> 4) & 31, j = k & 15;
+    if (WK == WK_INT4_PACK) {
+        reinterpret_cast<unsigned short*>(xs)[(((i * 2 + (j >> 3)) * 32 + l) << 3) + (j & 7)] =
+            (unsigned short)(__float_as_uint(v) >> 16);
+    } else {
+        reinterpret_cast<float*>(xs)[(((i * 4 + (j >> 2)) * 32 + l) << 2) + (j & 3)] = v;
+    }
 }
 
 /* ---- prologue: stage the activation vector ------------------------------- */
-template <int PRO>
-__device__ __forceinline__ void stage_activation(const GemvStage& g, float* xs, float* red) {
+template <int WK, int PRO>
+__device__ __forceinline__ void stage_activation(const GemvStage& g, unsigned char* xs, float* red) {
     const int K = g.K;
     const __nv_bfloat16* x = g.x;
-    if (g.x_index) x += (size_t)(*g.x_index) * K;
-    else if (g.x_key) x += (size_t)key_index(*g.x_key) * K;
+    if (g.x_index) x += (size_t)__ldcg(g.x_index) * K;
+    else if (g.x_key) x += (size_t)key_index(__ldcg(g.x_key)) * K;
     if (PRO == PRO_VEC) {
-        for (int k = threadIdx.x; k < K; k += blockDim.x) {
-            const float v = bf2f(x[k]);
-            const int s = xs_slot(k);
-            xs[s] = v;
-            xs[s + 1] = v;
-        }
+        for (int k = threadIdx.x; k < K; k += blockDim.x) xs_store<WK>(xs, k, ldcg_bf16(x + k));
     } else {
         /* 256 strided partial sums of squares, halving tree, rsqrtf(mean + eps):
          * src/slowar/kernels.cu:46-68 */
         float ss = 0.f;
         if (threadIdx.x < 256)
             for (int i = threadIdx.x; i < K; i += 256) {
-                const float v = bf2f(x[i]);
+                const float v = ldcg_bf16(x + i);
                 ss = __fmaf_rn(v, v, ss);
             }
         const float tot = block_tree<256, false>(ss, red);
         const float inv = rsqrtf(__fdiv_rn(tot, (float)K) + g.eps);
+        const bool emit = g.normed_out != nullptr && blockIdx.x == 0;
         for (int k = threadIdx.x; k < K; k += blockDim.x) {
-            const float v = bf16_round(__fmul_rn(__fmul_rn(bf2f(x[k]), inv), bf2f(g.norm_w[k])));
-            const int s = xs_slot(k);
-            xs[s] = v;
-            xs[s + 1] = v;
+            const __nv_bfloat16 nb = f2bf(__fmul_rn(__fmul_rn(ldcg_bf16(x + k), inv), bf2f(g.norm_w[k])));
+            xs_store<WK>(xs, k, bf2f(nb));
+            if (emit) g.normed_out[k] = nb;
         }
     }
 }
 
+/* Ask L2 for this CTA's slice of a stage's weights and scales (no registers held,
+ * nothing waits on it). */
+template <int WK, int EPI>
+__device__ __forceinline__ void gemv_prefetch_l2(const GemvStage& g, int row0, int cnt) {
+    if (cnt <= 0) return;
+    const size_t row_bytes = (WK == WK_INT4_PACK) ? (size_t)(g.K >> 1) : (size_t)g.K;
+    const size_t sc_row = (WK == WK_INT8_CH) ? 4 : (size_t)(g.K >> g.gshift) * 2;
+    const int regions = (EPI == EPI_SWIGLU) ? 2 : 1;
+    for (int r = 0; r < regions; r++) {
+        const size_t first = (size_t)row0 + (r ? (size_t)(g.N >> 1) : 0);
+        const char* wp = static_cast<const char*>(g.w) + first * row_bytes;
+        const size_t wlines = ((size_t)cnt * row_bytes + 127) >> 7;
+        for (size_t i = threadIdx.x; i < wlines; i += blockDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(wp + (i << 7)));
+        const char* sp = static_cast<const char*>(g.scales) + first * sc_row;
+        const size_t slines = ((size_t)cnt * sc_row + 127) >> 7;
+        for (size_t i = threadIdx.x; i < slines; i += blockDim.x)
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + (i << 7)));
+    }
+}
+
 /* ---- the stage ------------------------------------------------------------
- * Rows [row0, row0+cnt) of the matrix belong to this CTA; with EPI_SWIGLU the
- * CTA owns gate rows [row0, row0+cnt) and up rows [F+row0, F+row0+cnt), F = N/2.
- * The rows are walked in passes of at most g.rows_per_pass (what the partial
- * buffer in shared memory holds).  smem: dynamic shared memory base, sized by
+ * Rows [row0, row0+cnt_total) of the matrix belong to this CTA; with EPI_SWIGLU
+ * the CTA owns gate rows [row0, ..) and up rows [F+row0, ..), F = N/2.  The rows
+ * are walked in passes of at most g.rows_per_pass (what the partial buffer in
+ * shared memory holds).  smem: dynamic shared memory base, sized by
  * gemv_smem_bytes(wk, rows_per_pass * (swiglu ? 2 : 1), K, gshift).
  * All threads of the CTA (GEMV_THREADS) must call this. */
 template <int WK, int PRO, int EPI>
 __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsigned char* smem) {
     typedef typename LaneTile<WK>::type tile_t;
-    constexpr int R = JobRows<WK>::value;
     constexpr int SW = (EPI == EPI_SWIGLU) ? 2 : 1;
+    constexpr int R = GEMV_GROUP;
+    if (cnt_total <= 0) return; /* uniform over the CTA */
     const int K = g.K, T = K >> 9;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int F = g.N >> 1;
     const size_t row_bytes = (WK == WK_INT4_PACK) ? (size_t)(K >> 1) : (size_t)K;
-    const int sc_per_row = (WK == WK_INT8_CH) ? 0 : (K >> g.gshift);
+    const int sc_per_row = (WK == WK_INT8_CH) ? 1 : (K >> g.gshift);
     const int cap_rows = g.rows_per_pass * SW;
 
-    float* xs = reinterpret_cast<float*>(smem);
-    float* part = xs + 2 * K;
+    unsigned char* xs = smem;
+    float* part = reinterpret_cast<float*>(smem + ((gemv_x_bytes(WK, K) + 15) & ~(size_t)15));
     __half* sc_s = reinterpret_cast<__half*>(part + (size_t)cap_rows * T * 32);
-    float* red = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(sc_s) +
-                                          (((size_t)cap_rows * sc_per_row * 2 + 15) & ~(size_t)15));
-    const unsigned char* wbase = static_cast<const unsigned char*>(g.w);
-    const float4* xs4 = reinterpret_cast<const float4*>(xs);
+    float* red = reinterpret_cast<float*>(
+        reinterpret_cast<unsigned char*>(sc_s) +
+        ((WK == WK_INT8_CH) ? 0 : (((size_t)cap_rows * sc_per_row * 2 + 15) & ~(size_t)15)));
+    const unsigned char* wbase = static_cast<const unsigned char*>(g.w) + (size_t)lane * sizeof(tile_t);
     unsigned long long best = 0ull;
 
-    if (cnt_total <= 0) return; /* uniform over the CTA */
     for (int done = 0; done < cnt_total; done += g.rows_per_pass) {
         const int cnt = min(g.rows_per_pass, cnt_total - done);
         const int r0 = row0 + done;
@@ -218,66 +269,65 @@ __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsi
             if (EPI == EPI_SWIGLU) return lr < cnt ? r0 + lr : F + r0 + (lr - cnt);
             return r0 + lr;
         };
-        const int n_jobs = ((local_rows + R - 1) / R) * T;
-        auto load_job = [&](int job, tile_t* buf) {
-            const int oct = job / T, tile = job - oct * T;
-#pragma unroll
-            for (int r = 0; r < R; r++) {
-                int lr = oct * R + r;
-                lr = lr < local_rows ? lr : local_rows - 1;
-                const unsigned char* p = wbase + (size_t)global_row(lr) * row_bytes +
-                                         (size_t)tile * (sizeof(tile_t) * 32) + (size_t)lane * sizeof(tile_t);
-                buf[r] = *reinterpret_cast<const tile_t*>(p);
-            }
-        };
+        /* this warp's contiguous range of (tile-major) units */
+        const int U = local_rows * T;
+        int u = (int)((long long)U * warp / GEMV_WARPS);
+        const int u_end = (int)((long long)U * (warp + 1) / GEMV_WARPS);
+        int tile = u / local_rows, lr = u - tile * local_rows;
 
-        /* weight and scale traffic does not depend on the activations: start it first */
+        /* a group = up to R consecutive rows of one tile */
+        auto group_size = [&](int uu, int l) { return min(R, min(u_end - uu, local_rows - l)); };
+        auto load_group = [&](int t, int l, int n, tile_t* buf) {
+#pragma unroll
+            for (int r = 0; r < R; r++)
+                if (r < n)
+                    buf[r] = *reinterpret_cast<const tile_t*>(wbase + (size_t)global_row(l + r) * row_bytes +
+                                                              (size_t)t * (sizeof(tile_t) * 32));
+        };
         tile_t cur[R], nxt[R];
-        int job = warp;
-        if (job < n_jobs) load_job(job, cur);
+        int n_cur = (u < u_end) ? group_size(u, lr) : 0;
+        if (n_cur) load_group(tile, lr, n_cur, cur); /* weights do not depend on the activations: first */
         if constexpr (WK != WK_INT8_CH) {
             const __half* sg = static_cast<const __half*>(g.scales);
             for (int idx = threadIdx.x; idx < local_rows * sc_per_row; idx += blockDim.x) {
-                const int lr = idx / sc_per_row, c = idx - lr * sc_per_row;
-                sc_s[idx] = sg[(size_t)global_row(lr) * sc_per_row + c];
+                const int l = idx / sc_per_row, c = idx - l * sc_per_row;
+                sc_s[idx] = sg[(size_t)global_row(l) * sc_per_row + c];
             }
         }
-        if (done == 0) stage_activation<PRO>(g, xs, red);
+        if (done == 0) stage_activation<WK, PRO>(g, xs, red);
         __syncthreads();
 
-        for (; job < n_jobs; job += GEMV_WARPS) {
-            const int njob = job + GEMV_WARPS;
-            if (njob < n_jobs) load_job(njob, nxt);
-            const int oct = job / T, tile = job - oct * T;
-            float4 xq[8];
+        LaneX<WK> lx;
+        int x_tile = -1;
+        while (n_cur) {
+            /* next group: same tile while rows remain, else the first rows of the next tile */
+            int u2 = u + n_cur, lr2 = lr + n_cur, tile2 = tile;
+            if (lr2 == local_rows) { lr2 = 0; tile2++; }
+            const int n_nxt = (u2 < u_end) ? group_size(u2, lr2) : 0;
+            if (n_nxt) load_group(tile2, lr2, n_nxt, nxt);
+            if (tile != x_tile) { lx.load(xs, tile, lane); x_tile = tile; }
 #pragma unroll
-            for (int q = 0; q < 8; q++) xq[q] = xs4[(tile * 8 + q) * 32 + lane];
-#pragma unroll
-            for (int p = 0; p < R / 2; p++) {
-                float2 s = make_float2(0.f, 0.f);
-                chain_tile<WK>(cur[2 * p], cur[2 * p + 1], xq, s);
-                const int lr = oct * R + 2 * p;
-                if (lr < local_rows) part[((size_t)lr * T + tile) * 32 + lane] = s.x;
-                if (lr + 1 < local_rows) part[((size_t)(lr + 1) * T + tile) * 32 + lane] = s.y;
-            }
+            for (int r = 0; r < R; r++)
+                if (r < n_cur) part[((size_t)(lr + r) * T + tile) * 32 + lane] = lx.unit(cur[r]);
 #pragma unroll
             for (int r = 0; r < R; r++) cur[r] = nxt[r];
+            u = u2; lr = lr2; tile = tile2; n_cur = n_nxt;
         }
         __syncthreads();
 
         /* fold the tiles of one row in ascending order, merge lanes, finish */
-        auto fold_row = [&](int lr) -> float {
+        auto fold_row = [&](int l) -> float {
             float acc = 0.f;
-            const float* pr = part + (size_t)lr * T * 32 + lane;
+            const float* pr = part + (size_t)l * T * 32 + lane;
             if (WK == WK_INT8_CH) {
                 for (int i = 0; i < T; i++) acc += pr[i * 32];
             } else {
-                const __half* sr = sc_s + (size_t)lr * sc_per_row;
+                const __half* sr = sc_s + (size_t)l * sc_per_row;
                 for (int i = 0; i < T; i++)
                     acc = __fmaf_rn(pr[i * 32], __half2float(sr[(i * 512 + lane * 16) >> g.gshift]), acc);
             }
             acc = warp_tree_sum(acc);
-            if (WK == WK_INT8_CH) acc = __fmul_rn(acc, static_cast<const float*>(g.scales)[global_row(lr)]);
+            if (WK == WK_INT8_CH) acc = __fmul_rn(acc, static_cast<const float*>(g.scales)[global_row(l)]);
             return acc;
         };
 
@@ -300,19 +350,19 @@ __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsi
                     const __nv_bfloat16 yb = f2bf(acc);
                     if (EPI == EPI_RESID) {
                         const __nv_bfloat16* src = g.resid_src;
-                        if (g.resid_index) src += (size_t)(*g.resid_index) * g.N;
-                        else if (g.resid_key) src += (size_t)key_index(*g.resid_key) * g.N;
-                        g.y[n] = f2bf(__fadd_rn(bf2f(src[n]), bf2f(yb)));
+                        if (g.resid_index) src += (size_t)__ldcg(g.resid_index) * g.N;
+                        else if (g.resid_key) src += (size_t)key_index(__ldcg(g.resid_key)) * g.N;
+                        g.y[n] = f2bf(__fadd_rn(ldcg_bf16(src + n), bf2f(yb)));
                     } else {
                         g.y[n] = yb;
                     }
                     if (EPI == EPI_ARGMAX) {
                         /* order-preserving key: larger value first, then lower index
                          * (src/slowar/kernels.cu:1326-1357); -0 counts as +0 */
-                        uint32_t u = __float_as_uint(bf2f(yb));
-                        if (u == 0x80000000u) u = 0u;
-                        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-                        const unsigned long long key = ((unsigned long long)u << 32) | (0xFFFFFFFFu - (uint32_t)n);
+                        uint32_t uu = __float_as_uint(bf2f(yb));
+                        if (uu == 0x80000000u) uu = 0u;
+                        uu = (uu & 0x80000000u) ? ~uu : (uu | 0x80000000u);
+                        const unsigned long long key = ((unsigned long long)uu << 32) | (0xFFFFFFFFu - (uint32_t)n);
                         best = key > best ? key : best;
                     }
                 }
@@ -321,6 +371,14 @@ __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsi
         __syncthreads(); /* partials and scales are overwritten by the next pass */
     }
     if (EPI == EPI_ARGMAX && lane == 0 && best) atomicMax(g.argmax_key, best);
+}
+
+/* rows of the stage owned by CTA `cta` of `n_cta` */
+template <int EPI>
+__device__ __forceinline__ void gemv_cta_rows(const GemvStage& g, int cta, int n_cta, int& row0, int& cnt) {
+    const int units = (EPI == EPI_SWIGLU) ? (g.N >> 1) : g.N;
+    row0 = (int)((long long)units * cta / n_cta);
+    cnt = (int)((long long)units * (cta + 1) / n_cta) - row0;
 }
 
 }  // namespace s2p
