@@ -28,9 +28,20 @@ typedef struct {
     size_t download_bytes;          /* device->host bytes per tick */
     double weight_bytes_per_frame;  /* quantised weight + scale bytes one batch-1 frame streams */
     double kv_bytes_per_token;      /* KV bytes one session reads per cached token per frame */
+    int last_tick_persistent;       /* 1 = the whole tick ran as one persistent cooperative kernel */
 } s2p_b200_stats;
 
 s2p_status s2p_b200_model_stats(const s2p_model* m, s2p_b200_stats* out);
+
+/* Stage trace of the persistent tick kernel (no counterpart in the reference).  With
+ * S2P_TICK_TRACE=1 in the environment at model load, CTA 0 of every persistent tick
+ * stamps the SM clock at four points of each stage: stage entered, activation staged
+ * (GEMV stages; 0 otherwise), own work done, grid barrier passed.  This call copies the
+ * stamps of the most recent tick: out[4 * stage + point], types[stage] = stage kind
+ * (0 frame start, 1 GEMV, 2 backbone attention, 3 fast-AR attention, 4 sampler, 5 frame
+ * end).  *n_stages receives the stage count; at most max_stages are written.
+ * S2P_ERR_STATE if tracing is off or no persistent tick has run. */
+s2p_status s2p_b200_model_tick_trace(s2p_model* m, uint64_t* out, int32_t* types, int max_stages, int* n_stages);
 /* The stream every tick of this model is issued on (for external event timing). */
 cudaStream_t s2p_b200_model_stream(s2p_model* m);
 

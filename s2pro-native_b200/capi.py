@@ -118,13 +118,15 @@ class Stats(C.Structure):
     _fields_ = [("frames_decoded", C.c_uint64), ("n_slow_layers", C.c_int), ("last_tick_rows", C.c_int),
                 ("last_tick_fused", C.c_int), ("last_tick_graph", C.c_int), ("last_tick_kernels", C.c_int),
                 ("last_tick_device_ms", C.c_float), ("upload_bytes", C.c_size_t), ("download_bytes", C.c_size_t),
-                ("weight_bytes_per_frame", C.c_double), ("kv_bytes_per_token", C.c_double)]
+                ("weight_bytes_per_frame", C.c_double), ("kv_bytes_per_token", C.c_double),
+                ("last_tick_persistent", C.c_int)]
 
 
 EXT_PROTOTYPES = {
     "s2p_b200_version": (C.c_char_p, []),
     "s2p_b200_model_stats": (_I, [_P, C.POINTER(Stats)]),
     "s2p_b200_model_stream": (C.c_void_p, [_P]),
+    "s2p_b200_model_tick_trace": (_I, [_P, _P, _P, _I, C.POINTER(C.c_int)]),
     "s2p_b200_attention_decode_noalloc": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _S]),
 }
 

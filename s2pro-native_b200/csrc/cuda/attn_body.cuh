@@ -1,0 +1,242 @@
+/* Device body of the split-K decode attention (see attn.cu for the arithmetic
+ * contract), callable from a stand-alone kernel (one CTA per (row, kv head,
+ * worker)) and from the persistent tick kernel.  512 threads.  Everything
+ * another SM may have produced earlier in the same kernel (the qkv projection,
+ * the per-split partials) is read with L1-bypassing loads. */
+#pragma once
+#include <math.h>
+#include "common.cuh"
+#include "headops.cuh"
+#include "ops.h"
+#include "attn.cuh"
+
+namespace s2p {
+
+template <bool KV8> struct AttnSmem {
+    static constexpr int VB = KV8 ? 128 : 256; /* payload bytes per cached vector */
+    static constexpr int TS = VB + 4;          /* staged row stride (skewed) */
+    alignas(16) unsigned char tile[64 * TS];   /* K rows of the split */
+    alignas(16) unsigned char vtile[64 * TS];  /* V rows of the split */
+    alignas(8) __half ssc[64 * 4];             /* their group scales (INT8 cache) */
+    alignas(8) __half vssc[64 * 4];
+    float sq[4][128];
+    float sc[4][64];
+    float red[4][128];
+    float hm[4], hs[4];
+    int s_last;
+};
+
+__device__ __forceinline__ float ldcg_bf(const __nv_bfloat16* p) {
+    return bf_bits_to_f32(__ldcg(reinterpret_cast<const unsigned short*>(p)));
+}
+
+template <bool KV8, bool PREP>
+__device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, int kvh, int wk, int workers,
+                                AttnSmem<KV8>& sm) {
+    constexpr int VB = AttnSmem<KV8>::VB;
+    constexpr int TS = AttnSmem<KV8>::TS;
+
+    unsigned char* tile = sm.tile;
+    unsigned char* vtile = sm.vtile;
+    __half* ssc = sm.ssc;
+    __half* vssc = sm.vssc;
+    float (*sq)[128] = sm.sq;
+    float (*sc)[64] = sm.sc;
+    float (*red)[128] = sm.red;
+    float* hm = sm.hm;
+    float* hs = sm.hs;
+    const int tid = threadIdx.x;
+    const int QH = a.q_heads, KVH = a.kv_heads;
+    const int pos = a.pos_arr ? __ldcg(a.pos_arr + row) : a.pos0 + row * a.pos_row_step;
+    const int len = pos + 1;
+    const int n_active = (len + 63) >> 6;
+    const size_t plane = (size_t)kvh * a.max_seq;
+    unsigned char* kc = kv_payload(a.kv, row) + a.kv.k_off;
+    unsigned char* vc = kv_payload(a.kv, row) + a.kv.v_off;
+    __half* ks = KV8 ? reinterpret_cast<__half*>(kv_scales(a.kv, row) + a.kv.ks_off) : nullptr;
+    __half* vs = KV8 ? reinterpret_cast<__half*>(kv_scales(a.kv, row) + a.kv.vs_off) : nullptr;
+    const float scale = rsqrtf(128.0f);
+
+    /* Start the copies of a split's K and V rows (and scales) into shared memory; they run
+     * while the caller does something else.  `skip` (or -1): a row the caller writes itself. */
+    auto fetch_split = [&](int spl, int skip) {
+        const int start = spl << 6;
+        const int cnt = min(64, len - start);
+        for (int i = tid; i < cnt * (VB / 4); i += 512) {
+            const int rr = i / (VB / 4), cw = i - rr * (VB / 4);
+            if (start + rr == skip) continue;
+            const size_t off = (plane + start + rr) * VB + cw * 4;
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(tile + rr * TS + cw * 4)), "l"(kc + off) : "memory");
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(vtile + rr * TS + cw * 4)), "l"(vc + off) : "memory");
+        }
+        if (KV8)
+            for (int rr = tid; rr < cnt; rr += 512) {
+                if (start + rr == skip) continue;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(ssc + rr * 4)), "l"(ks + (plane + start + rr) * 4) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((uint32_t)__cvta_generic_to_shared(vssc + rr * 4)), "l"(vs + (plane + start + rr) * 4) : "memory");
+            }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    /* the first split of this worker is on its way before the query is prepared; the new
+     * position's row, if it falls into that split, is written below by this CTA itself */
+    const bool pre_has_new = PREP && wk == n_active - 1;
+    if (wk < n_active) fetch_split(wk, pre_has_new ? pos : -1);
+
+    {   /* queries of the four heads sharing this kv head, pre-scaled */
+        const int g = tid >> 7, t = tid & 127;
+        const int h = kvh * 4 + g;
+        float v;
+        if (PREP) {
+            v = ldcg_bf(pz.qkv + (size_t)row * (QH + 2 * KVH) * 128 + (size_t)h * 128 + t);
+            if (pz.q_norm) {
+                const float tot = head_tree_sum(__fmaf_rn(v, v, 0.f), red, g, t);
+                const float inv = rsqrtf(__fdiv_rn(tot, 128.0f) + pz.eps);
+                v = bf16_round(__fmul_rn(__fmul_rn(v, inv), bf2f(pz.q_norm[t])));
+            }
+            float c, s;
+            rope_cs(t >> 1, pos, pz.rope_base, c, s);
+            const float other = __shfl_xor_sync(S2P_FULL_MASK, v, 1);
+            v = rope_elem(t, v, other, c, s);
+        } else {
+            v = ldcg_bf(a.q + ((size_t)row * QH + h) * 128 + t);
+        }
+        sq[g][t] = __fmul_rn(v, scale);
+    }
+    if (PREP) {
+        /* the worker that owns the split holding the new position appends k and v */
+        const bool owner = ((n_active - 1) % workers) == wk;
+        if (owner) { /* uniform over the CTA */
+            const int g = tid >> 7, t = tid & 127; /* g 0: k, g 1: v, g 2,3 idle but join the barriers */
+            const size_t src = (size_t)row * (QH + 2 * KVH) * 128 + (size_t)(QH + (g == 1 ? KVH : 0) + kvh) * 128 + t;
+            float v = ldcg_bf(pz.qkv + (g < 2 ? src : 0));
+            if (pz.k_norm) { /* uniform */
+                const float tot = head_tree_sum(__fmaf_rn(v, v, 0.f), red, g, t);
+                if (g == 0) {
+                    const float inv = rsqrtf(__fdiv_rn(tot, 128.0f) + pz.eps);
+                    v = bf16_round(__fmul_rn(__fmul_rn(v, inv), bf2f(pz.k_norm[t])));
+                }
+            }
+            if (g == 0) {
+                float c, s;
+                rope_cs(t >> 1, pos, pz.rope_base, c, s);
+                const float other = __shfl_xor_sync(S2P_FULL_MASK, v, 1);
+                v = rope_elem(t, v, other, c, s);
+            }
+            if (g < 2) {
+                unsigned char* cache = g == 0 ? kc : vc;
+                const size_t vec = plane + pos;
+                unsigned char* trow = (g == 0 ? tile : vtile) + (pos & 63) * TS; /* its row of the staged split */
+                if (!KV8) {
+                    const __nv_bfloat16 vb = f2bf(v);
+                    reinterpret_cast<__nv_bfloat16*>(cache)[vec * 128 + t] = vb;
+                    if (pre_has_new) reinterpret_cast<__nv_bfloat16*>(trow)[t] = vb;
+                } else {
+                    __half hsc;
+                    const int8_t q8 = kv8_quant(v, hsc);
+                    reinterpret_cast<int8_t*>(cache)[vec * 128 + t] = q8;
+                    if (pre_has_new) reinterpret_cast<int8_t*>(trow)[t] = q8;
+                    if ((t & 31) == 0) {
+                        (g == 0 ? ks : vs)[vec * 4 + (t >> 5)] = hsc;
+                        if (pre_has_new) (g == 0 ? ssc : vssc)[(pos & 63) * 4 + (t >> 5)] = hsc;
+                    }
+                }
+            }
+        }
+    }
+    S2P_CTA_SYNC();
+
+    for (int spl = wk; spl < n_active; spl += workers) {
+        const int start = spl << 6;
+        const int cnt = min(64, len - start);
+        if (spl != wk) fetch_split(spl, -1); /* later splits: this CTA's own append, if any, is already visible */
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        S2P_CTA_SYNC();
+
+        /* scores: thread (head g4, position t4), one chain each */
+        const int g4 = (tid >> 6) & 3, t4 = tid & 63;
+        float d = -INFINITY;
+        if (tid < 256 && t4 < cnt) {
+            d = 0.f;
+            if (!KV8) {
+                const __nv_bfloat162* kr = reinterpret_cast<const __nv_bfloat162*>(tile + t4 * TS);
+#pragma unroll 8
+                for (int e = 0; e < 64; e++) {
+                    const float2 kf = __bfloat1622float2(kr[e]);
+                    d = __fmaf_rn(sq[g4][2 * e], kf.x, d);
+                    d = __fmaf_rn(sq[g4][2 * e + 1], kf.y, d);
+                }
+            } else {
+                const int8_t* kr = reinterpret_cast<const int8_t*>(tile + t4 * TS);
+#pragma unroll
+                for (int gi = 0; gi < 4; gi++) {
+                    float pp = 0.f;
+#pragma unroll 8
+                    for (int e = 0; e < 32; e++) pp = __fmaf_rn(sq[g4][gi * 32 + e], (float)kr[gi * 32 + e], pp);
+                    d = __fmaf_rn(pp, __half2float(ssc[t4 * 4 + gi]), d);
+                }
+            }
+        }
+        if (tid < 256) { /* split max per head: two warps of 32 slots each */
+            const float mx = warp_tree_max(d);
+            if ((tid & 31) == 0) red[0][tid >> 5] = mx;
+        }
+        S2P_CTA_SYNC();
+        float m = 0.f;
+        if (tid < 256) {
+            m = fmaxf(red[0][2 * g4], red[0][2 * g4 + 1]);
+            sc[g4][t4] = (t4 < cnt) ? expf(d - m) : 0.f;
+        }
+        S2P_CTA_SYNC();
+        if (tid < 256 && t4 < 32) { /* exp-sum: pairs (t, t+32), then 16..1 */
+            const float x = warp_tree_sum(sc[g4][t4] + sc[g4][t4 + 32]);
+            if (t4 == 0) { hm[g4] = m; hs[g4] = x; }
+        }
+        S2P_CTA_SYNC();
+        {
+            const int g = tid >> 7, dd = tid & 127;
+            float acc = 0.f;
+            if (!KV8) {
+                for (int j = 0; j < cnt; j++)
+                    acc = __fmaf_rn(sc[g][j], bf2f(reinterpret_cast<const __nv_bfloat16*>(vtile + j * TS)[dd]), acc);
+            } else {
+                for (int j = 0; j < cnt; j++)
+                    acc = __fmaf_rn(__fmul_rn(sc[g][j], __half2float(vssc[j * 4 + (dd >> 5)])),
+                                    (float)reinterpret_cast<const int8_t*>(vtile + j * TS)[dd], acc);
+            }
+            float* ph = a.part + (((size_t)row * QH + kvh * 4 + g) * a.n_split_slots + spl) * 130;
+            if (dd == 0) { ph[0] = hm[g]; ph[1] = hs[g]; }
+            ph[2 + dd] = acc;
+        }
+        S2P_CTA_SYNC(); /* tile, sc, hm/hs are rewritten by the next split */
+    }
+
+    /* the last worker of this (row, kv head) to finish merges the partials */
+    __threadfence();
+    S2P_CTA_SYNC();
+    unsigned int* ctr = a.counters + (size_t)row * KVH + kvh;
+    if (tid == 0) sm.s_last = (atomicAdd(ctr, 1u) == (unsigned)(workers - 1));
+    S2P_CTA_SYNC();
+    const bool last = sm.s_last != 0;
+    if (last) {
+        __threadfence();
+        const int g = tid >> 7, dd = tid & 127, h = kvh * 4 + g;
+        const float* pb = a.part + ((size_t)row * QH + h) * a.n_split_slots * 130;
+        float M = -INFINITY;
+        for (int s = 0; s < n_active; s++) M = fmaxf(M, __ldcg(pb + (size_t)s * 130));
+        float l = 0.f, acc = 0.f;
+        for (int s = 0; s < n_active; s++) {
+            const float* ph = pb + (size_t)s * 130;
+            const float ls = __ldcg(ph + 1);
+            if (ls == 0.f) continue;
+            const float w = expf(__ldcg(ph) - M);
+            l = __fmaf_rn(ls, w, l);
+            acc = __fmaf_rn(__ldcg(ph + 2 + dd), w, acc);
+        }
+        a.out[((size_t)row * QH + h) * 128 + dd] = f2bf(__fdiv_rn(acc, l));
+    }
+    if (last && tid == 0) *ctr = 0u;
+    S2P_CTA_SYNC(); /* the shared block may be reused by the caller right away */
+}
+
+
+}  // namespace s2p

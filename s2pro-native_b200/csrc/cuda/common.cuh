@@ -15,6 +15,13 @@
 
 #define S2P_FULL_MASK 0xffffffffu
 
+/* Barrier over the threads that run the device bodies in these headers.  A kernel
+ * whose CTA also holds threads outside that group (the copy-issuing warp of the
+ * persistent tick kernel) defines it as a named barrier before including them. */
+#ifndef S2P_CTA_SYNC
+#define S2P_CTA_SYNC() __syncthreads()
+#endif
+
 __device__ __forceinline__ float bf_bits_to_f32(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
 __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ __nv_bfloat16 f2bf(float v) { return __float2bfloat16(v); } /* RNE */
@@ -40,21 +47,40 @@ template <int T, bool IS_MAX>
 __device__ __forceinline__ float block_tree(float v, float* red) {
     const int t = threadIdx.x;
     if (t < T) red[t] = v;
-    __syncthreads();
+    S2P_CTA_SYNC();
 #pragma unroll
     for (int off = T >> 1; off >= 32; off >>= 1) {
         if (t < off) red[t] = IS_MAX ? fmaxf(red[t], red[t + off]) : red[t] + red[t + off];
-        __syncthreads();
+        S2P_CTA_SYNC();
     }
     if (t < 32) {
         float r = red[t];
         r = IS_MAX ? warp_tree_max(r) : warp_tree_sum(r);
         if (t == 0) red[0] = r;
     }
-    __syncthreads();
+    S2P_CTA_SYNC();
     const float out = red[0];
-    __syncthreads(); /* red may be reused by the caller right away */
+    S2P_CTA_SYNC(); /* red may be reused by the caller right away */
     return out;
+}
+
+/* The 256-value halving sum tree with two barriers instead of six: warp 0 forms the
+ * pairs of the levels 128, 64 and 32 itself (lane t holds the values t + 32 j),
+ * then the shuffle levels.  Same pairs as block_tree<256, false>, same result.
+ * Thread t < 256 contributes v; `red` needs 256 floats and must not be written
+ * again before the caller's next barrier.  All threads of the group must call it. */
+__device__ __forceinline__ float tree256_sum(float v, float* red) {
+    const int t = threadIdx.x;
+    if (t < 256) red[t] = v;
+    S2P_CTA_SYNC();
+    if (t < 32) {
+        const float a0 = red[t] + red[t + 128], a1 = red[t + 32] + red[t + 160];
+        const float a2 = red[t + 64] + red[t + 192], a3 = red[t + 96] + red[t + 224];
+        const float r = warp_tree_sum((a0 + a2) + (a1 + a3));
+        if (t == 0) red[256] = r;
+    }
+    S2P_CTA_SYNC();
+    return red[256];
 }
 
 /* Bytes of an int8x4 word (biased by 128) or nibbles of an int4x8 word (biased

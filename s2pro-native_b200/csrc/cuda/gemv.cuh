@@ -82,7 +82,7 @@ __host__ __device__ inline size_t gemv_smem_bytes(int wk, int rows_local, int K,
     size_t b = gemv_x_bytes(wk, K);
     b += (size_t)rows_local * T * 32 * sizeof(float);   /* per-tile lane partials */
     if (wk != WK_INT8_CH) b += ((size_t)rows_local * (K >> gshift) * 2 + 15) & ~(size_t)15;
-    return b + 1024 /* reduction scratch */;
+    return b + 2048 /* reduction scratch */;
 }
 
 /* index held in a packed arg-max key (see EPI_ARGMAX) */
@@ -170,44 +170,89 @@ template <> struct LaneX<WK_INT8_CH> {
 };
 template <> struct LaneX<WK_INT8_GRP> : LaneX<WK_INT8_CH> {};
 
-/* write activation k (already rounded to bf16, given as f32) into the staging area */
+/* ---- the staged activation vector -------------------------------------------
+ * Element k = 512 i + 16 l + j sits where lane l reads it for tile i: INT4 keeps
+ * bf16, eight to a uint4 at index (i*2 + (j>>3))*32 + l; INT8 keeps f32, four to a
+ * float4 at index (i*4 + (j>>2))*32 + l.  Eight consecutive k (one 16-byte vector
+ * of the source) therefore land in one uint4 or two float4. */
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
 template <int WK>
-__device__ __forceinline__ void xs_store(unsigned char* xs, int k, float v) {
-    const int i = k >> 9, l = (k >> 4) & 31, j = k & 15;
+__device__ __forceinline__ void xs_store_vec8(unsigned char* xs, int v, const uint4& q) {
+    const int i = v >> 6, l = (v >> 1) & 31, h = v & 1;
     if (WK == WK_INT4_PACK) {
-        reinterpret_cast<unsigned short*>(xs)[(((i * 2 + (j >> 3)) * 32 + l) << 3) + (j & 7)] =
-            (unsigned short)(__float_as_uint(v) >> 16);
+        reinterpret_cast<uint4*>(xs)[(i * 2 + h) * 32 + l] = q;
     } else {
-        reinterpret_cast<float*>(xs)[(((i * 4 + (j >> 2)) * 32 + l) << 2) + (j & 3)] = v;
+        float4* p = reinterpret_cast<float4*>(xs) + (i * 4 + h * 2) * 32 + l;
+        p[0] = make_float4(bf_lo(q.x), bf_hi(q.x), bf_lo(q.y), bf_hi(q.y));
+        p[32] = make_float4(bf_lo(q.z), bf_hi(q.z), bf_lo(q.w), bf_hi(q.w));
     }
 }
+template <int WK>
+__device__ __forceinline__ float xs_load(const unsigned char* xs, int k) {
+    const int i = k >> 9, l = (k >> 4) & 31, j = k & 15;
+    if (WK == WK_INT4_PACK)
+        return bf_bits_to_f32(reinterpret_cast<const unsigned short*>(xs)[(((i * 2 + (j >> 3)) * 32 + l) << 3) + (j & 7)]);
+    return reinterpret_cast<const float*>(xs)[(((i * 4 + (j >> 2)) * 32 + l) << 2) + (j & 3)];
+}
 
-/* ---- prologue: stage the activation vector ------------------------------- */
+/* ---- prologue: stage the activation vector -------------------------------
+ * `nthreads` threads (threadIdx.x < nthreads, a multiple of 32, >= 256) call this
+ * together.  x, norm_w and normed_out must be 16-byte aligned.  `red`: 257 floats. */
+__device__ __forceinline__ uint4 norm_vec8(const uint4& xq, const uint4& wq, float inv) {
+    const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w};
+    const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const __nv_bfloat16 lo = f2bf(__fmul_rn(__fmul_rn(bf_lo(xw[c]), inv), bf_lo(ww[c])));
+        const __nv_bfloat16 hi = f2bf(__fmul_rn(__fmul_rn(bf_hi(xw[c]), inv), bf_hi(ww[c])));
+        o[c] = (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 template <int WK, int PRO>
-__device__ __forceinline__ void stage_activation(const GemvStage& g, unsigned char* xs, float* red) {
-    const int K = g.K;
+__device__ __forceinline__ void stage_activation(const GemvStage& g, unsigned char* xs, float* red, int nthreads) {
+    const int K = g.K, NVEC = K >> 3;
     const __nv_bfloat16* x = g.x;
     if (g.x_index) x += (size_t)__ldcg(g.x_index) * K;
     else if (g.x_key) x += (size_t)key_index(__ldcg(g.x_key)) * K;
-    if (PRO == PRO_VEC) {
-        for (int k = threadIdx.x; k < K; k += blockDim.x) xs_store<WK>(xs, k, ldcg_bf16(x + k));
-    } else {
-        /* 256 strided partial sums of squares, halving tree, rsqrtf(mean + eps):
-         * src/slowar/kernels.cu:46-68 */
-        float ss = 0.f;
-        if (threadIdx.x < 256)
-            for (int i = threadIdx.x; i < K; i += 256) {
-                const float v = ldcg_bf16(x + i);
-                ss = __fmaf_rn(v, v, ss);
-            }
-        const float tot = block_tree<256, false>(ss, red);
-        const float inv = rsqrtf(__fdiv_rn(tot, (float)K) + g.eps);
-        const bool emit = g.normed_out != nullptr && blockIdx.x == 0;
-        for (int k = threadIdx.x; k < K; k += blockDim.x) {
-            const __nv_bfloat16 nb = f2bf(__fmul_rn(__fmul_rn(ldcg_bf16(x + k), inv), bf2f(g.norm_w[k])));
-            xs_store<WK>(xs, k, bf2f(nb));
-            if (emit) g.normed_out[k] = nb;
+    const uint4* xsrc = reinterpret_cast<const uint4*>(x);
+    const uint4* wsrc = reinterpret_cast<const uint4*>(g.norm_w);
+    /* the first vector of a thread stays in registers for the normalisation (the model's
+     * normed widths need no more than one per thread) */
+    const int v0 = threadIdx.x;
+    uint4 x0 = make_uint4(0, 0, 0, 0), w0 = x0;
+    if (v0 < NVEC) {
+        x0 = __ldcg(xsrc + v0);
+        if (PRO == PRO_NORM) w0 = wsrc[v0];
+        xs_store_vec8<WK>(xs, v0, x0);
+    }
+    for (int v = v0 + nthreads; v < NVEC; v += nthreads) xs_store_vec8<WK>(xs, v, __ldcg(xsrc + v));
+    if (PRO == PRO_VEC) return;
+    S2P_CTA_SYNC();
+    /* 256 strided partial sums of squares, halving tree, rsqrtf(mean + eps):
+     * src/slowar/kernels.cu:46-68 */
+    float ss = 0.f;
+    if (threadIdx.x < 256)
+        for (int i = threadIdx.x; i < K; i += 256) {
+            const float v = xs_load<WK>(xs, i);
+            ss = __fmaf_rn(v, v, ss);
         }
+    const float tot = tree256_sum(ss, red); /* its first barrier also orders the reads above before the rewrite below */
+    const float inv = rsqrtf(__fdiv_rn(tot, (float)K) + g.eps);
+    const bool emit = g.normed_out != nullptr && blockIdx.x == 0;
+    if (v0 < NVEC) {
+        const uint4 q = norm_vec8(x0, w0, inv);
+        xs_store_vec8<WK>(xs, v0, q);
+        if (emit) reinterpret_cast<uint4*>(g.normed_out)[v0] = q;
+    }
+    for (int v = v0 + nthreads; v < NVEC; v += nthreads) {
+        const uint4 q = norm_vec8(__ldcg(xsrc + v), wsrc[v], inv);
+        xs_store_vec8<WK>(xs, v, q);
+        if (emit) reinterpret_cast<uint4*>(g.normed_out)[v] = q;
     }
 }
 
@@ -294,8 +339,8 @@ __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsi
                 sc_s[idx] = sg[(size_t)global_row(l) * sc_per_row + c];
             }
         }
-        if (done == 0) stage_activation<WK, PRO>(g, xs, red);
-        __syncthreads();
+        if (done == 0) stage_activation<WK, PRO>(g, xs, red, GEMV_THREADS);
+        S2P_CTA_SYNC();
 
         LaneX<WK> lx;
         int x_tile = -1;
@@ -313,7 +358,7 @@ __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsi
             for (int r = 0; r < R; r++) cur[r] = nxt[r];
             u = u2; lr = lr2; tile = tile2; n_cur = n_nxt;
         }
-        __syncthreads();
+        S2P_CTA_SYNC();
 
         /* fold the tiles of one row in ascending order, merge lanes, finish */
         auto fold_row = [&](int l) -> float {
@@ -368,7 +413,7 @@ __device__ void gemv_stage_cta(const GemvStage& g, int row0, int cnt_total, unsi
                 }
             }
         }
-        __syncthreads(); /* partials and scales are overwritten by the next pass */
+        S2P_CTA_SYNC(); /* partials and scales are overwritten by the next pass */
     }
     if (EPI == EPI_ARGMAX && lane == 0 && best) atomicMax(g.argmax_key, best);
 }

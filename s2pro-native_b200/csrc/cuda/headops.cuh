@@ -37,13 +37,13 @@ __device__ __forceinline__ int8_t kv8_quant(float xv, __half& hsc_out) {
  * side (thread = g*128 + t).  red: [G][128] floats.  All threads must call. */
 __device__ __forceinline__ float head_tree_sum(float v, float (*red)[128], int g, int t) {
     red[g][t] = v;
-    __syncthreads();
+    S2P_CTA_SYNC();
     if (t < 64) red[g][t] += red[g][t + 64];
-    __syncthreads();
+    S2P_CTA_SYNC();
     if (t < 32) red[g][t] += red[g][t + 32];
-    __syncthreads();
+    S2P_CTA_SYNC();
     const float r = warp_tree_sum(red[g][t & 31]);
-    __syncthreads();
+    S2P_CTA_SYNC();
     return r;
 }
 

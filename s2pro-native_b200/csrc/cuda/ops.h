@@ -120,6 +120,94 @@ cudaError_t tick_finish_keys(const unsigned long long* keys, int rows, int32_t* 
 
 cudaError_t gemv_setup_all(void); /* once per device, before any stream capture */
 
+/* ---- persistent batch-1 decode tick (mega.cu) --------------------------------
+ * The whole frame is one cooperative kernel that walks a list of stages; a grid
+ * barrier separates stages unless MEGA_NO_BARRIER is set on the earlier one. */
+enum { MEGA_BEGIN = 0, MEGA_GEMV = 1, MEGA_ATTN_SLOW = 2, MEGA_ATTN_FAST = 3, MEGA_SAMPLE = 4, MEGA_FINISH = 5 };
+#define MEGA_NO_BARRIER 1
+typedef struct {
+    int type, flags;
+    /* MEGA_GEMV: y = epilogue(W * prologue(x)) */
+    LinRef lin;
+    int pro, epi;                 /* Prologue / Epilogue of gemv.cuh */
+    VecRef x;
+    const s2p_dev_bf16* norm_w;
+    s2p_dev_bf16* y;
+    VecRef resid;
+    unsigned long long* key;
+    s2p_dev_bf16* normed_out;
+    int rows_per_chunk;           /* rows (row pairs with the SwiGLU epilogue) one ring slot holds */
+    /* MEGA_ATTN_*: raw qkv in, attention output out */
+    const s2p_dev_bf16* qkv;
+    const s2p_dev_bf16* q_norm;
+    const s2p_dev_bf16* k_norm;
+    s2p_dev_bf16* out;
+    KvRef kv;
+    int pos;                      /* MEGA_ATTN_FAST: position in the fast-AR cache (= pass index) */
+} MegaStage;
+
+/* Ring geometry shared by the kernel and the host code that builds the copy commands. */
+#define MEGA_RING_SLOTS 6
+#define MEGA_RING_SLOT_BYTES 24576
+#define MEGA_PARTIAL_BYTES 10240
+
+/* One chunk of weights for the ring: up to four 1-D bulk copies (weight rows and group
+ * scales, each for the gate and the up half of a SwiGLU stage) into one slot. */
+typedef struct {
+    unsigned long long src[4];
+    unsigned int bytes[4];    /* 0 = unused; multiples of 16 */
+    unsigned int dst_off[4];  /* byte offset inside the slot; multiples of 16 */
+} MegaCopyCmd;
+
+/* Rows [row0, row0 + cnt) of a stage's N rows (row pairs with the SwiGLU epilogue) belong
+ * to CTA `cta` of `n_cta`; they are cut into n_chunks chunks of rc rows (the last may be
+ * shorter), rc <= rows_per_chunk. */
+typedef struct { int row0, cnt, rc, n_chunks; } MegaGeom;
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+static inline MegaGeom mega_stage_geom(int N, int swiglu, int rows_per_chunk, int cta, int n_cta) {
+    MegaGeom g;
+    const int units = swiglu ? (N >> 1) : N;
+    g.row0 = (int)((long long)units * cta / n_cta);
+    g.cnt = (int)((long long)units * (cta + 1) / n_cta) - g.row0;
+    g.n_chunks = g.cnt > 0 ? (g.cnt + rows_per_chunk - 1) / rows_per_chunk : 0;
+    g.rc = g.n_chunks ? (g.cnt + g.n_chunks - 1) / g.n_chunks : 0;
+    return g;
+}
+
+typedef struct {
+    const MegaStage* stages;      /* device memory */
+    int n_stages;
+    const MegaCopyCmd* cmds;      /* device memory: every CTA's copy commands in program order */
+    const int* cmd_start;         /* [n_cta + 1] first command of each CTA */
+    unsigned int* barrier;        /* device word, zero at launch */
+    int* status;                  /* device word, zero at launch; non-zero afterwards = a bounded wait gave up */
+    TickBeginArgs begin;
+    /* slow-AR attention */
+    int ctx_len, kv8, n_split_slots;
+    const int32_t* pos_arr;
+    float* part;
+    unsigned int* counters;
+    float eps, rope_base;
+    int head_dim;
+    /* sampler */
+    const s2p_dev_bf16* sem_logits; const s2p_dev_bf16* eos_logit;
+    SamplerState* const* states;
+    int64_t* out_tok; int32_t* out_sem; int32_t* out_codes; uint8_t* out_eos;
+    const unsigned long long* keys; /* [9] arg-max keys of the fast-AR steps */
+    /* optional per-stage SM-clock stamps of CTA 0: [n_stages][4] = stage entered, activation
+     * staged (GEMV), work done, barrier passed */
+    unsigned long long* trace;
+} MegaParams;
+
+/* bytes of one ring slot; a stage's rows_per_chunk must satisfy
+ * rows * regions * (row bytes + scale bytes per row) <= this */
+int mega_slot_bytes(void);
+int mega_max_local_rows(int K, int kind); /* rows whose per-tile partials fit the shared partial buffer */
+cudaError_t mega_setup(int* n_cta_out);   /* once per device: attribute + occupancy check; grid size */
+cudaError_t mega_launch(const MegaParams* p, int n_cta, cudaStream_t st);
+
 cudaError_t qkv_post(const QkvPostArgs* a, int rows, cudaStream_t st);
 cudaError_t attn_single(const AttnArgs* a, int rows, cudaStream_t st);
 cudaError_t attn_decode(const AttnArgs* a, int rows, cudaStream_t st);

@@ -12,8 +12,8 @@ namespace s2p {
 
 enum PipeError { PIPE_OK = 0, PIPE_ERR_TMA_WAIT = 1, PIPE_ERR_GRID_BARRIER = 2 };
 
-constexpr unsigned PIPE_MBAR_TRIES = 1u << 22;   /* each try_wait already blocks for a hardware time slice */
-constexpr unsigned PIPE_GRID_SPINS = 1u << 24;   /* ~1 s of polling an L2 word */
+constexpr unsigned PIPE_MBAR_TRIES = 1u << 20;   /* each try_wait already blocks for a hardware time slice */
+constexpr unsigned PIPE_GRID_SPINS = 1u << 22;   /* a few seconds of polling an L2 word */
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -40,6 +40,12 @@ __device__ __forceinline__ void tma_load_1d(void* dst, const void* src, unsigned
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+/* orders this thread's earlier generic-proxy accesses to shared memory (and those it
+ * has synchronised with) before its later async-proxy (bulk copy) writes */
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ int status_peek(const int* status) { return *reinterpret_cast<const volatile int*>(status); }
 
 /* Wait for phase `parity` of an mbarrier; false (and status set) on time-out or when
@@ -58,20 +64,21 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
  * when it reaches k * n_cta.  Called by every thread of the CTA. */
 __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int* status) {
     __shared__ int ok_s;
-    __syncthreads();
+    S2P_CTA_SYNC();
     if (threadIdx.x == 0) {
         int ok = 1;
-        __threadfence(); /* publish this CTA's stores before arriving */
-        atomicAdd(counter, 1u);
-        unsigned spins = 0;
-        while (*reinterpret_cast<volatile unsigned*>(counter) < target) {
+        /* release: publishes this CTA's stores (ordered before it by the CTA barrier above) */
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+        unsigned spins = 0, seen;
+        for (;;) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            if (seen >= target) break;
             if (++spins > PIPE_GRID_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_GRID_BARRIER); ok = 0; break; }
             if ((spins & 255u) == 0u && status_peek(status) != PIPE_OK) { ok = 0; break; }
         }
-        __threadfence();
         ok_s = ok && status_peek(status) == PIPE_OK;
     }
-    __syncthreads();
+    S2P_CTA_SYNC();
     return ok_s != 0;
 }
 

@@ -38,6 +38,15 @@ struct s2p_model {
     int n_slow;        /* backbone layers found in the checkpoint (<= S2P_SLOW_LAYERS) */
     int scratch_rows;  /* prefill row capacity */
     int fused_b1;      /* batch-1 fused stages enabled */
+    /* persistent batch-1 tick: stage program in device memory, sync words, grid size */
+    int mega_ok, mega_ctas, mega_n_stages, mega_built;
+    MegaStage* d_mega_stages;
+    MegaCopyCmd* d_mega_cmds;   /* every CTA's weight-copy commands */
+    int* d_mega_cmd_start;
+    unsigned int* d_mega_sync;  /* [0] grid-barrier counter, [1] status */
+    int* h_mega_status;         /* pinned copy of the status word */
+    unsigned long long* d_mega_trace; /* [stages][4] clock stamps, when S2P_TICK_TRACE=1 */
+    int32_t* mega_types;        /* host copy of the stage kinds */
     cudaStream_t stream;
 
     /* weights */
@@ -74,7 +83,7 @@ struct s2p_model {
     cudaEvent_t ev0, ev1;
     int tick_kernels;                 /* counted while a tick is enqueued or captured */
     int graph_kernels[S2P_MAX_BATCH + 1];
-    int last_rows, last_fused, last_graph, last_kernels;
+    int last_rows, last_fused, last_graph, last_kernels, last_mega;
     float last_device_ms;
 };
 

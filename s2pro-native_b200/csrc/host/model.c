@@ -233,6 +233,13 @@ s2p_status s2p_model_load(const char* model_dir, const s2p_model_opts* opts, s2p
     s2p_qcache* qc = NULL;
     if ((rc = s2p_gemm_init(m->ctx_len)) != S2P_OK) goto fail;
     if (gemv_setup_all() != cudaSuccess) { rc = S2P_ERR_CUDA; goto fail; }
+    if (m->fused_b1 && !s2p_env_is_one("S2P_NO_MEGA")) {
+        if (mega_setup(&m->mega_ctas) == cudaSuccess) m->mega_ok = 1;
+        else {
+            (void)cudaGetLastError();
+            fprintf(stderr, "[s2pro] persistent tick kernel unavailable on this device; using per-stage launches\n");
+        }
+    }
     if ((rc = s2p_qcache_open(model_dir, m->mode, &qc)) != S2P_OK) goto fail;
     if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) { rc = S2P_ERR_CUDA; goto fail; }
     if ((rc = s2p_st_open_dir(model_dir, &st)) != S2P_OK) goto fail;
@@ -332,6 +339,13 @@ void s2p_model_free(s2p_model* m) {
     for (size_t i = 0; i < sizeof(ts) / sizeof(ts[0]); i++) s2p_tensor_free(ts[i]);
     s2p_linear_free(&m->fast_out);
     if (m->attn_ctr) cudaFree(m->attn_ctr);
+    if (m->d_mega_stages) cudaFree(m->d_mega_stages);
+    if (m->d_mega_sync) cudaFree(m->d_mega_sync);
+    if (m->d_mega_cmds) cudaFree(m->d_mega_cmds);
+    if (m->d_mega_cmd_start) cudaFree(m->d_mega_cmd_start);
+    if (m->h_mega_status) cudaFreeHost(m->h_mega_status);
+    if (m->d_mega_trace) cudaFree(m->d_mega_trace);
+    free(m->mega_types);
     if (m->fstage) cudaFree(m->fstage);
     if (m->fcodes) cudaFree(m->fcodes);
     if (m->fkeys) cudaFree(m->fkeys);
@@ -363,6 +377,7 @@ s2p_status s2p_b200_model_stats(const s2p_model* m, s2p_b200_stats* out) {
     out->last_tick_fused = m->last_fused;
     out->last_tick_graph = m->last_graph;
     out->last_tick_kernels = m->last_kernels;
+    out->last_tick_persistent = m->last_mega;
     out->last_tick_device_ms = m->last_device_ms;
     out->upload_bytes = m->up_bytes;
     out->download_bytes = m->out_bytes;

@@ -581,6 +581,220 @@ static s2p_status tick_fused_b1(s2p_model* m, s2p_session* const* act, int decod
     return S2P_OK;
 }
 
+/* ---- persistent batch-1 tick ------------------------------------------------------
+ * The stage list mirrors tick_fused_b1 for a decoding row (it is built once per
+ * model: every per-frame quantity is read on the device from the upload block). */
+static int mega_gemv(MegaStage* st, const s2p_linear* lin, int pro, int epi) {
+    memset(st, 0, sizeof(*st));
+    st->type = MEGA_GEMV;
+    s2p_lin_ref(lin, &st->lin);
+    st->pro = pro; st->epi = epi;
+    const int regions = epi == 2 ? 2 : 1;
+    const size_t rb = st->lin.kind == 2 ? (size_t)st->lin.K / 2 : (size_t)st->lin.K;
+    const size_t sb = st->lin.kind == 0 ? 0 : (size_t)(st->lin.K >> st->lin.gshift) * 2;
+    if (st->lin.K % 512 || rb % 16 || sb % 16 || ((uintptr_t)st->lin.w & 15) || ((uintptr_t)st->lin.scales & 15)) return 0;
+    int rpc = (int)((size_t)mega_slot_bytes() / ((size_t)regions * (rb + sb)));
+    const int cap = mega_max_local_rows(st->lin.K, st->lin.kind) / regions;
+    if (rpc > cap) rpc = cap;
+    st->rows_per_chunk = rpc;
+    return rpc >= 1;
+}
+
+static s2p_status mega_build(s2p_model* m) {
+    const int cap = m->n_slow * 5 + 4 + S2P_NUM_CODEBOOKS * (S2P_FAST_LAYERS * 5 + 1) + 2;
+    MegaStage* prog = (MegaStage*)calloc((size_t)cap, sizeof(MegaStage));
+    if (!prog) return S2P_ERR_OOM;
+    tick_dev d;
+    tick_views(m, &d);
+    int n = 0, ok = 1;
+    MegaStage* st;
+    prog[n].type = MEGA_BEGIN; n++;
+    for (int l = 0; l < m->n_slow && ok; l++) {
+        const s2p_layer* L = &m->slow[l];
+        st = &prog[n++]; ok &= mega_gemv(st, &L->wqkv, 1, 0);
+        st->x.base = BF(m->sx); st->norm_w = L->attn_norm.data; st->y = BF(m->sqkv);
+        st = &prog[n++]; memset(st, 0, sizeof(*st));
+        st->type = MEGA_ATTN_SLOW; st->qkv = BF(m->sqkv); st->q_norm = L->q_norm.data; st->k_norm = L->k_norm.data;
+        st->out = BF(m->sattn); st->kv.bases = d.kv_bases; st->kv.sbases = d.kvs_bases;
+        slow_kv_offsets(m, l, &st->kv);
+        st = &prog[n++]; ok &= mega_gemv(st, &L->wo, 0, 1);
+        st->x.base = BF(m->sattn); st->resid.base = BF(m->sx); st->y = BF(m->sx);
+        st = &prog[n++]; ok &= mega_gemv(st, &L->gate_up, 1, 2);
+        st->x.base = BF(m->sx); st->norm_w = L->ffn_norm.data; st->y = BF(m->sffn);
+        st = &prog[n++]; ok &= mega_gemv(st, &L->w2, 0, 1);
+        st->x.base = BF(m->sffn); st->resid.base = BF(m->sx); st->y = BF(m->sx);
+    }
+    /* tied head on the INT8 sidecar: the 4096 semantic rows, then the EOS row; the first of
+     * the two also leaves the final-normed hidden state for the fast-AR */
+    for (int part = 0; part < 2 && ok; part++) {
+        st = &prog[n++]; memset(st, 0, sizeof(*st));
+        st->type = MEGA_GEMV; st->pro = 1; st->epi = 0;
+        st->lin.kind = 0; st->lin.K = S2P_DIM; st->lin.gshift = 0;
+        const int row = part == 0 ? S2P_TOK_SEMANTIC_START : S2P_TOK_EOS;
+        st->lin.N = part == 0 ? 4096 : 1;
+        st->lin.w = (const int8_t*)m->embed_i8.data + (size_t)row * S2P_DIM;
+        st->lin.scales = (const float*)m->embed_scale.data + row;
+        st->rows_per_chunk = mega_slot_bytes() / S2P_DIM;
+        if (st->rows_per_chunk > mega_max_local_rows(S2P_DIM, 0)) st->rows_per_chunk = mega_max_local_rows(S2P_DIM, 0);
+        if (((uintptr_t)st->lin.w & 15) || !m->embed_i8.data) ok = 0;
+        st->x.base = BF(m->sx); st->norm_w = m->final_norm.data;
+        st->y = part == 0 ? BF(m->slogc) : BF(m->sloge);
+        if (part == 0) { st->normed_out = BF(m->shidden); st->flags = MEGA_NO_BARRIER; }
+    }
+    st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_SAMPLE;
+    for (int cb = 0; cb < S2P_NUM_CODEBOOKS && ok; cb++) {
+        VecRef in;
+        memset(&in, 0, sizeof(in));
+        if (cb == 0) in.base = BF(m->shidden);
+        else {
+            in.base = BF(m->fast_emb);
+            if (cb == 1) in.index = d.sem;
+            else in.key = m->fkeys + (cb - 2);
+        }
+        VecRef fx;
+        memset(&fx, 0, sizeof(fx));
+        fx.base = BF(m->fx);
+        for (int l = 0; l < S2P_FAST_LAYERS && ok; l++) {
+            const s2p_layer* L = &m->fast[l];
+            const VecRef* src = l == 0 ? &in : &fx;
+            st = &prog[n++]; ok &= mega_gemv(st, &L->wqkv, 1, 0);
+            st->x = *src; st->norm_w = L->attn_norm.data; st->y = BF(m->fqkv);
+            st = &prog[n++]; memset(st, 0, sizeof(*st));
+            st->type = MEGA_ATTN_FAST; st->qkv = BF(m->fqkv); st->out = BF(m->fattn); st->pos = cb;
+            fast_kv_ref(m, l, &st->kv);
+            st = &prog[n++]; ok &= mega_gemv(st, &L->wo, 0, 1);
+            st->x.base = BF(m->fattn); st->resid = *src; st->y = BF(m->fx);
+            st = &prog[n++]; ok &= mega_gemv(st, &L->gate_up, 1, 2);
+            st->x = fx; st->norm_w = L->ffn_norm.data; st->y = BF(m->fhff);
+            st = &prog[n++]; ok &= mega_gemv(st, &L->w2, 0, 1);
+            st->x.base = BF(m->fhff); st->resid = fx; st->y = BF(m->fx);
+        }
+        if (cb > 0 && ok) {
+            st = &prog[n++]; ok &= mega_gemv(st, &m->fast_out, 1, 3);
+            st->x = fx; st->norm_w = m->fast_norm.data; st->y = BF(m->flogits); st->key = m->fkeys + (cb - 1);
+        }
+    }
+    st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_FINISH; st->flags = MEGA_NO_BARRIER;
+    m->mega_built = 1;
+    /* every CTA's copy commands, in the order its working warps consume the chunks */
+    const int n_cta = m->mega_ctas;
+    int* cmd_start = (int*)calloc((size_t)n_cta + 1, sizeof(int));
+    MegaCopyCmd* cmds = NULL;
+    size_t n_cmds = 0;
+    if (!cmd_start) { free(prog); return S2P_ERR_OOM; }
+    for (int pass = 0; pass < 2 && ok; pass++) {
+        size_t at = 0;
+        for (int c = 0; c < n_cta; c++) {
+            if (pass) cmd_start[c] = (int)at;
+            for (int i = 0; i < n; i++) {
+                const MegaStage* g = &prog[i];
+                if (g->type != MEGA_GEMV) continue;
+                const int regions = g->epi == 2 ? 2 : 1;
+                const MegaGeom ge = mega_stage_geom(g->lin.N, regions == 2, g->rows_per_chunk, c, n_cta);
+                if (!pass) { at += (size_t)ge.n_chunks; continue; }
+                const size_t rb = g->lin.kind == 2 ? (size_t)g->lin.K / 2 : (size_t)g->lin.K;
+                const size_t sb = g->lin.kind == 0 ? 0 : (size_t)(g->lin.K >> g->lin.gshift) * 2;
+                for (int j = 0; j < ge.n_chunks; j++) {
+                    MegaCopyCmd* cc = &cmds[at++];
+                    memset(cc, 0, sizeof(*cc));
+                    const int rows = ge.rc < ge.cnt - j * ge.rc ? ge.rc : ge.cnt - j * ge.rc;
+                    const size_t first = (size_t)ge.row0 + (size_t)j * ge.rc;
+                    const size_t wbytes = (size_t)rows * rb, sbytes = (size_t)rows * sb;
+                    int k = 0;
+                    for (int reg = 0; reg < regions; reg++) {
+                        const size_t grow = first + (reg ? (size_t)(g->lin.N >> 1) : 0);
+                        cc->src[k] = (unsigned long long)(uintptr_t)((const char*)g->lin.w + grow * rb);
+                        cc->bytes[k] = (unsigned int)wbytes;
+                        cc->dst_off[k] = (unsigned int)((size_t)reg * wbytes);
+                        k++;
+                        if (sbytes) {
+                            cc->src[k] = (unsigned long long)(uintptr_t)((const char*)g->lin.scales + grow * sb);
+                            cc->bytes[k] = (unsigned int)sbytes;
+                            cc->dst_off[k] = (unsigned int)((size_t)regions * wbytes + (size_t)reg * sbytes);
+                            k++;
+                        }
+                    }
+                    if ((size_t)regions * (wbytes + sbytes) > (size_t)mega_slot_bytes()) ok = 0;
+                }
+            }
+        }
+        if (!pass) {
+            n_cmds = at;
+            cmds = (MegaCopyCmd*)malloc((n_cmds ? n_cmds : 1) * sizeof(MegaCopyCmd));
+            if (!cmds) { free(prog); free(cmd_start); return S2P_ERR_OOM; }
+        } else {
+            cmd_start[n_cta] = (int)at;
+        }
+    }
+    if (!ok || n > cap) {
+        free(cmds); free(cmd_start);
+        free(prog);
+        m->mega_ok = 0;
+        fprintf(stderr, "[s2pro] persistent tick kernel: a weight layout does not fit its copy engine rules; "
+                        "using per-stage launches\n");
+        return S2P_OK;
+    }
+    cudaError_t e = cudaMalloc((void**)&m->d_mega_stages, (size_t)n * sizeof(MegaStage));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&m->d_mega_sync, 2 * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMallocHost((void**)&m->h_mega_status, sizeof(int));
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(m->d_mega_stages, prog, (size_t)n * sizeof(MegaStage), cudaMemcpyHostToDevice, m->stream);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&m->d_mega_cmds, (n_cmds ? n_cmds : 1) * sizeof(MegaCopyCmd));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&m->d_mega_cmd_start, ((size_t)n_cta + 1) * sizeof(int));
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(m->d_mega_cmds, cmds, n_cmds * sizeof(MegaCopyCmd), cudaMemcpyHostToDevice, m->stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(m->d_mega_cmd_start, cmd_start, ((size_t)n_cta + 1) * sizeof(int), cudaMemcpyHostToDevice,
+                            m->stream);
+    if (e == cudaSuccess && s2p_env_is_one("S2P_TICK_TRACE")) {
+        e = cudaMalloc((void**)&m->d_mega_trace, (size_t)n * 16 * sizeof(unsigned long long));
+        if (e == cudaSuccess) e = cudaMemsetAsync(m->d_mega_trace, 0, (size_t)n * 16 * sizeof(unsigned long long), m->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    m->mega_types = (int32_t*)malloc((size_t)n * sizeof(int32_t));
+    if (m->mega_types)
+        for (int i = 0; i < n; i++) m->mega_types[i] = prog[i].type;
+    free(prog);
+    free(cmds);
+    free(cmd_start);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "[s2pro] CUDA error %s at %s:%d\n", cudaGetErrorString(e), __FILE__, __LINE__);
+        return S2P_ERR_CUDA;
+    }
+    m->mega_n_stages = n;
+    return S2P_OK;
+}
+
+static s2p_status tick_mega(s2p_model* m) {
+    cudaStream_t st = m->stream;
+    tick_dev d;
+    tick_views(m, &d);
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->d_up, m->h_up, m->up_bytes, cudaMemcpyHostToDevice, st));
+    S2P_CUDA_TRY(cudaMemsetAsync(m->d_mega_sync, 0, 2 * sizeof(unsigned int), st));
+    MegaParams P;
+    memset(&P, 0, sizeof(P));
+    P.stages = m->d_mega_stages; P.n_stages = m->mega_n_stages;
+    P.cmds = m->d_mega_cmds; P.cmd_start = m->d_mega_cmd_start;
+    P.barrier = m->d_mega_sync; P.status = (int*)(m->d_mega_sync + 1);
+    if (!m->embed_i8_only) P.begin.embed = (const s2p_dev_bf16*)m->embed.data;
+    P.begin.embed_i8 = (const int8_t*)m->embed_i8.data;
+    P.begin.embed_scale = (const float*)m->embed_scale.data;
+    P.begin.cb_emb = (const s2p_dev_bf16*)m->cb_emb.data;
+    P.begin.ids = d.ids; P.begin.codes = d.codes; P.begin.mask = d.mask;
+    P.begin.x = BF(m->sx); P.begin.keys = m->fkeys;
+    P.ctx_len = m->ctx_len; P.kv8 = m->kv8; P.n_split_slots = m->n_split_slots;
+    P.pos_arr = d.pos; P.part = (float*)m->attn_part.data; P.counters = m->attn_ctr;
+    P.eps = S2P_NORM_EPS; P.rope_base = S2P_ROPE_BASE; P.head_dim = S2P_HEAD_DIM;
+    P.sem_logits = BF(m->slogc); P.eos_logit = BF(m->sloge);
+    P.states = d.samp; P.out_tok = d.tok; P.out_sem = d.sem; P.out_codes = d.ocodes; P.out_eos = d.eos;
+    P.keys = m->fkeys;
+    P.trace = m->d_mega_trace;
+    S2P_LAUNCH(m, mega_launch(&P, m->mega_ctas, st));
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->h_out, m->d_out, m->out_bytes, cudaMemcpyDeviceToHost, st));
+    S2P_CUDA_TRY(cudaMemcpyAsync(m->h_mega_status, m->d_mega_sync + 1, sizeof(int), cudaMemcpyDeviceToHost, st));
+    return S2P_OK;
+}
+
 s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, int32_t* out_codes, int* eos) {
     if (!m || !sess || !out_codes || !eos || n < 0 || n > m->max_sessions) return S2P_ERR_INVALID;
     for (int i = 0; i < n; i++) {
@@ -642,10 +856,15 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
     /* the library GEMM of the BF16 mode is kept out of stream capture */
     const int graphs = !s2p_env_is_one("S2P_NO_GRAPHS") && dump_dir() == NULL && m->mode == S2P_GEMM_INT8;
     const int fused = m->fused_b1 && nact == 1 && !m->head_full;
-    const int steady = bd == nact && graphs; /* every row decoding: the launch sequence is frame-invariant */
     s2p_status rc = S2P_OK;
+    if (fused && bd == 1 && m->mega_ok && !m->mega_built && dump_dir() == NULL) S2P_TRY(mega_build(m));
+    const int mega = fused && bd == 1 && m->mega_ok && m->mega_built && dump_dir() == NULL;
+    const int steady = bd == nact && graphs && !mega; /* every row decoding: the launch sequence is frame-invariant */
     m->tick_kernels = 0;
-    if (steady) {
+    if (mega) {
+        S2P_CUDA_TRY(cudaEventRecord(m->ev0, st));
+        S2P_TRY(tick_mega(m));
+    } else if (steady) {
         if (!m->gready[bd]) {
             S2P_CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
             rc = fused ? tick_fused_b1(m, act, 1) : tick_general(m, act, bd, nact);
@@ -678,7 +897,12 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
     }
     S2P_CUDA_TRY(cudaEventRecord(m->ev1, st));
     S2P_CUDA_TRY(cudaStreamSynchronize(st));
+    if (mega && *m->h_mega_status != 0) {
+        fprintf(stderr, "[s2pro] persistent tick kernel gave up on a bounded wait (code %d)\n", *m->h_mega_status);
+        return S2P_ERR_INTERNAL;
+    }
     m->last_rows = nact; m->last_fused = fused; m->last_graph = steady; m->last_kernels = m->tick_kernels;
+    m->last_mega = mega;
     if (cudaEventElapsedTime(&m->last_device_ms, m->ev0, m->ev1) != cudaSuccess) m->last_device_ms = 0.f;
     for (int b = 0; b < bd; b++) act[b]->kv_len++;
     m->frames_decoded += (uint64_t)nact;
@@ -701,6 +925,16 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
         s->state = SESS_DECODING;
         eos[i] = 0;
     }
+    return S2P_OK;
+}
+
+s2p_status s2p_b200_model_tick_trace(s2p_model* m, uint64_t* out, int32_t* types, int max_stages, int* n_stages) {
+    if (!m || !out || !n_stages || max_stages < 0) return S2P_ERR_INVALID;
+    if (!m->d_mega_trace || !m->last_mega) return S2P_ERR_STATE;
+    const int n = m->mega_n_stages < max_stages ? m->mega_n_stages : max_stages;
+    *n_stages = m->mega_n_stages;
+    S2P_CUDA_TRY(cudaMemcpy(out, m->d_mega_trace, (size_t)n * 16 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    if (types && m->mega_types) memcpy(types, m->mega_types, (size_t)n * sizeof(int32_t));
     return S2P_OK;
 }
 

@@ -2,7 +2,8 @@
 process: the reference caches its S2P_* switches on first use).
 
 Loads the same synthetic checkpoint into the reference library rebuilt for
-sm_100a and into this library (fused batch-1 path and general path), runs
+sm_100a and into this library (persistent tick kernel, per-stage fused batch-1
+path and general path), runs
 identical API calls on both and prints one JSON object with what matched.
 Usage: model_parity_worker.py MODE N_SLOW FRAMES   (MODE: int8 | int4)
 """
@@ -34,8 +35,9 @@ def main():
     ref = C.CDLL(os.path.join(ROOT, "oracle", "_ref", "libs2pref_l2.so" if n_slow == 2 else "libs2pref.so"))
     capi.bind(ref, capi.PROTOTYPES, strict=False)
 
-    def load(L, fused):
+    def load(L, fused, persistent=True):
         os.environ["S2P_NO_FUSED"] = "0" if fused else "1"
+        os.environ["S2P_NO_MEGA"] = "0" if persistent else "1"
         opts = capi.ModelOpts(capi.GEMM_INT8, 4096, 4)
         m = C.c_void_p()
         rc = L.s2p_model_load(ckpt.encode(), C.byref(opts), C.byref(m))
@@ -77,7 +79,9 @@ def main():
         return buf
 
     ids = synth.random_prompt(prompt_len, 7)
-    models = {"ref": (ref, load(ref, True)), "fused": (mine, load(mine, True)), "general": (mine, load(mine, False))}
+    models = {"ref": (ref, load(ref, True)), "persistent": (mine, load(mine, True)),
+              "fused": (mine, load(mine, True, persistent=False)), "general": (mine, load(mine, False))}
+    paths = ("persistent", "fused", "general")
     result = {"mode": mode, "n_slow": n_slow, "frames": frames, "runs": {}}
     for temp, seed, tag in ((0.0, 0, "greedy"), (0.8, 42, "sampled")):
         res = {}
@@ -88,13 +92,17 @@ def main():
             out, ms = run(L, s, frames)
             kv_after = kvblob(L, m, s, prompt_len + len([o for o in out if o is not None]) - 1) if len(out) > 1 else kv
             res[name] = (out, kv, kv_after, ms)
+            if name != "ref":
+                st = capi.Stats()
+                assert L.s2p_b200_model_stats(m, C.byref(st)) == 0
+                res[name] += ((st.last_tick_persistent, st.last_tick_fused, st.last_tick_kernels, st.last_tick_device_ms),)
             L.s2p_session_destroy(s)
         entry = {"frames_ref": len(res["ref"][0]), "eos": res["ref"][0][-1] is None}
-        for name in ("fused", "general"):
+        for name in paths:
             n_same = sum(1 for a, b in zip(res[name][0], res["ref"][0]) if a == b)
             entry[name] = {"kv_prefill_identical": bool(torch.equal(res[name][1], res["ref"][1])),
                            "kv_after_identical": bool(res[name][2].shape == res["ref"][2].shape and torch.equal(res[name][2], res["ref"][2])),
-                           "frames_identical": n_same, "frames": len(res[name][0]), "ms_wall": res[name][3]}
+                           "frames_identical": n_same, "frames": len(res[name][0]), "ms_wall": res[name][3], "tick": res[name][4]}
         entry["ref_ms_wall"] = res["ref"][3]
         result["runs"][tag] = entry
     # lockstep batch of 3 sessions with different prompts: general path vs reference

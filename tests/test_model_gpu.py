@@ -27,12 +27,17 @@ def run_worker(mode, n_slow, frames, prompt=64):
 
 def check(res):
     for tag, run in res["runs"].items():
-        for path in ("fused", "general"):
+        for path in ("persistent", "fused", "general"):
             r = run[path]
             assert r["kv_prefill_identical"], f"{tag}/{path}: KV cache after prefill differs from the reference"
             assert r["frames"] == run["frames_ref"], f"{tag}/{path}: frame count {r['frames']} vs {run['frames_ref']}"
             assert r["frames_identical"] == run["frames_ref"], f"{tag}/{path}: {r['frames_identical']}/{run['frames_ref']} frames identical"
             assert r["kv_after_identical"], f"{tag}/{path}: KV cache after decode differs"
+        if run["frames_ref"] > 1:
+            # the three ways this library runs a batch-1 tick were really three ways
+            assert run["persistent"]["tick"][0] == 1 and run["persistent"]["tick"][2] == 1
+            assert run["fused"]["tick"][0] == 0 and run["fused"]["tick"][1] == 1
+            assert run["general"]["tick"][1] == 0
     assert res["batch3_identical"] == 12
     assert res["chunked_prefill_same_frames"]
 
