@@ -35,21 +35,30 @@ constexpr int MEGA_WORKERS = 512;
 constexpr int MEGA_THREADS = MEGA_WORKERS;
 constexpr int MEGA_ISSUER = MEGA_WORKERS - 32;  /* lane 0 of the last warp issues the copies */
 constexpr int MEGA_SLOTS = MEGA_RING_SLOTS;
-constexpr int MEGA_SLOT_BYTES = MEGA_RING_SLOT_BYTES;
-constexpr int MEGA_X_BYTES = S2P_FFN_DIM * 4;   /* staged activation vector, f32 at most */
-constexpr int MEGA_PART_BYTES = MEGA_PARTIAL_BYTES; /* per-tile lane partials of one chunk; three of them */
-constexpr int MEGA_PARTS = 3;
+constexpr int MEGA_PARTS = MEGA_PARTIAL_BUFFERS;
 constexpr int MEGA_RED_BYTES = 4352;            /* 260 floats tree | 256 residuals | 512 row scales */
-constexpr int MEGA_WORK_BYTES = MEGA_X_BYTES + MEGA_PARTS * MEGA_PART_BYTES + MEGA_RED_BYTES;
-constexpr int MEGA_SMEM_BYTES = MEGA_SLOTS * MEGA_SLOT_BYTES + MEGA_WORK_BYTES + 256;
-
-static_assert(sizeof(AttnSmem<false>) <= MEGA_WORK_BYTES, "attention scratch must fit the work area");
-static_assert(sizeof(SamplerSmem<MEGA_WORKERS>) <= MEGA_WORK_BYTES, "sampler scratch must fit the work area");
+constexpr int MEGA_TAIL_BYTES = 256;            /* mbarriers, the staged copy command */
+constexpr int MEGA_SMEM_MAX = 225 * 1024; /* 227 KB per CTA less the kernel's static shared memory */
+constexpr int MEGA_PART_BYTES_DEFAULT = 22528;
+/* shared memory: ring slots | work area (x | partial buffers | red) | tail.  Attention and the
+ * sampler overlay the work area. */
+constexpr int MEGA_MIN_WORK = 19456 + MEGA_PARTS * MEGA_PART_BYTES_DEFAULT;
+static_assert(sizeof(AttnSmem<false>) <= MEGA_MIN_WORK, "attention scratch must fit the work area");
+static_assert(sizeof(SamplerSmem<MEGA_WORKERS>) <= MEGA_MIN_WORK, "sampler scratch must fit the work area");
 static_assert(sizeof(MegaCopyCmd) == 64, "one copy command per 64-byte line");
 
 __device__ __forceinline__ bool cta_sync_and(bool p) { return __syncthreads_and(p ? 1 : 0) != 0; }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+/* order-preserving arg-max key: larger value first, then lower index
+ * (src/slowar/kernels.cu:1326-1357); -0 counts as +0 */
+__device__ __forceinline__ unsigned long long argmax_key(__nv_bfloat16 yb, int n) {
+    uint32_t uu = __float_as_uint(bf2f(yb));
+    if (uu == 0x80000000u) uu = 0u;
+    uu = (uu & 0x80000000u) ? ~uu : (uu | 0x80000000u);
+    return ((unsigned long long)uu << 32) | (0xFFFFFFFFu - (uint32_t)n);
 }
 
 struct Ring {
@@ -59,6 +68,7 @@ struct Ring {
     uint64_t* pdone;   /* [MEGA_PARTS] all warps have folded their rows of it (its slot and buffer are free) */
     int* status;
     int cta, n_cta;
+    int slot_bytes, part_floats, x_bytes;
     unsigned consumed; /* chunks consumed so far (every thread keeps its own copy) */
     /* issuer thread only: this CTA's command list (built by the host with mega_stage_geom,
      * the function the consumers use), how many were issued, and the next one, loaded early */
@@ -85,7 +95,7 @@ __device__ __forceinline__ void ring_load_next(Ring& r) {
 __device__ __forceinline__ void ring_issue_upto(Ring& r, unsigned limit) {
     while (r.issued < limit && r.issued < r.n_cmds) {
         const unsigned slot = r.issued % MEGA_SLOTS;
-        unsigned char* dst = r.slots + (size_t)slot * MEGA_SLOT_BYTES;
+        unsigned char* dst = r.slots + (size_t)slot * r.slot_bytes;
         asm volatile("cp.async.wait_all;" ::: "memory");
         const MegaCopyCmd c = *r.next;
         fence_proxy_async_smem(); /* the slot's previous chunk was read through the generic proxy */
@@ -114,8 +124,8 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
     const unsigned sb = (WK == WK_INT8_CH) ? 0u : (unsigned)(K >> gshift) * 2u;
 
     unsigned char* xs = work;
-    float* part0 = reinterpret_cast<float*>(work + MEGA_X_BYTES);
-    float* red = reinterpret_cast<float*>(work + MEGA_X_BYTES + MEGA_PARTS * MEGA_PART_BYTES);
+    float* part0 = reinterpret_cast<float*>(work + r.x_bytes);
+    float* red = part0 + MEGA_PARTS * r.part_floats;
     float* resid_s = red + 260;  /* residual values of this CTA's rows */
     float* rscale_s = red + 516; /* per-channel row scales of this CTA's rows (gate rows, then up rows) */
     {
@@ -153,8 +163,8 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         const unsigned q = q0 + (unsigned)j, slot = q % MEGA_SLOTS, b = q % MEGA_PARTS;
         const int cnt = min(ge.rc, ge.cnt - j * ge.rc);
         const int local_rows = cnt * SW;
-        const unsigned char* wsl = r.slots + (size_t)slot * MEGA_SLOT_BYTES;
-        float* part = part0 + b * (MEGA_PART_BYTES / 4);
+        const unsigned char* wsl = r.slots + (size_t)slot * r.slot_bytes;
+        float* part = part0 + b * r.part_floats;
         const long long c0 = trace ? clock64() : 0;
         if (!mbar_wait_bounded(r.full + slot, (q / MEGA_SLOTS) & 1u, r.status)) return false;
         /* the buffer's previous chunk (q - 3) must be folded by everyone; that also frees its slot */
@@ -217,14 +227,16 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         const int cnt = min(ge.rc, ge.cnt - j * ge.rc);
         const int l0 = j * ge.rc, r0 = ge.row0 + l0;
         const int local_rows = cnt * SW;
-        const unsigned char* ssl = r.slots + (size_t)slot * MEGA_SLOT_BYTES + (size_t)local_rows * rb;
-        const float* part = part0 + b * (MEGA_PART_BYTES / 4);
+        const unsigned char* ssl = r.slots + (size_t)slot * r.slot_bytes + (size_t)local_rows * rb;
+        const float* part = part0 + b * r.part_floats;
         const long long c0 = trace ? clock64() : 0;
         if (!mbar_wait_bounded(r.pfull + b, (q / MEGA_PARTS) & 1u, r.status)) return false;
         const long long c1 = trace ? clock64() : 0;
         if (warp < cnt) {
+            /* second chain: the up row of the pair, or (plain rows) row warp + 16 of the chunk */
             const bool two = (SW == 2);
-            const int la = warp, lb = two ? warp + cnt : warp;
+            const bool second = !two && warp + GEMV_WARPS < cnt;
+            const int la = warp, lb = two ? warp + cnt : (second ? warp + GEMV_WARPS : warp);
             float accA = 0.f, accB = 0.f;
             const float* pa = part + (size_t)la * pstride + lane;
             const float* pb = part + (size_t)lb * pstride + lane;
@@ -248,7 +260,7 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
             }
             if (WK == WK_INT8_CH) {
                 accA = __fmul_rn(accA, rscale_s[l0 + la]);
-                accB = __fmul_rn(accB, rscale_s[two ? ge.cnt + l0 + la : l0 + la]);
+                accB = __fmul_rn(accB, rscale_s[two ? ge.cnt + l0 + la : l0 + lb]);
             }
             if (lane == 0) {
                 const int n = r0 + la;
@@ -261,12 +273,13 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
                     const __nv_bfloat16 yb = f2bf(accA);
                     if (s.epi == EPI_RESID) s.y[n] = f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb)));
                     else s.y[n] = yb;
-                    if (s.epi == EPI_ARGMAX) {
-                        uint32_t uu = __float_as_uint(bf2f(yb));
-                        if (uu == 0x80000000u) uu = 0u;
-                        uu = (uu & 0x80000000u) ? ~uu : (uu | 0x80000000u);
-                        const unsigned long long key = ((unsigned long long)uu << 32) | (0xFFFFFFFFu - (uint32_t)n);
-                        best = key > best ? key : best;
+                    if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(yb, n));
+                    if (second) {
+                        const int n2 = n + GEMV_WARPS;
+                        const __nv_bfloat16 y2 = f2bf(accB);
+                        if (s.epi == EPI_RESID) s.y[n2] = f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2)));
+                        else s.y[n2] = y2;
+                        if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(y2, n2));
                     }
                 }
             }
@@ -398,15 +411,17 @@ __device__ void tick_begin_cta(const TickBeginArgs& a) {
 
 __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    unsigned char* work = smem + (size_t)MEGA_SLOTS * MEGA_SLOT_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(work + MEGA_WORK_BYTES);
-    MegaCopyCmd* next_cmd = reinterpret_cast<MegaCopyCmd*>(work + MEGA_WORK_BYTES + 128);
+    unsigned char* work = smem + (size_t)MEGA_SLOTS * P.lay.slot_bytes;
+    unsigned char* tail = work + P.lay.x_bytes + MEGA_PARTS * P.lay.part_bytes + MEGA_RED_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
+    MegaCopyCmd* next_cmd = reinterpret_cast<MegaCopyCmd*>(tail + 128);
     static_assert(MEGA_SLOTS + 2 * MEGA_PARTS <= 16, "the barrier words precede the staged command");
     const int cta = blockIdx.x, n_cta = gridDim.x, tid = threadIdx.x;
 
     Ring ring;
     ring.slots = smem; ring.full = bars; ring.pfull = bars + MEGA_SLOTS; ring.pdone = bars + MEGA_SLOTS + MEGA_PARTS;
     ring.status = P.status;
+    ring.slot_bytes = P.lay.slot_bytes; ring.part_floats = P.lay.part_bytes / 4; ring.x_bytes = P.lay.x_bytes;
     ring.cta = cta; ring.n_cta = n_cta; ring.consumed = 0;
     ring.cmds = P.cmds + P.cmd_start[cta];
     ring.n_cmds = (unsigned)(P.cmd_start[cta + 1] - P.cmd_start[cta]);
@@ -473,6 +488,11 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         default: break;
         }
         if (tr && tid == 0) tr[2] = clock64();
+        if (P.trace && tid == 0) { /* every CTA: when its own work of the stage was done, on the GPU-wide timer */
+            unsigned long long gt;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+            P.trace[(size_t)P.n_stages * 16 + (size_t)si * n_cta + cta] = gt;
+        }
         /* without a grid barrier the next stage still reuses the work area: wait for this
          * CTA's slowest warp */
         if (s.flags & MEGA_NO_BARRIER) S2P_CTA_SYNC();
@@ -493,21 +513,26 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     }
 }
 
-extern "C" int mega_slot_bytes(void) { return MEGA_SLOT_BYTES; }
-extern "C" int mega_max_local_rows(int K, int kind) {
-    (void)kind;
-    const int fit = MEGA_PART_BYTES / ((K >> 9) * 128);
-    return fit < GEMV_WARPS ? fit : GEMV_WARPS; /* one row per warp in the fold */
+extern "C" void mega_layout(int x_bytes, MegaLayout* out) {
+    out->x_bytes = (x_bytes + 255) & ~255;
+    out->part_bytes = MEGA_PART_BYTES_DEFAULT;
+    const int fixed = out->x_bytes + MEGA_PARTS * out->part_bytes + MEGA_RED_BYTES + MEGA_TAIL_BYTES;
+    out->slot_bytes = ((MEGA_SMEM_MAX - fixed) / MEGA_SLOTS) & ~1023;
+    out->total_bytes = MEGA_SLOTS * out->slot_bytes + fixed;
+}
+extern "C" int mega_max_local_rows(const MegaLayout* lay, int K) {
+    const int fit = lay->part_bytes / ((K >> 9) * 128);
+    return fit < 2 * GEMV_WARPS ? fit : 2 * GEMV_WARPS; /* the fold takes two rows per warp */
 }
 
 extern "C" cudaError_t mega_setup(int* n_cta_out) {
-    cudaError_t e = cudaFuncSetAttribute(k_tick_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, MEGA_SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(k_tick_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, MEGA_SMEM_MAX);
     if (e != cudaSuccess) return e;
     int dev = 0, sms = 0, coop = 0, per_sm = 0;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return e;
     if ((e = cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev)) != cudaSuccess) return e;
-    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tick_mega, MEGA_THREADS, MEGA_SMEM_BYTES)) !=
+    if ((e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_tick_mega, MEGA_THREADS, MEGA_SMEM_MAX)) !=
         cudaSuccess)
         return e;
     if (!coop || per_sm < 1 || sms < 2 * S2P_SLOW_KV_HEADS) return cudaErrorNotSupported;
@@ -518,8 +543,9 @@ extern "C" cudaError_t mega_setup(int* n_cta_out) {
 extern "C" cudaError_t mega_launch(const MegaParams* p, int n_cta, cudaStream_t st) {
     MegaParams P = *p;
     void* args[] = {&P};
+    if (P.lay.total_bytes <= 0 || P.lay.total_bytes > MEGA_SMEM_MAX) return cudaErrorInvalidValue;
     return cudaLaunchCooperativeKernel((const void*)k_tick_mega, dim3((unsigned)n_cta), dim3(MEGA_THREADS), args,
-                                       MEGA_SMEM_BYTES, st);
+                                       (size_t)P.lay.total_bytes, st);
 }
 
 }  // namespace s2p

@@ -147,9 +147,16 @@ typedef struct {
 } MegaStage;
 
 /* Ring geometry shared by the kernel and the host code that builds the copy commands. */
-#define MEGA_RING_SLOTS 6
-#define MEGA_RING_SLOT_BYTES 24576
-#define MEGA_PARTIAL_BYTES 10240
+#define MEGA_RING_SLOTS 4
+#define MEGA_PARTIAL_BUFFERS 2
+/* How one CTA's shared memory is cut up; chosen by the host per model (an all-INT4 model
+ * stages bf16 activations and has room for larger ring slots than one with INT8 layers). */
+typedef struct {
+    int x_bytes;     /* staged activation vector */
+    int slot_bytes;  /* one ring slot */
+    int part_bytes;  /* one buffer of per-tile lane partials */
+    int total_bytes; /* dynamic shared memory of the launch */
+} MegaLayout;
 
 /* One chunk of weights for the ring: up to four 1-D bulk copies (weight rows and group
  * scales, each for the gate and the up half of a SwiGLU stage) into one slot. */
@@ -179,6 +186,7 @@ static inline MegaGeom mega_stage_geom(int N, int swiglu, int rows_per_chunk, in
 typedef struct {
     const MegaStage* stages;      /* device memory */
     int n_stages;
+    MegaLayout lay;
     const MegaCopyCmd* cmds;      /* device memory: every CTA's copy commands in program order */
     const int* cmd_start;         /* [n_cta + 1] first command of each CTA */
     unsigned int* barrier;        /* device word, zero at launch */
@@ -203,8 +211,9 @@ typedef struct {
 
 /* bytes of one ring slot; a stage's rows_per_chunk must satisfy
  * rows * regions * (row bytes + scale bytes per row) <= this */
-int mega_slot_bytes(void);
-int mega_max_local_rows(int K, int kind); /* rows whose per-tile partials fit the shared partial buffer */
+/* layout for a model whose widest staged activation needs x_bytes */
+void mega_layout(int x_bytes, MegaLayout* out);
+int mega_max_local_rows(const MegaLayout* lay, int K); /* rows of one chunk the fold and the partial buffer can take */
 cudaError_t mega_setup(int* n_cta_out);   /* once per device: attribute + occupancy check; grid size */
 cudaError_t mega_launch(const MegaParams* p, int n_cta, cudaStream_t st);
 

@@ -40,6 +40,7 @@ struct s2p_model {
     int fused_b1;      /* batch-1 fused stages enabled */
     /* persistent batch-1 tick: stage program in device memory, sync words, grid size */
     int mega_ok, mega_ctas, mega_n_stages, mega_built;
+    MegaLayout mega_lay;
     MegaStage* d_mega_stages;
     MegaCopyCmd* d_mega_cmds;   /* every CTA's weight-copy commands */
     int* d_mega_cmd_start;

@@ -584,7 +584,7 @@ static s2p_status tick_fused_b1(s2p_model* m, s2p_session* const* act, int decod
 /* ---- persistent batch-1 tick ------------------------------------------------------
  * The stage list mirrors tick_fused_b1 for a decoding row (it is built once per
  * model: every per-frame quantity is read on the device from the upload block). */
-static int mega_gemv(MegaStage* st, const s2p_linear* lin, int pro, int epi) {
+static int mega_gemv(const MegaLayout* lay, MegaStage* st, const s2p_linear* lin, int pro, int epi) {
     memset(st, 0, sizeof(*st));
     st->type = MEGA_GEMV;
     s2p_lin_ref(lin, &st->lin);
@@ -593,8 +593,8 @@ static int mega_gemv(MegaStage* st, const s2p_linear* lin, int pro, int epi) {
     const size_t rb = st->lin.kind == 2 ? (size_t)st->lin.K / 2 : (size_t)st->lin.K;
     const size_t sb = st->lin.kind == 0 ? 0 : (size_t)(st->lin.K >> st->lin.gshift) * 2;
     if (st->lin.K % 512 || rb % 16 || sb % 16 || ((uintptr_t)st->lin.w & 15) || ((uintptr_t)st->lin.scales & 15)) return 0;
-    int rpc = (int)((size_t)mega_slot_bytes() / ((size_t)regions * (rb + sb)));
-    const int cap = mega_max_local_rows(st->lin.K, st->lin.kind) / regions;
+    int rpc = (int)((size_t)lay->slot_bytes / ((size_t)regions * (rb + sb)));
+    const int cap = mega_max_local_rows(lay, st->lin.K) / regions;
     if (rpc > cap) rpc = cap;
     st->rows_per_chunk = rpc;
     return rpc >= 1;
@@ -608,20 +608,34 @@ static s2p_status mega_build(s2p_model* m) {
     tick_views(m, &d);
     int n = 0, ok = 1;
     MegaStage* st;
+    {   /* widest staged activation: bf16 for packed INT4 weights, f32 for int8 codes */
+        int xb = S2P_DIM * 4; /* the tied head is per-channel INT8 on the model width */
+        for (int l = 0; l < m->n_slow + S2P_FAST_LAYERS; l++) {
+            const s2p_layer* L = l < m->n_slow ? &m->slow[l] : &m->fast[l - m->n_slow];
+            const s2p_linear* lins[4] = {&L->wqkv, &L->wo, &L->gate_up, &L->w2};
+            for (int i = 0; i < 4; i++) {
+                LinRef lr;
+                s2p_lin_ref(lins[i], &lr);
+                const int b = lr.K * (lr.kind == 2 ? 2 : 4);
+                if (b > xb) xb = b;
+            }
+        }
+        mega_layout(xb, &m->mega_lay);
+    }
     prog[n].type = MEGA_BEGIN; n++;
     for (int l = 0; l < m->n_slow && ok; l++) {
         const s2p_layer* L = &m->slow[l];
-        st = &prog[n++]; ok &= mega_gemv(st, &L->wqkv, 1, 0);
+        st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wqkv, 1, 0);
         st->x.base = BF(m->sx); st->norm_w = L->attn_norm.data; st->y = BF(m->sqkv);
         st = &prog[n++]; memset(st, 0, sizeof(*st));
         st->type = MEGA_ATTN_SLOW; st->qkv = BF(m->sqkv); st->q_norm = L->q_norm.data; st->k_norm = L->k_norm.data;
         st->out = BF(m->sattn); st->kv.bases = d.kv_bases; st->kv.sbases = d.kvs_bases;
         slow_kv_offsets(m, l, &st->kv);
-        st = &prog[n++]; ok &= mega_gemv(st, &L->wo, 0, 1);
+        st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wo, 0, 1);
         st->x.base = BF(m->sattn); st->resid.base = BF(m->sx); st->y = BF(m->sx);
-        st = &prog[n++]; ok &= mega_gemv(st, &L->gate_up, 1, 2);
+        st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->gate_up, 1, 2);
         st->x.base = BF(m->sx); st->norm_w = L->ffn_norm.data; st->y = BF(m->sffn);
-        st = &prog[n++]; ok &= mega_gemv(st, &L->w2, 0, 1);
+        st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->w2, 0, 1);
         st->x.base = BF(m->sffn); st->resid.base = BF(m->sx); st->y = BF(m->sx);
     }
     /* tied head on the INT8 sidecar: the 4096 semantic rows, then the EOS row; the first of
@@ -634,8 +648,9 @@ static s2p_status mega_build(s2p_model* m) {
         st->lin.N = part == 0 ? 4096 : 1;
         st->lin.w = (const int8_t*)m->embed_i8.data + (size_t)row * S2P_DIM;
         st->lin.scales = (const float*)m->embed_scale.data + row;
-        st->rows_per_chunk = mega_slot_bytes() / S2P_DIM;
-        if (st->rows_per_chunk > mega_max_local_rows(S2P_DIM, 0)) st->rows_per_chunk = mega_max_local_rows(S2P_DIM, 0);
+        st->rows_per_chunk = m->mega_lay.slot_bytes / S2P_DIM;
+        if (st->rows_per_chunk > mega_max_local_rows(&m->mega_lay, S2P_DIM))
+            st->rows_per_chunk = mega_max_local_rows(&m->mega_lay, S2P_DIM);
         if (((uintptr_t)st->lin.w & 15) || !m->embed_i8.data) ok = 0;
         st->x.base = BF(m->sx); st->norm_w = m->final_norm.data;
         st->y = part == 0 ? BF(m->slogc) : BF(m->sloge);
@@ -657,20 +672,20 @@ static s2p_status mega_build(s2p_model* m) {
         for (int l = 0; l < S2P_FAST_LAYERS && ok; l++) {
             const s2p_layer* L = &m->fast[l];
             const VecRef* src = l == 0 ? &in : &fx;
-            st = &prog[n++]; ok &= mega_gemv(st, &L->wqkv, 1, 0);
+            st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wqkv, 1, 0);
             st->x = *src; st->norm_w = L->attn_norm.data; st->y = BF(m->fqkv);
             st = &prog[n++]; memset(st, 0, sizeof(*st));
             st->type = MEGA_ATTN_FAST; st->qkv = BF(m->fqkv); st->out = BF(m->fattn); st->pos = cb;
             fast_kv_ref(m, l, &st->kv);
-            st = &prog[n++]; ok &= mega_gemv(st, &L->wo, 0, 1);
+            st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wo, 0, 1);
             st->x.base = BF(m->fattn); st->resid = *src; st->y = BF(m->fx);
-            st = &prog[n++]; ok &= mega_gemv(st, &L->gate_up, 1, 2);
+            st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->gate_up, 1, 2);
             st->x = fx; st->norm_w = L->ffn_norm.data; st->y = BF(m->fhff);
-            st = &prog[n++]; ok &= mega_gemv(st, &L->w2, 0, 1);
+            st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->w2, 0, 1);
             st->x.base = BF(m->fhff); st->resid = fx; st->y = BF(m->fx);
         }
         if (cb > 0 && ok) {
-            st = &prog[n++]; ok &= mega_gemv(st, &m->fast_out, 1, 3);
+            st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &m->fast_out, 1, 3);
             st->x = fx; st->norm_w = m->fast_norm.data; st->y = BF(m->flogits); st->key = m->fkeys + (cb - 1);
         }
     }
@@ -714,7 +729,7 @@ static s2p_status mega_build(s2p_model* m) {
                             k++;
                         }
                     }
-                    if ((size_t)regions * (wbytes + sbytes) > (size_t)mega_slot_bytes()) ok = 0;
+                    if ((size_t)regions * (wbytes + sbytes) > (size_t)m->mega_lay.slot_bytes) ok = 0;
                 }
             }
         }
@@ -747,8 +762,9 @@ static s2p_status mega_build(s2p_model* m) {
         e = cudaMemcpyAsync(m->d_mega_cmd_start, cmd_start, ((size_t)n_cta + 1) * sizeof(int), cudaMemcpyHostToDevice,
                             m->stream);
     if (e == cudaSuccess && s2p_env_is_one("S2P_TICK_TRACE")) {
-        e = cudaMalloc((void**)&m->d_mega_trace, (size_t)n * 16 * sizeof(unsigned long long));
-        if (e == cudaSuccess) e = cudaMemsetAsync(m->d_mega_trace, 0, (size_t)n * 16 * sizeof(unsigned long long), m->stream);
+        const size_t tb = (size_t)n * (16 + (size_t)n_cta) * sizeof(unsigned long long);
+        e = cudaMalloc((void**)&m->d_mega_trace, tb);
+        if (e == cudaSuccess) e = cudaMemsetAsync(m->d_mega_trace, 0, tb, m->stream);
     }
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     m->mega_types = (int32_t*)malloc((size_t)n * sizeof(int32_t));
@@ -774,7 +790,7 @@ static s2p_status tick_mega(s2p_model* m) {
     MegaParams P;
     memset(&P, 0, sizeof(P));
     P.stages = m->d_mega_stages; P.n_stages = m->mega_n_stages;
-    P.cmds = m->d_mega_cmds; P.cmd_start = m->d_mega_cmd_start;
+    P.cmds = m->d_mega_cmds; P.cmd_start = m->d_mega_cmd_start; P.lay = m->mega_lay;
     P.barrier = m->d_mega_sync; P.status = (int*)(m->d_mega_sync + 1);
     if (!m->embed_i8_only) P.begin.embed = (const s2p_dev_bf16*)m->embed.data;
     P.begin.embed_i8 = (const int8_t*)m->embed_i8.data;
@@ -934,6 +950,9 @@ s2p_status s2p_b200_model_tick_trace(s2p_model* m, uint64_t* out, int32_t* types
     const int n = m->mega_n_stages < max_stages ? m->mega_n_stages : max_stages;
     *n_stages = m->mega_n_stages;
     S2P_CUDA_TRY(cudaMemcpy(out, m->d_mega_trace, (size_t)n * 16 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    if (getenv("S2P_TICK_TRACE_ALL") && max_stages >= m->mega_n_stages) /* probe: per-CTA finish stamps follow */
+        S2P_CUDA_TRY(cudaMemcpy(out + (size_t)m->mega_n_stages * 16, m->d_mega_trace + (size_t)m->mega_n_stages * 16,
+                                (size_t)m->mega_n_stages * m->mega_ctas * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     if (types && m->mega_types) memcpy(types, m->mega_types, (size_t)n * sizeof(int32_t));
     return S2P_OK;
 }
