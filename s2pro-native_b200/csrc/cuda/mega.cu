@@ -36,10 +36,11 @@ constexpr int MEGA_THREADS = MEGA_WORKERS;
 constexpr int MEGA_ISSUER = MEGA_WORKERS - 32;  /* lane 0 of the last warp issues the copies */
 constexpr int MEGA_SLOTS = MEGA_RING_SLOTS;
 constexpr int MEGA_PARTS = MEGA_PARTIAL_BUFFERS;
-constexpr int MEGA_RED_BYTES = 4352;            /* 260 floats tree | 256 residuals | 512 row scales */
-constexpr int MEGA_TAIL_BYTES = 256;            /* mbarriers, the staged copy command */
+constexpr int MEGA_RED_BYTES = 3072;            /* 260 floats tree | 256 residuals | 252 row scales */
+constexpr int MEGA_TAIL_BYTES = 1024;           /* mbarriers, the staged copy command, two stage descriptors */
+static_assert(sizeof(MegaStage) % 16 == 0 && 2 * sizeof(MegaStage) + 256 <= MEGA_TAIL_BYTES, "descriptor staging");
 constexpr int MEGA_SMEM_MAX = 225 * 1024; /* 227 KB per CTA less the kernel's static shared memory */
-constexpr int MEGA_PART_BYTES_DEFAULT = 22528;
+constexpr int MEGA_PART_BYTES_DEFAULT = 19456;  /* 152 (row, tile) units: 30 rows of 5 tiles, 19 of 8, 8 of 19 */
 /* shared memory: ring slots | work area (x | partial buffers | red) | tail.  Attention and the
  * sampler overlay the work area. */
 constexpr int MEGA_MIN_WORK = 19456 + MEGA_PARTS * MEGA_PART_BYTES_DEFAULT;
@@ -111,12 +112,12 @@ __device__ __forceinline__ void ring_issue_upto(Ring& r, unsigned limit) {
 
 /* One GEMV stage of this CTA, chunk by chunk out of the ring.  Returns false
  * (uniformly over the working warps) if a bounded wait gave up. */
-template <int WK>
+template <int WK, int TT> /* TT: K / 512 known at compile time (loops unroll), or 0 */
 __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* trace) {
     typedef typename LaneTile<WK>::type tile_t;
     const MegaGeom ge = mega_stage_geom(s.lin.N, s.epi == EPI_SWIGLU, s.rows_per_chunk, r.cta, r.n_cta);
     if (ge.cnt <= 0) return true; /* uniform over the CTA */
-    const int K = s.lin.K, T = K >> 9, gshift = s.lin.gshift;
+    const int K = s.lin.K, T = TT ? TT : (K >> 9), gshift = s.lin.gshift;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int SW = (s.epi == EPI_SWIGLU) ? 2 : 1;
     const int F = s.lin.N >> 1;
@@ -241,23 +242,26 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
             const float* pa = part + (size_t)la * pstride + lane;
             const float* pb = part + (size_t)lb * pstride + lane;
             if (WK == WK_INT8_CH) {
-#pragma unroll 4
+#pragma unroll
                 for (int i = 0; i < T; i++) { accA += pa[i * 32]; accB += pb[i * 32]; }
             } else {
                 const __half* sa = reinterpret_cast<const __half*>(ssl + (size_t)la * sb);
                 const __half* sbp = reinterpret_cast<const __half*>(ssl + (size_t)lb * sb);
-#pragma unroll 4
+                const int sl = (lane * 16) >> gshift, sstep = 512 >> gshift;
+#pragma unroll
                 for (int i = 0; i < T; i++) {
-                    const int si = (i * 512 + lane * 16) >> gshift;
-                    accA = __fmaf_rn(pa[i * 32], __half2float(sa[si]), accA);
-                    accB = __fmaf_rn(pb[i * 32], __half2float(sbp[si]), accB);
+                    accA = __fmaf_rn(pa[i * 32], __half2float(sa[sl + i * sstep]), accA);
+                    accB = __fmaf_rn(pb[i * 32], __half2float(sbp[sl + i * sstep]), accB);
                 }
             }
+            const long long f1 = trace ? clock64() : 0;
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) {
                 accA += __shfl_xor_sync(S2P_FULL_MASK, accA, off);
                 accB += __shfl_xor_sync(S2P_FULL_MASK, accB, off);
             }
+            const long long f2 = trace ? clock64() : 0;
+            if (trace && threadIdx.x == 0) { trace[8] += f1 - c1; trace[9] += f2 - f1; }
             if (WK == WK_INT8_CH) {
                 accA = __fmul_rn(accA, rscale_s[l0 + la]);
                 accB = __fmul_rn(accB, rscale_s[two ? ge.cnt + l0 + la : l0 + lb]);
@@ -311,6 +315,23 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
     /* every chunk so far is folded by every warp: all their slots are free */
     if (threadIdx.x == MEGA_ISSUER) ring_issue_upto(r, r.consumed + MEGA_SLOTS);
     return true;
+}
+
+template <int WK>
+__device__ __forceinline__ bool gemv_dispatch_t(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
+    switch (s.lin.K) { /* the model's three input widths get fully unrolled tile loops */
+    case S2P_DIM: return gemv_chunks<WK, S2P_DIM / 512>(s, r, work, tr);
+    case S2P_SLOW_Q_HEADS * S2P_HEAD_DIM: return gemv_chunks<WK, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM / 512>(s, r, work, tr);
+    case S2P_FFN_DIM: return gemv_chunks<WK, S2P_FFN_DIM / 512>(s, r, work, tr);
+    default: return gemv_chunks<WK, 0>(s, r, work, tr);
+    }
+}
+__device__ bool gemv_dispatch(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
+    switch (s.lin.kind) {
+    case WK_INT8_CH: return gemv_dispatch_t<WK_INT8_CH>(s, r, work, tr);
+    case WK_INT8_GRP: return gemv_dispatch_t<WK_INT8_GRP>(s, r, work, tr);
+    default: return gemv_dispatch_t<WK_INT4_PACK>(s, r, work, tr);
+    }
 }
 
 /* ---- fast-AR attention stage: head RoPE, cache append and single-tile causal
@@ -438,22 +459,33 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     }
     __syncthreads(); /* the barriers are initialised before anyone waits on them */
 
+    /* Stage descriptors are staged one stage ahead in shared memory: read from global
+     * memory at the start of a stage they would cost two dependent cache misses. */
+    MegaStage* st_buf = reinterpret_cast<MegaStage*>(tail + 256);
+    constexpr int ST_VECS = (int)(sizeof(MegaStage) / 16);
+    auto stage_prefetch = [&](int si) {
+        if (si < P.n_stages && tid < ST_VECS)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(st_buf + (si & 1)) + 16u * tid),
+                         "l"(reinterpret_cast<const char*>(P.stages + si) + 16 * tid) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage_prefetch(0);
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncthreads();
+
     unsigned n_bar = 0;
     bool ok = true;
     for (int si = 0; si < P.n_stages && ok; si++) {
-        const MegaStage& s = P.stages[si];
+        const MegaStage& s = st_buf[si & 1];
+        stage_prefetch(si + 1); /* the other buffer held stage si - 1, which every thread has left */
         unsigned long long* tr = (P.trace && cta == 0) ? P.trace + (size_t)si * 16 : nullptr;
-        if (tr && tid == 0) { tr[0] = clock64(); tr[4] = tr[5] = tr[6] = tr[7] = 0; }
+        if (tr && tid == 0) { tr[0] = clock64(); tr[4] = tr[5] = tr[6] = tr[7] = tr[8] = tr[9] = 0; }
         switch (s.type) {
         case MEGA_BEGIN:
             if (cta == 0) tick_begin_cta(P.begin);
             break;
         case MEGA_GEMV:
-            switch (s.lin.kind) {
-            case WK_INT8_CH: ok = gemv_chunks<WK_INT8_CH>(s, ring, work, tr); break;
-            case WK_INT8_GRP: ok = gemv_chunks<WK_INT8_GRP>(s, ring, work, tr); break;
-            default: ok = gemv_chunks<WK_INT4_PACK>(s, ring, work, tr); break;
-            }
+            ok = gemv_dispatch(s, ring, work, tr);
             break;
         case MEGA_ATTN_SLOW: {
             const int workers = n_cta / S2P_SLOW_KV_HEADS;
@@ -493,10 +525,12 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
             P.trace[(size_t)P.n_stages * 16 + (size_t)si * n_cta + cta] = gt;
         }
+        asm volatile("cp.async.wait_all;" ::: "memory"); /* the next descriptor; the barrier below publishes it */
+        const int no_barrier = s.flags & MEGA_NO_BARRIER;
         /* without a grid barrier the next stage still reuses the work area: wait for this
          * CTA's slowest warp */
-        if (s.flags & MEGA_NO_BARRIER) S2P_CTA_SYNC();
-        if (ok && !(s.flags & MEGA_NO_BARRIER)) {
+        if (no_barrier) S2P_CTA_SYNC();
+        if (ok && !no_barrier) {
             n_bar++;
             ok = grid_barrier(P.barrier, n_bar * (unsigned)n_cta, P.status);
         }
@@ -517,7 +551,7 @@ extern "C" void mega_layout(int x_bytes, MegaLayout* out) {
     out->x_bytes = (x_bytes + 255) & ~255;
     out->part_bytes = MEGA_PART_BYTES_DEFAULT;
     const int fixed = out->x_bytes + MEGA_PARTS * out->part_bytes + MEGA_RED_BYTES + MEGA_TAIL_BYTES;
-    out->slot_bytes = ((MEGA_SMEM_MAX - fixed) / MEGA_SLOTS) & ~1023;
+    out->slot_bytes = ((MEGA_SMEM_MAX - fixed) / MEGA_SLOTS) & ~255;
     out->total_bytes = MEGA_SLOTS * out->slot_bytes + fixed;
 }
 extern "C" int mega_max_local_rows(const MegaLayout* lay, int K) {

@@ -144,6 +144,7 @@ typedef struct {
     s2p_dev_bf16* out;
     KvRef kv;
     int pos;                      /* MEGA_ATTN_FAST: position in the fast-AR cache (= pass index) */
+    int pad_[3];                  /* the kernel stages descriptors with 16-byte copies */
 } MegaStage;
 
 /* Ring geometry shared by the kernel and the host code that builds the copy commands. */
