@@ -46,6 +46,17 @@ def algorithmic_bytes_per_frame(mode, n_slow=36):
     return n_slow * layer + 10 * 4 * layer + 9 * fast_head + 4097 * (2560 + 4)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_tick_mega launch, from the ncu capture summarised in
+# profiles/k_tick_mega_int4_b1.md (36+4 layers, all-INT4, batch 1, ~540 cached positions)
+NCU_TRAFFIC_TICK_MEGA_INT4 = 4428316672
+
+
+def ncu_traffic_per_launch(mode, layers, batch, stats):
+    if mode == "int4" and layers == 36 and batch == 1 and stats.last_tick_persistent:
+        return NCU_TRAFFIC_TICK_MEGA_INT4
+    return None
+
+
 def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -286,11 +297,14 @@ def run_ours(args, rank, world):
         "e2e": {"value": round(step_wall, 4), "unit": "ms/frame", "h2d_bytes_per_step": int(stats.upload_bytes),
                 "d2h_bytes_per_step": int(stats.download_bytes)},
         "gpu_launches": int(stats.last_tick_kernels) * args.steps,
-        "tick": {"kernels": int(stats.last_tick_kernels), "fused": int(stats.last_tick_fused), "graph": int(stats.last_tick_graph),
+        "tick": {"kernels": int(stats.last_tick_kernels), "persistent": int(stats.last_tick_persistent),
+                 "fused": int(stats.last_tick_fused), "graph": int(stats.last_tick_graph),
                  "device_ms_p50": round(statistics.median(dev_ms), 4), "device_ms_p95": round(sorted(dev_ms)[int(0.95 * (len(dev_ms) - 1))], 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "traffic": None, "peak_source": peak_kind,
-                     "note": "whole tick: algorithmic weight bytes per frame / device time per frame; per-kernel figures under roofline_kernels",
+                     "traffic": ncu_traffic_per_launch(args.mode, args.layers, args.batch, stats), "peak_source": peak_kind,
+                     "kernel": "k_tick_mega (one launch = one frame)" if stats.last_tick_persistent else "whole tick (per-stage launches)",
+                     "note": "algorithmic weight bytes per frame / device time of the tick, CUDA events on the model stream; "
+                             "roofline_kernels lists the stand-alone GEMV stage kernels of the non-persistent path",
                      "algorithmic_bytes_per_frame": int(algo), "modelled_bytes_with_kv": int(traffic_model)},
         "clocks": sampler.summary(),
     }
