@@ -45,6 +45,21 @@ s2p_status s2p_b200_model_tick_trace(s2p_model* m, uint64_t* out, int32_t* types
 /* The stream every tick of this model is issued on (for external event timing). */
 cudaStream_t s2p_b200_model_stream(s2p_model* m);
 
+/* Tensor-parallel batch-1 decode over 2, 4 or 8 GPUs of one node (no counterpart in the
+ * reference, which runs one GPU per process and has no sharded path).  One process per GPU
+ * loads the same checkpoint, exports a handle to its exchange arena, receives the handles of
+ * all ranks (any transport: the caller exchanges 64-byte blobs), and attaches before creating
+ * sessions.  From then on every rank must issue the same API calls with the same arguments in
+ * the same order; the persistent tick kernels of the ranks split the rows of every matrix
+ * between them, store each stage's outputs into every rank's arena over NVLink and meet at a
+ * barrier that spans the ranks.  Every row is still computed by one thread block with the
+ * single-GPU arithmetic, so the frames are bit-identical to a single-GPU run.  Each kv head's
+ * cache is kept current only on the rank that attends over it: KV blobs saved from a
+ * tensor-parallel session are not portable.  Prefill is replicated on every rank. */
+#define S2P_B200_TP_HANDLE_BYTES 64
+s2p_status s2p_b200_model_tp_export(s2p_model* m, void* handle_out);
+s2p_status s2p_b200_model_tp_attach(s2p_model* m, int rank, int world, const void* handles);
+
 /* Decode attention that never asks the driver for memory.  (No counterpart in the
  * reference: its split-K attention takes a caller-allocated scratch pointer.)
  *

@@ -232,7 +232,9 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
             l = __fmaf_rn(ls, w, l);
             acc = __fmaf_rn(__ldcg(ph + 2 + dd), w, acc);
         }
-        a.out[((size_t)row * QH + h) * 128 + dd] = f2bf(__fdiv_rn(acc, l));
+        const __nv_bfloat16 ob = f2bf(__fdiv_rn(acc, l));
+        a.out[((size_t)row * QH + h) * 128 + dd] = ob;
+        for (int p = 0; p < a.n_out_peers; p++) a.out_peers[p][((size_t)row * QH + h) * 128 + dd] = ob;
     }
     if (last && tid == 0) *ctr = 0u;
     S2P_CTA_SYNC(); /* the shared block may be reused by the caller right away */

@@ -62,6 +62,17 @@ __device__ __forceinline__ unsigned long long argmax_key(__nv_bfloat16 yb, int n
     return ((unsigned long long)uu << 32) | (0xFFFFFFFFu - (uint32_t)n);
 }
 
+/* store a stage output into the own exchange arena and, tensor-parallel, into every peer's */
+template <class T>
+__device__ __forceinline__ void store_all(const MegaParams& P, T* p, T v) {
+    *p = v;
+    if (P.tp_world > 1) {
+        const size_t off = reinterpret_cast<unsigned char*>(p) - P.tp_base[P.tp_rank];
+        for (int r = 0; r < P.tp_world; r++)
+            if (r != P.tp_rank) *reinterpret_cast<T*>(P.tp_base[r] + off) = v;
+    }
+}
+
 struct Ring {
     unsigned char* slots;
     uint64_t* full;    /* [MEGA_SLOTS] a chunk has landed */
@@ -113,7 +124,7 @@ __device__ __forceinline__ void ring_issue_upto(Ring& r, unsigned limit) {
 /* One GEMV stage of this CTA, chunk by chunk out of the ring.  Returns false
  * (uniformly over the working warps) if a bounded wait gave up. */
 template <int WK, int TT> /* TT: K / 512 known at compile time (loops unroll), or 0 */
-__device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* trace) {
+__device__ bool gemv_chunks(const MegaParams& P, const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* trace) {
     typedef typename LaneTile<WK>::type tile_t;
     const MegaGeom ge = mega_stage_geom(s.lin.N, s.epi == EPI_SWIGLU, s.rows_per_chunk, r.cta, r.n_cta);
     if (ge.cnt <= 0) return true; /* uniform over the CTA */
@@ -272,17 +283,15 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
                     const float gate = bf16_round(accA), up = bf16_round(accB);
                     const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gate)));
                     const float sil = bf16_round(__fmul_rn(gate, sig));
-                    s.y[n] = f2bf(__fmul_rn(sil, up));
+                    store_all(P, s.y + n, f2bf(__fmul_rn(sil, up)));
                 } else {
                     const __nv_bfloat16 yb = f2bf(accA);
-                    if (s.epi == EPI_RESID) s.y[n] = f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb)));
-                    else s.y[n] = yb;
+                    store_all(P, s.y + n, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb))) : yb);
                     if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(yb, n));
                     if (second) {
                         const int n2 = n + GEMV_WARPS;
                         const __nv_bfloat16 y2 = f2bf(accB);
-                        if (s.epi == EPI_RESID) s.y[n2] = f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2)));
-                        else s.y[n2] = y2;
+                        store_all(P, s.y + n2, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2))) : y2);
                         if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(y2, n2));
                     }
                 }
@@ -308,7 +317,14 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         }
     }
     if (ok) ok = fold_chunk(ge.n_chunks - 1);
-    if (s.epi == EPI_ARGMAX && lane == 0 && best) atomicMax(s.key, best);
+    if (s.epi == EPI_ARGMAX && lane == 0 && best) {
+        atomicMax(s.key, best);
+        if (P.tp_world > 1) {
+            const size_t off = reinterpret_cast<unsigned char*>(s.key) - P.tp_base[P.tp_rank];
+            for (int q = 0; q < P.tp_world; q++)
+                if (q != P.tp_rank) atomicMax_system(reinterpret_cast<unsigned long long*>(P.tp_base[q] + off), best);
+        }
+    }
     r.consumed = q0 + (unsigned)ge.n_chunks;
     /* a warp that gave up skipped its remaining chunks: everyone leaves with the same verdict */
     if (!cta_sync_and(ok)) return false;
@@ -318,19 +334,20 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
 }
 
 template <int WK>
-__device__ __forceinline__ bool gemv_dispatch_t(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
+__device__ __forceinline__ bool gemv_dispatch_t(const MegaParams& P, const MegaStage& s, Ring& r, unsigned char* work,
+                                                unsigned long long* tr) {
     switch (s.lin.K) { /* the model's three input widths get fully unrolled tile loops */
-    case S2P_DIM: return gemv_chunks<WK, S2P_DIM / 512>(s, r, work, tr);
-    case S2P_SLOW_Q_HEADS * S2P_HEAD_DIM: return gemv_chunks<WK, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM / 512>(s, r, work, tr);
-    case S2P_FFN_DIM: return gemv_chunks<WK, S2P_FFN_DIM / 512>(s, r, work, tr);
-    default: return gemv_chunks<WK, 0>(s, r, work, tr);
+    case S2P_DIM: return gemv_chunks<WK, S2P_DIM / 512>(P, s, r, work, tr);
+    case S2P_SLOW_Q_HEADS * S2P_HEAD_DIM: return gemv_chunks<WK, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM / 512>(P, s, r, work, tr);
+    case S2P_FFN_DIM: return gemv_chunks<WK, S2P_FFN_DIM / 512>(P, s, r, work, tr);
+    default: return gemv_chunks<WK, 0>(P, s, r, work, tr);
     }
 }
-__device__ bool gemv_dispatch(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
+__device__ bool gemv_dispatch(const MegaParams& P, const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
     switch (s.lin.kind) {
-    case WK_INT8_CH: return gemv_dispatch_t<WK_INT8_CH>(s, r, work, tr);
-    case WK_INT8_GRP: return gemv_dispatch_t<WK_INT8_GRP>(s, r, work, tr);
-    default: return gemv_dispatch_t<WK_INT4_PACK>(s, r, work, tr);
+    case WK_INT8_CH: return gemv_dispatch_t<WK_INT8_CH>(P, s, r, work, tr);
+    case WK_INT8_GRP: return gemv_dispatch_t<WK_INT8_GRP>(P, s, r, work, tr);
+    default: return gemv_dispatch_t<WK_INT4_PACK>(P, s, r, work, tr);
     }
 }
 
@@ -350,7 +367,7 @@ struct FastAttnSmem {
     float sp[4][32];
 };
 
-__device__ void fast_attn_cta(const MegaStage& s, int kvh, float rope_base, int head_dim, FastAttnSmem& sm) {
+__device__ void fast_attn_cta(const MegaParams& P, const MegaStage& s, int kvh, float rope_base, int head_dim, FastAttnSmem& sm) {
     const int tid = threadIdx.x, g = tid >> 7, t = tid & 127;
     const int QH = S2P_SLOW_Q_HEADS, KVH = S2P_SLOW_KV_HEADS;
     const int pos = s.pos, len = pos + 1;
@@ -397,7 +414,7 @@ __device__ void fast_attn_cta(const MegaStage& s, int kvh, float rope_base, int 
     {
         float acc = __fmul_rn(0.f, 0.f);
         for (int j = 0; j < len; j++) acc = __fmaf_rn(sm.sp[g][j], sm.vt[j][t], acc);
-        s.out[(size_t)(kvh * 4 + g) * 128 + t] = f2bf(__fdiv_rn(acc, sm.sp[g][31]));
+        store_all(P, s.out + (size_t)(kvh * 4 + g) * 128 + t, f2bf(__fdiv_rn(acc, sm.sp[g][31])));
     }
     __syncthreads();
 }
@@ -437,15 +454,18 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
     MegaCopyCmd* next_cmd = reinterpret_cast<MegaCopyCmd*>(tail + 128);
     static_assert(MEGA_SLOTS + 2 * MEGA_PARTS <= 16, "the barrier words precede the staged command");
-    const int cta = blockIdx.x, n_cta = gridDim.x, tid = threadIdx.x;
+    /* cta / n_cta: position in the grid of all ranks (they equal blockIdx.x / gridDim.x on one GPU) */
+    const int n_local = gridDim.x, tid = threadIdx.x;
+    const int cta = P.tp_rank * n_local + blockIdx.x, n_cta = P.tp_world * n_local;
+    const bool cta0 = blockIdx.x == 0; /* the CTA of each rank that runs the frame start, the sampler and the frame end */
 
     Ring ring;
     ring.slots = smem; ring.full = bars; ring.pfull = bars + MEGA_SLOTS; ring.pdone = bars + MEGA_SLOTS + MEGA_PARTS;
     ring.status = P.status;
     ring.slot_bytes = P.lay.slot_bytes; ring.part_floats = P.lay.part_bytes / 4; ring.x_bytes = P.lay.x_bytes;
     ring.cta = cta; ring.n_cta = n_cta; ring.consumed = 0;
-    ring.cmds = P.cmds + P.cmd_start[cta];
-    ring.n_cmds = (unsigned)(P.cmd_start[cta + 1] - P.cmd_start[cta]);
+    ring.cmds = P.cmds + P.cmd_start[blockIdx.x];
+    ring.n_cmds = (unsigned)(P.cmd_start[blockIdx.x + 1] - P.cmd_start[blockIdx.x]);
     ring.issued = 0; ring.next = next_cmd;
     if (tid == MEGA_ISSUER) {
         for (int i = 0; i < MEGA_SLOTS; i++) mbar_init(ring.full + i, 1);
@@ -478,16 +498,18 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     for (int si = 0; si < P.n_stages && ok; si++) {
         const MegaStage& s = st_buf[si & 1];
         stage_prefetch(si + 1); /* the other buffer held stage si - 1, which every thread has left */
-        unsigned long long* tr = (P.trace && cta == 0) ? P.trace + (size_t)si * 16 : nullptr;
+        unsigned long long* tr = (P.trace && cta0) ? P.trace + (size_t)si * 16 : nullptr;
         if (tr && tid == 0) { tr[0] = clock64(); tr[4] = tr[5] = tr[6] = tr[7] = tr[8] = tr[9] = 0; }
         switch (s.type) {
         case MEGA_BEGIN:
-            if (cta == 0) tick_begin_cta(P.begin);
+            if (cta0) tick_begin_cta(P.begin);
             break;
         case MEGA_GEMV:
-            ok = gemv_dispatch(s, ring, work, tr);
+            ok = gemv_dispatch(P, s, ring, work, tr);
             break;
         case MEGA_ATTN_SLOW: {
+            /* the workers of one kv head are consecutive CTAs of one rank (8 divides by tp_world);
+             * its cache planes are only kept current on that rank */
             const int workers = n_cta / S2P_SLOW_KV_HEADS;
             if (cta < workers * S2P_SLOW_KV_HEADS) {
                 AttnArgs a = {};
@@ -495,6 +517,11 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
                 a.q_heads = S2P_SLOW_Q_HEADS; a.kv_heads = S2P_SLOW_KV_HEADS; a.max_seq = P.ctx_len; a.kv8 = P.kv8;
                 a.pos_arr = P.pos_arr; a.kv = s.kv; a.part = P.part; a.counters = P.counters;
                 a.n_split_slots = P.n_split_slots; a.workers = workers; a.head_dim = P.head_dim;
+                if (P.tp_world > 1) {
+                    const size_t off = reinterpret_cast<unsigned char*>(s.out) - P.tp_base[P.tp_rank];
+                    for (int q = 0; q < P.tp_world; q++)
+                        if (q != P.tp_rank) a.out_peers[a.n_out_peers++] = reinterpret_cast<__nv_bfloat16*>(P.tp_base[q] + off);
+                }
                 const AttnPrep pz = {s.qkv, s.q_norm, s.k_norm, P.eps, P.rope_base};
                 if (P.kv8)
                     attn_decode_cta<true, true>(a, pz, 0, cta / workers, cta % workers, workers,
@@ -506,16 +533,18 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
             break;
         }
         case MEGA_ATTN_FAST:
-            if (cta < S2P_SLOW_KV_HEADS)
-                fast_attn_cta(s, cta, P.rope_base, P.head_dim, *reinterpret_cast<FastAttnSmem*>(work));
+            /* kv head h of the fast-AR lives on rank h / (8 / tp_world), always in the same CTA */
+            if ((int)blockIdx.x < S2P_SLOW_KV_HEADS / P.tp_world)
+                fast_attn_cta(P, s, P.tp_rank * (S2P_SLOW_KV_HEADS / P.tp_world) + blockIdx.x, P.rope_base, P.head_dim,
+                              *reinterpret_cast<FastAttnSmem*>(work));
             break;
         case MEGA_SAMPLE:
-            if (cta == 0)
+            if (cta0) /* every rank samples for itself: same logits, same state, same draw */
                 sampler_cta<MEGA_WORKERS>(P.sem_logits, P.eos_logit, P.states[0], P.out_tok, P.out_sem, P.out_codes,
                                           P.out_eos, *reinterpret_cast<SamplerSmem<MEGA_WORKERS>*>(work));
             break;
         case MEGA_FINISH:
-            if (cta == 0 && tid < 9) P.out_codes[tid + 1] = (int32_t)key_index(__ldcg(P.keys + tid));
+            if (cta0 && tid < 9) P.out_codes[tid + 1] = (int32_t)key_index(__ldcg(P.keys + tid));
             break;
         default: break;
         }
@@ -523,7 +552,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         if (P.trace && tid == 0) { /* every CTA: when its own work of the stage was done, on the GPU-wide timer */
             unsigned long long gt;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-            P.trace[(size_t)P.n_stages * 16 + (size_t)si * n_cta + cta] = gt;
+            P.trace[(size_t)P.n_stages * 16 + (size_t)si * n_local + blockIdx.x] = gt;
         }
         asm volatile("cp.async.wait_all;" ::: "memory"); /* the next descriptor; the barrier below publishes it */
         const int no_barrier = s.flags & MEGA_NO_BARRIER;
@@ -532,7 +561,10 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         if (no_barrier) S2P_CTA_SYNC();
         if (ok && !no_barrier) {
             n_bar++;
-            ok = grid_barrier(P.barrier, n_bar * (unsigned)n_cta, P.status);
+            unsigned* counters[8];
+            const size_t boff = reinterpret_cast<unsigned char*>(P.barrier) - P.tp_base[P.tp_rank];
+            for (int q = 0; q < P.tp_world; q++) counters[q] = reinterpret_cast<unsigned*>(P.tp_base[q] + boff);
+            ok = grid_barrier_tp(counters, P.tp_rank, P.tp_world, (P.bar_base + n_bar) * (unsigned)n_cta, P.status);
         }
         if (tr && tid == 0) tr[3] = clock64();
     }

@@ -52,6 +52,9 @@ typedef struct {
     unsigned int* counters; /* [rows][kv_heads], zero between launches */
     int n_split_slots;      /* ceil(ctx_len / 64) */
     int workers;            /* CTAs per (row, kv head) */
+    /* tensor-parallel ticks: the merged output is also stored into these peers' buffers */
+    int n_out_peers;
+    s2p_dev_bf16* out_peers[7];
     /* Always 128, but passed at run time: the single-pass kernel derives its query
      * scale as rsqrtf((float)head_dim) on the device, as the reference's does
      * (src/slowar/kernels.cu:258); a compile-time 128 would be folded to the
@@ -190,7 +193,15 @@ typedef struct {
     MegaLayout lay;
     const MegaCopyCmd* cmds;      /* device memory: every CTA's copy commands in program order */
     const int* cmd_start;         /* [n_cta + 1] first command of each CTA */
-    unsigned int* barrier;        /* device word, zero at launch */
+    /* Tensor parallelism over `tp_world` GPUs (1 = single GPU): the CTAs of all ranks form one
+     * grid of tp_world * gridDim.x CTAs for the row partition of every matrix; every output of a
+     * stage is stored into the exchange arena of every rank (tp_base[r] is rank r's arena as
+     * mapped into this process, tp_base[tp_rank] its own), and the stage barrier counts the CTAs
+     * of all ranks.  Every pointer of a stage descriptor that is written points into the own arena. */
+    int tp_rank, tp_world;
+    unsigned char* tp_base[8];
+    unsigned int bar_base;        /* barriers completed by earlier ticks (the counters are never reset) */
+    unsigned int* barrier;        /* arena word counting barrier arrivals of all ranks' CTAs */
     int* status;                  /* device word, zero at launch; non-zero afterwards = a bounded wait gave up */
     TickBeginArgs begin;
     /* slow-AR attention */

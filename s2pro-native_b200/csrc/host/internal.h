@@ -7,6 +7,7 @@
 #include "s2p_b200_ext.h"
 #include "../cuda/ops.h"
 
+#define S2P_TP_ARENA_BYTES (256 * 1024)
 #define S2P_MAX_BATCH 256 /* cap on lockstep rows / concurrent sessions */
 #define S2P_KV_PLANES_PER_LAYER (2 * S2P_SLOW_KV_HEADS)
 
@@ -40,6 +41,13 @@ struct s2p_model {
     int fused_b1;      /* batch-1 fused stages enabled */
     /* persistent batch-1 tick: stage program in device memory, sync words, grid size */
     int mega_ok, mega_ctas, mega_n_stages, mega_built;
+    int mega_barriers;          /* grid barriers of one tick */
+    unsigned int mega_ticks;    /* persistent ticks issued so far */
+    /* exchange arena (all buffers the persistent tick writes) and its mappings on the ranks of a
+     * tensor-parallel group; tp_base[tp_rank] == tp_arena */
+    void* tp_arena;
+    void* tp_base[8];
+    int tp_rank, tp_world;
     MegaLayout mega_lay;
     MegaStage* d_mega_stages;
     MegaCopyCmd* d_mega_cmds;   /* every CTA's weight-copy commands */

@@ -226,6 +226,7 @@ s2p_status s2p_model_load(const char* model_dir, const s2p_model_opts* opts, s2p
             fprintf(stderr, "[s2pro] S2P_KV4 is not served (measured out upstream); using INT8 KV\n");
         if (m->kv8) fprintf(stderr, "[s2pro] S2P_KV8: INT8 KV cache (g32 per head vector, f16 scales)\n");
     }
+    m->tp_world = 1;
     m->fused_b1 = (m->mode == S2P_GEMM_INT8) && !s2p_env_is_one("S2P_NO_FUSED");
 
     s2p_status rc;
@@ -234,7 +235,11 @@ s2p_status s2p_model_load(const char* model_dir, const s2p_model_opts* opts, s2p
     if ((rc = s2p_gemm_init(m->ctx_len)) != S2P_OK) goto fail;
     if (gemv_setup_all() != cudaSuccess) { rc = S2P_ERR_CUDA; goto fail; }
     if (m->fused_b1 && !s2p_env_is_one("S2P_NO_MEGA")) {
-        if (mega_setup(&m->mega_ctas) == cudaSuccess) m->mega_ok = 1;
+        if (mega_setup(&m->mega_ctas) == cudaSuccess && cudaMalloc(&m->tp_arena, S2P_TP_ARENA_BYTES) == cudaSuccess &&
+            cudaMemset(m->tp_arena, 0, S2P_TP_ARENA_BYTES) == cudaSuccess) {
+            m->mega_ok = 1;
+            m->tp_base[0] = m->tp_arena;
+        }
         else {
             (void)cudaGetLastError();
             fprintf(stderr, "[s2pro] persistent tick kernel unavailable on this device; using per-stage launches\n");
@@ -341,6 +346,9 @@ void s2p_model_free(s2p_model* m) {
     if (m->attn_ctr) cudaFree(m->attn_ctr);
     if (m->d_mega_stages) cudaFree(m->d_mega_stages);
     if (m->d_mega_sync) cudaFree(m->d_mega_sync);
+    for (int r = 0; r < m->tp_world; r++)
+        if (r != m->tp_rank && m->tp_base[r]) cudaIpcCloseMemHandle(m->tp_base[r]);
+    if (m->tp_arena) cudaFree(m->tp_arena);
     if (m->d_mega_cmds) cudaFree(m->d_mega_cmds);
     if (m->d_mega_cmd_start) cudaFree(m->d_mega_cmd_start);
     if (m->h_mega_status) cudaFreeHost(m->h_mega_status);

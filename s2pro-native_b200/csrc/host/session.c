@@ -600,12 +600,44 @@ static int mega_gemv(const MegaLayout* lay, MegaStage* st, const s2p_linear* lin
     return rpc >= 1;
 }
 
+/* The buffers the persistent tick writes live in one allocation, the exchange arena, so that
+ * tensor-parallel peers can address them at the same offsets in their mapping of it. */
+typedef struct {
+    s2p_dev_bf16 *x, *qkv, *attn, *ffn, *hidden, *logc, *loge, *fx, *fqkv, *fattn, *fhff, *flogits;
+    unsigned long long* keys;
+    unsigned int* barrier;
+} mega_arena;
+
+static void arena_views(const s2p_model* m, mega_arena* a) {
+    char* p = (char*)m->tp_arena;
+    size_t off = 0;
+#define ARENA_TAKE(field, type, count) a->field = (type*)(p + off); off += (((size_t)(count) * sizeof(type)) + 255) & ~(size_t)255
+    ARENA_TAKE(barrier, unsigned int, 1);
+    ARENA_TAKE(keys, unsigned long long, 16);
+    ARENA_TAKE(x, s2p_dev_bf16, S2P_DIM);
+    ARENA_TAKE(qkv, s2p_dev_bf16, S2P_QKV_WIDTH);
+    ARENA_TAKE(attn, s2p_dev_bf16, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM);
+    ARENA_TAKE(ffn, s2p_dev_bf16, S2P_FFN_DIM);
+    ARENA_TAKE(hidden, s2p_dev_bf16, S2P_DIM);
+    ARENA_TAKE(logc, s2p_dev_bf16, 4096);
+    ARENA_TAKE(loge, s2p_dev_bf16, 8);
+    ARENA_TAKE(fx, s2p_dev_bf16, S2P_DIM);
+    ARENA_TAKE(fqkv, s2p_dev_bf16, S2P_QKV_WIDTH);
+    ARENA_TAKE(fattn, s2p_dev_bf16, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM);
+    ARENA_TAKE(fhff, s2p_dev_bf16, S2P_FFN_DIM);
+    ARENA_TAKE(flogits, s2p_dev_bf16, S2P_CB_SIZE);
+#undef ARENA_TAKE
+    (void)off; /* < S2P_TP_ARENA_BYTES */
+}
+
 static s2p_status mega_build(s2p_model* m) {
     const int cap = m->n_slow * 5 + 4 + S2P_NUM_CODEBOOKS * (S2P_FAST_LAYERS * 5 + 1) + 2;
     MegaStage* prog = (MegaStage*)calloc((size_t)cap, sizeof(MegaStage));
     if (!prog) return S2P_ERR_OOM;
     tick_dev d;
     tick_views(m, &d);
+    mega_arena A;
+    arena_views(m, &A);
     int n = 0, ok = 1;
     MegaStage* st;
     {   /* widest staged activation: bf16 for packed INT4 weights, f32 for int8 codes */
@@ -626,17 +658,17 @@ static s2p_status mega_build(s2p_model* m) {
     for (int l = 0; l < m->n_slow && ok; l++) {
         const s2p_layer* L = &m->slow[l];
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wqkv, 1, 0);
-        st->x.base = BF(m->sx); st->norm_w = L->attn_norm.data; st->y = BF(m->sqkv);
+        st->x.base = A.x; st->norm_w = L->attn_norm.data; st->y = A.qkv;
         st = &prog[n++]; memset(st, 0, sizeof(*st));
-        st->type = MEGA_ATTN_SLOW; st->qkv = BF(m->sqkv); st->q_norm = L->q_norm.data; st->k_norm = L->k_norm.data;
-        st->out = BF(m->sattn); st->kv.bases = d.kv_bases; st->kv.sbases = d.kvs_bases;
+        st->type = MEGA_ATTN_SLOW; st->qkv = A.qkv; st->q_norm = L->q_norm.data; st->k_norm = L->k_norm.data;
+        st->out = A.attn; st->kv.bases = d.kv_bases; st->kv.sbases = d.kvs_bases;
         slow_kv_offsets(m, l, &st->kv);
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wo, 0, 1);
-        st->x.base = BF(m->sattn); st->resid.base = BF(m->sx); st->y = BF(m->sx);
+        st->x.base = A.attn; st->resid.base = A.x; st->y = A.x;
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->gate_up, 1, 2);
-        st->x.base = BF(m->sx); st->norm_w = L->ffn_norm.data; st->y = BF(m->sffn);
+        st->x.base = A.x; st->norm_w = L->ffn_norm.data; st->y = A.ffn;
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->w2, 0, 1);
-        st->x.base = BF(m->sffn); st->resid.base = BF(m->sx); st->y = BF(m->sx);
+        st->x.base = A.ffn; st->resid.base = A.x; st->y = A.x;
     }
     /* tied head on the INT8 sidecar: the 4096 semantic rows, then the EOS row; the first of
      * the two also leaves the final-normed hidden state for the fast-AR */
@@ -652,45 +684,47 @@ static s2p_status mega_build(s2p_model* m) {
         if (st->rows_per_chunk > mega_max_local_rows(&m->mega_lay, S2P_DIM))
             st->rows_per_chunk = mega_max_local_rows(&m->mega_lay, S2P_DIM);
         if (((uintptr_t)st->lin.w & 15) || !m->embed_i8.data) ok = 0;
-        st->x.base = BF(m->sx); st->norm_w = m->final_norm.data;
-        st->y = part == 0 ? BF(m->slogc) : BF(m->sloge);
-        if (part == 0) { st->normed_out = BF(m->shidden); st->flags = MEGA_NO_BARRIER; }
+        st->x.base = A.x; st->norm_w = m->final_norm.data;
+        st->y = part == 0 ? A.logc : A.loge;
+        if (part == 0) { st->normed_out = A.hidden; st->flags = MEGA_NO_BARRIER; }
     }
     st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_SAMPLE;
     for (int cb = 0; cb < S2P_NUM_CODEBOOKS && ok; cb++) {
         VecRef in;
         memset(&in, 0, sizeof(in));
-        if (cb == 0) in.base = BF(m->shidden);
+        if (cb == 0) in.base = A.hidden;
         else {
             in.base = BF(m->fast_emb);
             if (cb == 1) in.index = d.sem;
-            else in.key = m->fkeys + (cb - 2);
+            else in.key = A.keys + (cb - 2);
         }
         VecRef fx;
         memset(&fx, 0, sizeof(fx));
-        fx.base = BF(m->fx);
+        fx.base = A.fx;
         for (int l = 0; l < S2P_FAST_LAYERS && ok; l++) {
             const s2p_layer* L = &m->fast[l];
             const VecRef* src = l == 0 ? &in : &fx;
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wqkv, 1, 0);
-            st->x = *src; st->norm_w = L->attn_norm.data; st->y = BF(m->fqkv);
+            st->x = *src; st->norm_w = L->attn_norm.data; st->y = A.fqkv;
             st = &prog[n++]; memset(st, 0, sizeof(*st));
-            st->type = MEGA_ATTN_FAST; st->qkv = BF(m->fqkv); st->out = BF(m->fattn); st->pos = cb;
+            st->type = MEGA_ATTN_FAST; st->qkv = A.fqkv; st->out = A.fattn; st->pos = cb;
             fast_kv_ref(m, l, &st->kv);
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wo, 0, 1);
-            st->x.base = BF(m->fattn); st->resid = *src; st->y = BF(m->fx);
+            st->x.base = A.fattn; st->resid = *src; st->y = A.fx;
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->gate_up, 1, 2);
-            st->x = fx; st->norm_w = L->ffn_norm.data; st->y = BF(m->fhff);
+            st->x = fx; st->norm_w = L->ffn_norm.data; st->y = A.fhff;
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->w2, 0, 1);
-            st->x.base = BF(m->fhff); st->resid = fx; st->y = BF(m->fx);
+            st->x.base = A.fhff; st->resid = fx; st->y = A.fx;
         }
         if (cb > 0 && ok) {
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &m->fast_out, 1, 3);
-            st->x = fx; st->norm_w = m->fast_norm.data; st->y = BF(m->flogits); st->key = m->fkeys + (cb - 1);
+            st->x = fx; st->norm_w = m->fast_norm.data; st->y = A.flogits; st->key = A.keys + (cb - 1);
         }
     }
     st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_FINISH; st->flags = MEGA_NO_BARRIER;
     m->mega_built = 1;
+    m->mega_barriers = 0;
+    for (int i = 0; i < n; i++) m->mega_barriers += !(prog[i].flags & MEGA_NO_BARRIER);
     /* every CTA's copy commands, in the order its working warps consume the chunks */
     const int n_cta = m->mega_ctas;
     int* cmd_start = (int*)calloc((size_t)n_cta + 1, sizeof(int));
@@ -705,7 +739,8 @@ static s2p_status mega_build(s2p_model* m) {
                 const MegaStage* g = &prog[i];
                 if (g->type != MEGA_GEMV) continue;
                 const int regions = g->epi == 2 ? 2 : 1;
-                const MegaGeom ge = mega_stage_geom(g->lin.N, regions == 2, g->rows_per_chunk, c, n_cta);
+                const MegaGeom ge = mega_stage_geom(g->lin.N, regions == 2, g->rows_per_chunk, m->tp_rank * n_cta + c,
+                                                    m->tp_world * n_cta);
                 if (!pass) { at += (size_t)ge.n_chunks; continue; }
                 const size_t rb = g->lin.kind == 2 ? (size_t)g->lin.K / 2 : (size_t)g->lin.K;
                 const size_t sb = g->lin.kind == 0 ? 0 : (size_t)(g->lin.K >> g->lin.gshift) * 2;
@@ -786,24 +821,30 @@ static s2p_status tick_mega(s2p_model* m) {
     tick_dev d;
     tick_views(m, &d);
     S2P_CUDA_TRY(cudaMemcpyAsync(m->d_up, m->h_up, m->up_bytes, cudaMemcpyHostToDevice, st));
-    S2P_CUDA_TRY(cudaMemsetAsync(m->d_mega_sync, 0, 2 * sizeof(unsigned int), st));
+    S2P_CUDA_TRY(cudaMemsetAsync(m->d_mega_sync, 0, 2 * sizeof(unsigned int), st)); /* [1]: the status word */
+    mega_arena A;
+    arena_views(m, &A);
     MegaParams P;
     memset(&P, 0, sizeof(P));
     P.stages = m->d_mega_stages; P.n_stages = m->mega_n_stages;
     P.cmds = m->d_mega_cmds; P.cmd_start = m->d_mega_cmd_start; P.lay = m->mega_lay;
-    P.barrier = m->d_mega_sync; P.status = (int*)(m->d_mega_sync + 1);
+    P.barrier = A.barrier; P.status = (int*)(m->d_mega_sync + 1);
+    P.tp_rank = m->tp_rank; P.tp_world = m->tp_world;
+    for (int r = 0; r < m->tp_world; r++) P.tp_base[r] = (unsigned char*)m->tp_base[r];
+    P.bar_base = m->mega_ticks * (unsigned int)m->mega_barriers; /* wraps with the device counters */
+    m->mega_ticks++;
     if (!m->embed_i8_only) P.begin.embed = (const s2p_dev_bf16*)m->embed.data;
     P.begin.embed_i8 = (const int8_t*)m->embed_i8.data;
     P.begin.embed_scale = (const float*)m->embed_scale.data;
     P.begin.cb_emb = (const s2p_dev_bf16*)m->cb_emb.data;
     P.begin.ids = d.ids; P.begin.codes = d.codes; P.begin.mask = d.mask;
-    P.begin.x = BF(m->sx); P.begin.keys = m->fkeys;
+    P.begin.x = A.x; P.begin.keys = A.keys;
     P.ctx_len = m->ctx_len; P.kv8 = m->kv8; P.n_split_slots = m->n_split_slots;
     P.pos_arr = d.pos; P.part = (float*)m->attn_part.data; P.counters = m->attn_ctr;
     P.eps = S2P_NORM_EPS; P.rope_base = S2P_ROPE_BASE; P.head_dim = S2P_HEAD_DIM;
-    P.sem_logits = BF(m->slogc); P.eos_logit = BF(m->sloge);
+    P.sem_logits = A.logc; P.eos_logit = A.loge;
     P.states = d.samp; P.out_tok = d.tok; P.out_sem = d.sem; P.out_codes = d.ocodes; P.out_eos = d.eos;
-    P.keys = m->fkeys;
+    P.keys = A.keys;
     P.trace = m->d_mega_trace;
     S2P_LAUNCH(m, mega_launch(&P, m->mega_ctas, st));
     S2P_CUDA_TRY(cudaMemcpyAsync(m->h_out, m->d_out, m->out_bytes, cudaMemcpyDeviceToHost, st));
@@ -941,6 +982,34 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
         s->state = SESS_DECODING;
         eos[i] = 0;
     }
+    return S2P_OK;
+}
+
+/* ---- tensor-parallel attach (include/s2p_b200_ext.h) ------------------------------- */
+s2p_status s2p_b200_model_tp_export(s2p_model* m, void* handle_out) {
+    if (!m || !handle_out) return S2P_ERR_INVALID;
+    if (!m->mega_ok || !m->tp_arena) return S2P_ERR_UNSUPPORTED;
+    cudaIpcMemHandle_t h;
+    S2P_CUDA_TRY(cudaIpcGetMemHandle(&h, m->tp_arena));
+    memcpy(handle_out, &h, sizeof(h));
+    return S2P_OK;
+}
+
+s2p_status s2p_b200_model_tp_attach(s2p_model* m, int rank, int world, const void* handles) {
+    if (!m || !handles || rank < 0 || rank >= world) return S2P_ERR_INVALID;
+    if (world != 1 && world != 2 && world != 4 && world != 8) return S2P_ERR_INVALID;
+    if (!m->mega_ok || !m->tp_arena) return S2P_ERR_UNSUPPORTED;
+    if (m->tp_world != 1 || m->mega_ticks != 0 || m->n_sessions != 0) return S2P_ERR_STATE; /* attach once, before any session */
+    for (int r = 0; r < world; r++) {
+        if (r == rank) { m->tp_base[r] = m->tp_arena; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles + (size_t)r * sizeof(h), sizeof(h));
+        void* p = NULL;
+        S2P_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        m->tp_base[r] = p;
+    }
+    m->tp_rank = rank; m->tp_world = world;
+    m->mega_built = 0; /* the row partition depends on the world size */
     return S2P_OK;
 }
 
