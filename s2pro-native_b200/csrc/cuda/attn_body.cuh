@@ -234,7 +234,9 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
         }
         const __nv_bfloat16 ob = f2bf(__fdiv_rn(acc, l));
         a.out[((size_t)row * QH + h) * 128 + dd] = ob;
-        for (int p = 0; p < a.n_out_peers; p++) a.out_peers[p][((size_t)row * QH + h) * 128 + dd] = ob;
+        for (int p = 0; p < a.n_out_peers; p++)
+            *reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(a.out + ((size_t)row * QH + h) * 128 + dd) +
+                                              a.out_peer_delta[p]) = ob;
     }
     if (last && tid == 0) *ctr = 0u;
     S2P_CTA_SYNC(); /* the shared block may be reused by the caller right away */

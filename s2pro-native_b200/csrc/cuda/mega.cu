@@ -62,15 +62,21 @@ __device__ __forceinline__ unsigned long long argmax_key(__nv_bfloat16 yb, int n
     return ((unsigned long long)uu << 32) | (0xFFFFFFFFu - (uint32_t)n);
 }
 
+/* The tensor-parallel group as the kernel uses it: the OTHER ranks' arenas as byte offsets
+ * from the own one (a pointer into the own arena plus delta[i] is the same cell in a peer's).
+ * Kept in shared memory: indexing the kernel parameter array with a run-time index would cost
+ * a local-memory copy of the parameters. */
+struct TpPeers {
+    long long delta[7];
+    int n; /* tp_world - 1; 0 on a single GPU */
+};
+__shared__ TpPeers g_tp;
+
 /* store a stage output into the own exchange arena and, tensor-parallel, into every peer's */
 template <class T>
-__device__ __forceinline__ void store_all(const MegaParams& P, T* p, T v) {
+__device__ __forceinline__ void store_all(T* p, T v) {
     *p = v;
-    if (P.tp_world > 1) {
-        const size_t off = reinterpret_cast<unsigned char*>(p) - P.tp_base[P.tp_rank];
-        for (int r = 0; r < P.tp_world; r++)
-            if (r != P.tp_rank) *reinterpret_cast<T*>(P.tp_base[r] + off) = v;
-    }
+    for (int i = 0; i < g_tp.n; i++) *reinterpret_cast<T*>(reinterpret_cast<unsigned char*>(p) + g_tp.delta[i]) = v;
 }
 
 struct Ring {
@@ -124,7 +130,7 @@ __device__ __forceinline__ void ring_issue_upto(Ring& r, unsigned limit) {
 /* One GEMV stage of this CTA, chunk by chunk out of the ring.  Returns false
  * (uniformly over the working warps) if a bounded wait gave up. */
 template <int WK, int TT> /* TT: K / 512 known at compile time (loops unroll), or 0 */
-__device__ bool gemv_chunks(const MegaParams& P, const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* trace) {
+__device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* trace) {
     typedef typename LaneTile<WK>::type tile_t;
     const MegaGeom ge = mega_stage_geom(s.lin.N, s.epi == EPI_SWIGLU, s.rows_per_chunk, r.cta, r.n_cta);
     if (ge.cnt <= 0) return true; /* uniform over the CTA */
@@ -283,15 +289,15 @@ __device__ bool gemv_chunks(const MegaParams& P, const MegaStage& s, Ring& r, un
                     const float gate = bf16_round(accA), up = bf16_round(accB);
                     const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gate)));
                     const float sil = bf16_round(__fmul_rn(gate, sig));
-                    store_all(P, s.y + n, f2bf(__fmul_rn(sil, up)));
+                    store_all(s.y + n, f2bf(__fmul_rn(sil, up)));
                 } else {
                     const __nv_bfloat16 yb = f2bf(accA);
-                    store_all(P, s.y + n, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb))) : yb);
+                    store_all(s.y + n, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb))) : yb);
                     if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(yb, n));
                     if (second) {
                         const int n2 = n + GEMV_WARPS;
                         const __nv_bfloat16 y2 = f2bf(accB);
-                        store_all(P, s.y + n2, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2))) : y2);
+                        store_all(s.y + n2, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2))) : y2);
                         if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(y2, n2));
                     }
                 }
@@ -319,11 +325,8 @@ __device__ bool gemv_chunks(const MegaParams& P, const MegaStage& s, Ring& r, un
     if (ok) ok = fold_chunk(ge.n_chunks - 1);
     if (s.epi == EPI_ARGMAX && lane == 0 && best) {
         atomicMax(s.key, best);
-        if (P.tp_world > 1) {
-            const size_t off = reinterpret_cast<unsigned char*>(s.key) - P.tp_base[P.tp_rank];
-            for (int q = 0; q < P.tp_world; q++)
-                if (q != P.tp_rank) atomicMax_system(reinterpret_cast<unsigned long long*>(P.tp_base[q] + off), best);
-        }
+        for (int i = 0; i < g_tp.n; i++)
+            atomicMax_system(reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(s.key) + g_tp.delta[i]), best);
     }
     r.consumed = q0 + (unsigned)ge.n_chunks;
     /* a warp that gave up skipped its remaining chunks: everyone leaves with the same verdict */
@@ -334,20 +337,19 @@ __device__ bool gemv_chunks(const MegaParams& P, const MegaStage& s, Ring& r, un
 }
 
 template <int WK>
-__device__ __forceinline__ bool gemv_dispatch_t(const MegaParams& P, const MegaStage& s, Ring& r, unsigned char* work,
-                                                unsigned long long* tr) {
+__device__ __forceinline__ bool gemv_dispatch_t(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
     switch (s.lin.K) { /* the model's three input widths get fully unrolled tile loops */
-    case S2P_DIM: return gemv_chunks<WK, S2P_DIM / 512>(P, s, r, work, tr);
-    case S2P_SLOW_Q_HEADS * S2P_HEAD_DIM: return gemv_chunks<WK, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM / 512>(P, s, r, work, tr);
-    case S2P_FFN_DIM: return gemv_chunks<WK, S2P_FFN_DIM / 512>(P, s, r, work, tr);
-    default: return gemv_chunks<WK, 0>(P, s, r, work, tr);
+    case S2P_DIM: return gemv_chunks<WK, S2P_DIM / 512>(s, r, work, tr);
+    case S2P_SLOW_Q_HEADS * S2P_HEAD_DIM: return gemv_chunks<WK, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM / 512>(s, r, work, tr);
+    case S2P_FFN_DIM: return gemv_chunks<WK, S2P_FFN_DIM / 512>(s, r, work, tr);
+    default: return gemv_chunks<WK, 0>(s, r, work, tr);
     }
 }
-__device__ bool gemv_dispatch(const MegaParams& P, const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
+__device__ bool gemv_dispatch(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
     switch (s.lin.kind) {
-    case WK_INT8_CH: return gemv_dispatch_t<WK_INT8_CH>(P, s, r, work, tr);
-    case WK_INT8_GRP: return gemv_dispatch_t<WK_INT8_GRP>(P, s, r, work, tr);
-    default: return gemv_dispatch_t<WK_INT4_PACK>(P, s, r, work, tr);
+    case WK_INT8_CH: return gemv_dispatch_t<WK_INT8_CH>(s, r, work, tr);
+    case WK_INT8_GRP: return gemv_dispatch_t<WK_INT8_GRP>(s, r, work, tr);
+    default: return gemv_dispatch_t<WK_INT4_PACK>(s, r, work, tr);
     }
 }
 
@@ -367,7 +369,7 @@ struct FastAttnSmem {
     float sp[4][32];
 };
 
-__device__ void fast_attn_cta(const MegaParams& P, const MegaStage& s, int kvh, float rope_base, int head_dim, FastAttnSmem& sm) {
+__device__ void fast_attn_cta(const MegaStage& s, int kvh, float rope_base, int head_dim, FastAttnSmem& sm) {
     const int tid = threadIdx.x, g = tid >> 7, t = tid & 127;
     const int QH = S2P_SLOW_Q_HEADS, KVH = S2P_SLOW_KV_HEADS;
     const int pos = s.pos, len = pos + 1;
@@ -414,7 +416,7 @@ __device__ void fast_attn_cta(const MegaParams& P, const MegaStage& s, int kvh, 
     {
         float acc = __fmul_rn(0.f, 0.f);
         for (int j = 0; j < len; j++) acc = __fmaf_rn(sm.sp[g][j], sm.vt[j][t], acc);
-        store_all(P, s.out + (size_t)(kvh * 4 + g) * 128 + t, f2bf(__fdiv_rn(acc, sm.sp[g][31])));
+        store_all(s.out + (size_t)(kvh * 4 + g) * 128 + t, f2bf(__fdiv_rn(acc, sm.sp[g][31])));
     }
     __syncthreads();
 }
@@ -459,6 +461,19 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     const int cta = P.tp_rank * n_local + blockIdx.x, n_cta = P.tp_world * n_local;
     const bool cta0 = blockIdx.x == 0; /* the CTA of each rank that runs the frame start, the sampler and the frame end */
 
+    if (tid == 0) { /* constant indices only: see TpPeers */
+        int n = 0;
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            if (q < P.tp_world && q != P.tp_rank) {
+                long long d = 0;
+#pragma unroll
+                for (int me = 0; me < 8; me++)
+                    if (me == P.tp_rank) d = (long long)(P.tp_base[q] - P.tp_base[me]);
+                g_tp.delta[n++] = d;
+            }
+        g_tp.n = n;
+    }
     Ring ring;
     ring.slots = smem; ring.full = bars; ring.pfull = bars + MEGA_SLOTS; ring.pdone = bars + MEGA_SLOTS + MEGA_PARTS;
     ring.status = P.status;
@@ -505,7 +520,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
             if (cta0) tick_begin_cta(P.begin);
             break;
         case MEGA_GEMV:
-            ok = gemv_dispatch(P, s, ring, work, tr);
+            ok = gemv_dispatch(s, ring, work, tr);
             break;
         case MEGA_ATTN_SLOW: {
             /* the workers of one kv head are consecutive CTAs of one rank (8 divides by tp_world);
@@ -517,11 +532,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
                 a.q_heads = S2P_SLOW_Q_HEADS; a.kv_heads = S2P_SLOW_KV_HEADS; a.max_seq = P.ctx_len; a.kv8 = P.kv8;
                 a.pos_arr = P.pos_arr; a.kv = s.kv; a.part = P.part; a.counters = P.counters;
                 a.n_split_slots = P.n_split_slots; a.workers = workers; a.head_dim = P.head_dim;
-                if (P.tp_world > 1) {
-                    const size_t off = reinterpret_cast<unsigned char*>(s.out) - P.tp_base[P.tp_rank];
-                    for (int q = 0; q < P.tp_world; q++)
-                        if (q != P.tp_rank) a.out_peers[a.n_out_peers++] = reinterpret_cast<__nv_bfloat16*>(P.tp_base[q] + off);
-                }
+                a.n_out_peers = g_tp.n; a.out_peer_delta = g_tp.delta;
                 const AttnPrep pz = {s.qkv, s.q_norm, s.k_norm, P.eps, P.rope_base};
                 if (P.kv8)
                     attn_decode_cta<true, true>(a, pz, 0, cta / workers, cta % workers, workers,
@@ -535,7 +546,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         case MEGA_ATTN_FAST:
             /* kv head h of the fast-AR lives on rank h / (8 / tp_world), always in the same CTA */
             if ((int)blockIdx.x < S2P_SLOW_KV_HEADS / P.tp_world)
-                fast_attn_cta(P, s, P.tp_rank * (S2P_SLOW_KV_HEADS / P.tp_world) + blockIdx.x, P.rope_base, P.head_dim,
+                fast_attn_cta(s, P.tp_rank * (S2P_SLOW_KV_HEADS / P.tp_world) + blockIdx.x, P.rope_base, P.head_dim,
                               *reinterpret_cast<FastAttnSmem*>(work));
             break;
         case MEGA_SAMPLE:
@@ -561,10 +572,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         if (no_barrier) S2P_CTA_SYNC();
         if (ok && !no_barrier) {
             n_bar++;
-            unsigned* counters[8];
-            const size_t boff = reinterpret_cast<unsigned char*>(P.barrier) - P.tp_base[P.tp_rank];
-            for (int q = 0; q < P.tp_world; q++) counters[q] = reinterpret_cast<unsigned*>(P.tp_base[q] + boff);
-            ok = grid_barrier_tp(counters, P.tp_rank, P.tp_world, (P.bar_base + n_bar) * (unsigned)n_cta, P.status);
+            ok = grid_barrier_tp(P.barrier, g_tp.delta, g_tp.n, (P.bar_base + n_bar) * (unsigned)n_cta, P.status);
         }
         if (tr && tid == 0) tr[3] = clock64();
     }

@@ -52,9 +52,10 @@ typedef struct {
     unsigned int* counters; /* [rows][kv_heads], zero between launches */
     int n_split_slots;      /* ceil(ctx_len / 64) */
     int workers;            /* CTAs per (row, kv head) */
-    /* tensor-parallel ticks: the merged output is also stored into these peers' buffers */
+    /* tensor-parallel ticks: the merged output is also stored into the peers' buffers, the same
+     * cell out_peer_delta[i] bytes away (i < n_out_peers) */
     int n_out_peers;
-    s2p_dev_bf16* out_peers[7];
+    const long long* out_peer_delta;
     /* Always 128, but passed at run time: the single-pass kernel derives its query
      * scale as rsqrtf((float)head_dim) on the device, as the reference's does
      * (src/slowar/kernels.cu:258); a compile-time 128 would be folded to the

@@ -82,28 +82,30 @@ __device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target,
     return ok_s != 0;
 }
 
-/* The same barrier across the persistent kernels of `world` GPUs, each with n_cta_local
- * CTAs: thread 0 of every CTA publishes its CTA's stores system-wide and adds one to the
- * counter in every rank's exchange arena (counters[r]; counters[rank] is the local one), then
- * polls the local counter.  The counters are never reset: `target` is the running total
- * (barriers so far, this one included) x CTAs of all ranks, compared wrap-safely. */
-__device__ __forceinline__ bool grid_barrier_tp(unsigned* const* counters, int rank, int world, unsigned target, int* status) {
+/* The same barrier across the persistent kernels of several GPUs: thread 0 of every CTA
+ * publishes its CTA's stores system-wide and adds one to the counter in the own exchange arena
+ * and in every peer's (the same cell, peer_delta[i] bytes away), then polls the own counter.
+ * The counters are never reset: `target` is the running total (barriers so far, this one
+ * included) x CTAs of all ranks, compared wrap-safely.  n_peers == 0: one GPU. */
+__device__ __forceinline__ bool grid_barrier_tp(unsigned* counter, const long long* peer_delta, int n_peers, unsigned target,
+                                                int* status) {
     __shared__ int ok_tp;
     S2P_CTA_SYNC();
     if (threadIdx.x == 0) {
         int ok = 1;
-        if (world > 1) {
+        if (n_peers > 0) {
             asm volatile("fence.acq_rel.sys;" ::: "memory");
-            for (int r = 0; r < world; r++)
-                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(counters[r]) : "memory");
+            asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
+            for (int i = 0; i < n_peers; i++)
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;"
+                             ::"l"(reinterpret_cast<unsigned char*>(counter) + peer_delta[i]) : "memory");
         } else {
-            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counters[0]) : "memory");
+            asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
         }
         unsigned spins = 0, seen;
-        unsigned* mine = counters[rank];
         for (;;) {
-            if (world > 1) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (n_peers > 0) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+            else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
             if ((int)(seen - target) >= 0) break;
             if (++spins > PIPE_GRID_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_GRID_BARRIER); ok = 0; break; }
             if ((spins & 255u) == 0u && status_peek(status) != PIPE_OK) { ok = 0; break; }
