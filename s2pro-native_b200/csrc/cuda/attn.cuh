@@ -11,6 +11,11 @@ struct AttnPrep {
     const __nv_bfloat16* q_norm; /* [128] or NULL */
     const __nv_bfloat16* k_norm;
     float eps, rope_base;
+    /* persistent tick only: the projection arrives as flagged 32-bit words (bf16 | tag << 16),
+     * one per element, and every load waits (bounded) for its word's tag */
+    const uint32_t* qkv_ll;
+    unsigned qkv_tag;
+    int* status;
 };
 
 cudaError_t launch_attn_decode(const AttnArgs& a, const AttnPrep* prep, int rows, cudaStream_t st);

@@ -9,6 +9,7 @@
 #include "headops.cuh"
 #include "ops.h"
 #include "attn.cuh"
+#include "pipe.cuh"
 
 namespace s2p {
 
@@ -28,6 +29,15 @@ template <bool KV8> struct AttnSmem {
 
 __device__ __forceinline__ float ldcg_bf(const __nv_bfloat16* p) {
     return bf_bits_to_f32(__ldcg(reinterpret_cast<const unsigned short*>(p)));
+}
+/* element idx of the raw qkv projection: plain bf16, or a flagged word to wait for */
+__device__ __forceinline__ float prep_load(const AttnPrep& pz, size_t idx) {
+    if (pz.qkv_ll) {
+        uint32_t w;
+        if (!flag_wait1(pz.qkv_ll + idx, pz.qkv_tag, pz.status, w)) return 0.f; /* status is set; the kernel winds down */
+        return flag_payload(w);
+    }
+    return ldcg_bf(pz.qkv + idx);
 }
 
 template <bool KV8, bool PREP>
@@ -87,7 +97,7 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
         const int h = kvh * 4 + g;
         float v;
         if (PREP) {
-            v = ldcg_bf(pz.qkv + (size_t)row * (QH + 2 * KVH) * 128 + (size_t)h * 128 + t);
+            v = prep_load(pz, (size_t)row * (QH + 2 * KVH) * 128 + (size_t)h * 128 + t);
             if (pz.q_norm) {
                 const float tot = head_tree_sum(__fmaf_rn(v, v, 0.f), red, g, t);
                 const float inv = rsqrtf(__fdiv_rn(tot, 128.0f) + pz.eps);
@@ -108,7 +118,7 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
         if (owner) { /* uniform over the CTA */
             const int g = tid >> 7, t = tid & 127; /* g 0: k, g 1: v, g 2,3 idle but join the barriers */
             const size_t src = (size_t)row * (QH + 2 * KVH) * 128 + (size_t)(QH + (g == 1 ? KVH : 0) + kvh) * 128 + t;
-            float v = ldcg_bf(pz.qkv + (g < 2 ? src : 0));
+            float v = prep_load(pz, g < 2 ? src : 0);
             if (pz.k_norm) { /* uniform */
                 const float tot = head_tree_sum(__fmaf_rn(v, v, 0.f), red, g, t);
                 if (g == 0) {
@@ -233,10 +243,18 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
             acc = __fmaf_rn(__ldcg(ph + 2 + dd), w, acc);
         }
         const __nv_bfloat16 ob = f2bf(__fdiv_rn(acc, l));
-        a.out[((size_t)row * QH + h) * 128 + dd] = ob;
-        for (int p = 0; p < a.n_out_peers; p++)
-            *reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(a.out + ((size_t)row * QH + h) * 128 + dd) +
-                                              a.out_peer_delta[p]) = ob;
+        const size_t oi = ((size_t)row * QH + h) * 128 + dd;
+        if (a.out_ll) {
+            uint32_t* ow = reinterpret_cast<uint32_t*>(a.out) + oi;
+            const uint32_t word = flag_word(ob, a.out_ll_tag);
+            *ow = word;
+            for (int p = 0; p < a.n_out_peers; p++)
+                *reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(ow) + a.out_peer_delta[p]) = word;
+        } else {
+            a.out[oi] = ob;
+            for (int p = 0; p < a.n_out_peers; p++)
+                *reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(a.out + oi) + a.out_peer_delta[p]) = ob;
+        }
     }
     if (last && tid == 0) *ctr = 0u;
     S2P_CTA_SYNC(); /* the shared block may be reused by the caller right away */

@@ -213,24 +213,22 @@ __device__ __forceinline__ uint4 norm_vec8(const uint4& xq, const uint4& wq, flo
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-template <int WK, int PRO>
-__device__ __forceinline__ void stage_activation(const GemvStage& g, unsigned char* xs, float* red, int nthreads) {
+/* `load(v)` returns the eight consecutive bf16 activations 8v .. 8v+7 as a uint4 */
+template <int WK, int PRO, class LoadVec>
+__device__ __forceinline__ void stage_activation_from(const GemvStage& g, LoadVec load, unsigned char* xs, float* red,
+                                                      int nthreads) {
     const int K = g.K, NVEC = K >> 3;
-    const __nv_bfloat16* x = g.x;
-    if (g.x_index) x += (size_t)__ldcg(g.x_index) * K;
-    else if (g.x_key) x += (size_t)key_index(__ldcg(g.x_key)) * K;
-    const uint4* xsrc = reinterpret_cast<const uint4*>(x);
     const uint4* wsrc = reinterpret_cast<const uint4*>(g.norm_w);
     /* the first vector of a thread stays in registers for the normalisation (the model's
      * normed widths need no more than one per thread) */
     const int v0 = threadIdx.x;
     uint4 x0 = make_uint4(0, 0, 0, 0), w0 = x0;
     if (v0 < NVEC) {
-        x0 = __ldcg(xsrc + v0);
         if (PRO == PRO_NORM) w0 = wsrc[v0];
+        x0 = load(v0);
         xs_store_vec8<WK>(xs, v0, x0);
     }
-    for (int v = v0 + nthreads; v < NVEC; v += nthreads) xs_store_vec8<WK>(xs, v, __ldcg(xsrc + v));
+    for (int v = v0 + nthreads; v < NVEC; v += nthreads) xs_store_vec8<WK>(xs, v, load(v));
     if (PRO == PRO_VEC) return;
     S2P_CTA_SYNC();
     /* 256 strided partial sums of squares, halving tree, rsqrtf(mean + eps):
@@ -250,10 +248,19 @@ __device__ __forceinline__ void stage_activation(const GemvStage& g, unsigned ch
         if (emit) reinterpret_cast<uint4*>(g.normed_out)[v0] = q;
     }
     for (int v = v0 + nthreads; v < NVEC; v += nthreads) {
-        const uint4 q = norm_vec8(__ldcg(xsrc + v), wsrc[v], inv);
+        const uint4 q = norm_vec8(load(v), wsrc[v], inv);
         xs_store_vec8<WK>(xs, v, q);
         if (emit) reinterpret_cast<uint4*>(g.normed_out)[v] = q;
     }
+}
+
+template <int WK, int PRO>
+__device__ __forceinline__ void stage_activation(const GemvStage& g, unsigned char* xs, float* red, int nthreads) {
+    const __nv_bfloat16* x = g.x;
+    if (g.x_index) x += (size_t)__ldcg(g.x_index) * g.K;
+    else if (g.x_key) x += (size_t)key_index(__ldcg(g.x_key)) * g.K;
+    const uint4* xsrc = reinterpret_cast<const uint4*>(x);
+    stage_activation_from<WK, PRO>(g, [xsrc](int v) { return __ldcg(xsrc + v); }, xs, red, nthreads);
 }
 
 /* Ask L2 for this CTA's slice of a stage's weights and scales (no registers held,

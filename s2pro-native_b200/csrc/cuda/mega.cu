@@ -87,6 +87,8 @@ struct Ring {
     int* status;
     int cta, n_cta;
     int slot_bytes, part_floats, x_bytes;
+    unsigned seq_base; /* stage instances of earlier ticks */
+    unsigned tag;      /* the tag this stage writes into its flagged outputs */
     unsigned consumed; /* chunks consumed so far (every thread keeps its own copy) */
     /* issuer thread only: this CTA's command list (built by the host with mega_stage_geom,
      * the function the consumers use), how many were issued, and the next one, loaded early */
@@ -141,6 +143,7 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
     const unsigned rb = (WK == WK_INT4_PACK) ? (unsigned)(K >> 1) : (unsigned)K;
     const unsigned sb = (WK == WK_INT8_CH) ? 0u : (unsigned)(K >> gshift) * 2u;
 
+    bool ok = true;
     unsigned char* xs = work;
     float* part0 = reinterpret_cast<float*>(work + r.x_bytes);
     float* red = part0 + MEGA_PARTS * r.part_floats;
@@ -152,7 +155,10 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
             const __nv_bfloat16* resid = s.resid.base;
             if (s.resid.index) resid += (size_t)__ldcg(s.resid.index) * s.lin.N;
             else if (s.resid.key) resid += (size_t)key_index(__ldcg(s.resid.key)) * s.lin.N;
-            resid_s[threadIdx.x] = ldcg_bf16(resid + ge.row0 + threadIdx.x);
+            /* a flagged residual needs no wait: this CTA has already read the whole vector as an input */
+            resid_s[threadIdx.x] = (s.io_flags & MEGA_RESID_LL)
+                                       ? flag_payload(__ldcg(reinterpret_cast<const uint32_t*>(resid) + ge.row0 + threadIdx.x))
+                                       : ldcg_bf16(resid + ge.row0 + threadIdx.x);
         }
         if (WK == WK_INT8_CH && threadIdx.x < ge.cnt * SW) {
             const int l = threadIdx.x;
@@ -162,13 +168,31 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         GemvStage g = {};
         g.K = K; g.x = s.x.base; g.x_index = s.x.index; g.x_key = s.x.key;
         g.norm_w = s.norm_w; g.eps = S2P_NORM_EPS; g.normed_out = s.normed_out;
-        if (s.pro == PRO_NORM) stage_activation<WK, PRO_NORM>(g, xs, red, MEGA_WORKERS);
-        else stage_activation<WK, PRO_VEC>(g, xs, red, MEGA_WORKERS);
+        if (s.x_from >= 0) {
+            /* the input arrives as flagged words from the CTAs (of all ranks) of stage x_from:
+             * wait for each word's tag instead of a grid barrier */
+            const uint4* xll = reinterpret_cast<const uint4*>(s.x.base);
+            const unsigned tag = (r.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
+            int* status = r.status;
+            auto load = [xll, tag, status, &ok](int v) -> uint4 {
+                uint4 a, b;
+                if (!flag_wait4(xll + 2 * v, tag, status, a) || !flag_wait4(xll + 2 * v + 1, tag, status, b)) {
+                    ok = false;
+                    return make_uint4(0, 0, 0, 0);
+                }
+                return make_uint4((a.x & 0xFFFFu) | (a.y << 16), (a.z & 0xFFFFu) | (a.w << 16), (b.x & 0xFFFFu) | (b.y << 16),
+                                  (b.z & 0xFFFFu) | (b.w << 16));
+            };
+            if (s.pro == PRO_NORM) stage_activation_from<WK, PRO_NORM>(g, load, xs, red, MEGA_WORKERS);
+            else stage_activation_from<WK, PRO_VEC>(g, load, xs, red, MEGA_WORKERS);
+        } else {
+            if (s.pro == PRO_NORM) stage_activation<WK, PRO_NORM>(g, xs, red, MEGA_WORKERS);
+            else stage_activation<WK, PRO_VEC>(g, xs, red, MEGA_WORKERS);
+        }
     }
-    S2P_CTA_SYNC();
+    if (!cta_sync_and(ok)) return false;
     if (trace && threadIdx.x == 0) trace[1] = clock64();
     unsigned long long best = 0ull;
-    bool ok = true;
     const unsigned q0 = r.consumed;
     const int pstride = T * 32;
 
@@ -238,6 +262,14 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         return true;
     };
 
+    /* output n of the stage: a bf16 cell, or a flagged word consumers wait on */
+    const bool y_ll = (s.io_flags & MEGA_Y_LL) != 0;
+    const unsigned my_tag = r.tag;
+    auto put_y = [&](int n, __nv_bfloat16 v) {
+        if (y_ll) store_all(reinterpret_cast<uint32_t*>(s.y) + n, flag_word(v, my_tag));
+        else store_all(s.y + n, v);
+    };
+
     /* fold the tiles of row `warp` (rows `warp` and `warp + cnt` of a SwiGLU pair, chains
      * interleaved) in ascending order, merge lanes, run the epilogue */
     auto fold_chunk = [&](int j) -> bool {
@@ -289,15 +321,15 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
                     const float gate = bf16_round(accA), up = bf16_round(accB);
                     const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gate)));
                     const float sil = bf16_round(__fmul_rn(gate, sig));
-                    store_all(s.y + n, f2bf(__fmul_rn(sil, up)));
+                    put_y(n, f2bf(__fmul_rn(sil, up)));
                 } else {
                     const __nv_bfloat16 yb = f2bf(accA);
-                    store_all(s.y + n, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb))) : yb);
+                    put_y(n, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb))) : yb);
                     if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(yb, n));
                     if (second) {
                         const int n2 = n + GEMV_WARPS;
                         const __nv_bfloat16 y2 = f2bf(accB);
-                        store_all(s.y + n2, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2))) : y2);
+                        put_y(n2, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2))) : y2);
                         if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(y2, n2));
                     }
                 }
@@ -369,7 +401,13 @@ struct FastAttnSmem {
     float sp[4][32];
 };
 
-__device__ void fast_attn_cta(const MegaStage& s, int kvh, float rope_base, int head_dim, FastAttnSmem& sm) {
+__device__ void fast_attn_cta(const MegaStage& s, int kvh, float rope_base, int head_dim, unsigned in_tag, unsigned out_tag,
+                              int* status, FastAttnSmem& sm) {
+    auto qkv_at = [&](size_t idx) -> float { /* flagged words from the projection stage */
+        uint32_t w;
+        if (!flag_wait1(reinterpret_cast<const uint32_t*>(s.qkv) + idx, in_tag, status, w)) return 0.f;
+        return flag_payload(w);
+    };
     const int tid = threadIdx.x, g = tid >> 7, t = tid & 127;
     const int QH = S2P_SLOW_Q_HEADS, KVH = S2P_SLOW_KV_HEADS;
     const int pos = s.pos, len = pos + 1;
@@ -378,13 +416,13 @@ __device__ void fast_attn_cta(const MegaStage& s, int kvh, float rope_base, int 
     float c, sn;
     rope_cs(t >> 1, pos, rope_base, c, sn);
     {   /* query of head kvh*4+g: RoPE, bf16, scale */
-        float v = ldcg_bf(s.qkv + (size_t)(kvh * 4 + g) * 128 + t);
+        float v = qkv_at((size_t)(kvh * 4 + g) * 128 + t);
         const float other = __shfl_xor_sync(S2P_FULL_MASK, v, 1);
         v = rope_elem(t, v, other, c, sn);
         sm.sq[g][t] = __fmul_rn(v, rsqrtf((float)head_dim));
     }
     if (g < 2) { /* g 0: new key (RoPE), g 1: new value; both appended at `pos` */
-        float v = ldcg_bf(s.qkv + (size_t)(QH + (g == 1 ? KVH : 0) + kvh) * 128 + t);
+        float v = qkv_at((size_t)(QH + (g == 1 ? KVH : 0) + kvh) * 128 + t);
         if (g == 0) {
             const float other = __shfl_xor_sync(S2P_FULL_MASK, v, 1);
             v = rope_elem(t, v, other, c, sn);
@@ -416,13 +454,13 @@ __device__ void fast_attn_cta(const MegaStage& s, int kvh, float rope_base, int 
     {
         float acc = __fmul_rn(0.f, 0.f);
         for (int j = 0; j < len; j++) acc = __fmaf_rn(sm.sp[g][j], sm.vt[j][t], acc);
-        store_all(s.out + (size_t)(kvh * 4 + g) * 128 + t, f2bf(__fdiv_rn(acc, sm.sp[g][31])));
+        store_all(reinterpret_cast<uint32_t*>(s.out) + (size_t)(kvh * 4 + g) * 128 + t, flag_word(f2bf(__fdiv_rn(acc, sm.sp[g][31])), out_tag));
     }
     __syncthreads();
 }
 
 /* frame start for the single decode row (k_tick_begin of tick.cu, row 0) */
-__device__ void tick_begin_cta(const TickBeginArgs& a) {
+__device__ void tick_begin_cta(const TickBeginArgs& a, unsigned tag) {
     const int64_t id = a.ids[0];
     const bool vq = a.mask[0] != 0;
     int idx[S2P_NUM_CODEBOOKS];
@@ -444,7 +482,7 @@ __device__ void tick_begin_cta(const TickBeginArgs& a) {
             v = bf16_round(__fadd_rn(v, bf16_round(acc)));
             v = bf16_round(__fmul_rn(v, inv_sqrt11));
         }
-        a.x[d] = f2bf(v);
+        reinterpret_cast<uint32_t*>(a.x)[d] = flag_word(f2bf(v), tag); /* own arena only: every rank runs the frame start */
     }
     if (a.keys && threadIdx.x < 9) a.keys[threadIdx.x] = 0ull;
 }
@@ -477,6 +515,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     Ring ring;
     ring.slots = smem; ring.full = bars; ring.pfull = bars + MEGA_SLOTS; ring.pdone = bars + MEGA_SLOTS + MEGA_PARTS;
     ring.status = P.status;
+    ring.seq_base = P.seq_base; ring.tag = 0;
     ring.slot_bytes = P.lay.slot_bytes; ring.part_floats = P.lay.part_bytes / 4; ring.x_bytes = P.lay.x_bytes;
     ring.cta = cta; ring.n_cta = n_cta; ring.consumed = 0;
     ring.cmds = P.cmds + P.cmd_start[blockIdx.x];
@@ -515,9 +554,12 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         stage_prefetch(si + 1); /* the other buffer held stage si - 1, which every thread has left */
         unsigned long long* tr = (P.trace && cta0) ? P.trace + (size_t)si * 16 : nullptr;
         if (tr && tid == 0) { tr[0] = clock64(); tr[4] = tr[5] = tr[6] = tr[7] = tr[8] = tr[9] = 0; }
+        const unsigned my_tag = (P.seq_base + (unsigned)si + 1u) & 0xFFFFu;
+        const unsigned in_tag = (P.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
+        ring.tag = my_tag;
         switch (s.type) {
         case MEGA_BEGIN:
-            if (cta0) tick_begin_cta(P.begin);
+            if (cta0) tick_begin_cta(P.begin, my_tag);
             break;
         case MEGA_GEMV:
             ok = gemv_dispatch(s, ring, work, tr);
@@ -533,7 +575,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
                 a.pos_arr = P.pos_arr; a.kv = s.kv; a.part = P.part; a.counters = P.counters;
                 a.n_split_slots = P.n_split_slots; a.workers = workers; a.head_dim = P.head_dim;
                 a.n_out_peers = g_tp.n; a.out_peer_delta = g_tp.delta;
-                const AttnPrep pz = {s.qkv, s.q_norm, s.k_norm, P.eps, P.rope_base};
+                a.out_ll = 1; a.out_ll_tag = my_tag;
+                const AttnPrep pz = {s.qkv, s.q_norm, s.k_norm, P.eps, P.rope_base,
+                                     reinterpret_cast<const uint32_t*>(s.qkv), in_tag, P.status};
                 if (P.kv8)
                     attn_decode_cta<true, true>(a, pz, 0, cta / workers, cta % workers, workers,
                                                 *reinterpret_cast<AttnSmem<true>*>(work));
@@ -546,13 +590,26 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         case MEGA_ATTN_FAST:
             /* kv head h of the fast-AR lives on rank h / (8 / tp_world), always in the same CTA */
             if ((int)blockIdx.x < S2P_SLOW_KV_HEADS / P.tp_world)
-                fast_attn_cta(s, P.tp_rank * (S2P_SLOW_KV_HEADS / P.tp_world) + blockIdx.x, P.rope_base, P.head_dim,
-                              *reinterpret_cast<FastAttnSmem*>(work));
+                fast_attn_cta(s, P.tp_rank * (S2P_SLOW_KV_HEADS / P.tp_world) + blockIdx.x, P.rope_base, P.head_dim, in_tag,
+                              my_tag, P.status, *reinterpret_cast<FastAttnSmem*>(work));
             break;
         case MEGA_SAMPLE:
-            if (cta0) /* every rank samples for itself: same logits, same state, same draw */
-                sampler_cta<MEGA_WORKERS>(P.sem_logits, P.eos_logit, P.states[0], P.out_tok, P.out_sem, P.out_codes,
-                                          P.out_eos, *reinterpret_cast<SamplerSmem<MEGA_WORKERS>*>(work));
+            if (cta0) { /* every rank samples for itself: same logits, same state, same draw */
+                /* the head stages wrote flagged words: wait for them and unflag into the scratch row */
+                const uint32_t* lc = reinterpret_cast<const uint32_t*>(P.sem_logits);
+                const unsigned tc = (P.seq_base + (unsigned)P.logc_from + 1u) & 0xFFFFu;
+                const unsigned te = (P.seq_base + (unsigned)P.loge_from + 1u) & 0xFFFFu;
+                for (int i = tid; i < 4097; i += MEGA_WORKERS) {
+                    uint32_t w = 0;
+                    if (i < 4096) flag_wait1(lc + i, tc, P.status, w);
+                    else flag_wait1(reinterpret_cast<const uint32_t*>(P.eos_logit), te, P.status, w);
+                    reinterpret_cast<unsigned short*>(P.logits_plain)[i] = (unsigned short)(w & 0xFFFFu);
+                }
+                __threadfence_block();
+                S2P_CTA_SYNC();
+                sampler_cta<MEGA_WORKERS>(P.logits_plain, P.logits_plain + 4096, P.states[0], P.out_tok, P.out_sem,
+                                          P.out_codes, P.out_eos, *reinterpret_cast<SamplerSmem<MEGA_WORKERS>*>(work));
+            }
             break;
         case MEGA_FINISH:
             if (cta0 && tid < 9) P.out_codes[tid + 1] = (int32_t)key_index(__ldcg(P.keys + tid));

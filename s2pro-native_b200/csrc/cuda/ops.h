@@ -56,6 +56,10 @@ typedef struct {
      * cell out_peer_delta[i] bytes away (i < n_out_peers) */
     int n_out_peers;
     const long long* out_peer_delta;
+    /* persistent tick only: when non-zero the merged output is written as flagged 32-bit words
+     * (bf16 | out_ll_tag << 16) into `out` taken as a uint32 array */
+    int out_ll;
+    unsigned out_ll_tag;
     /* Always 128, but passed at run time: the single-pass kernel derives its query
      * scale as rsqrtf((float)head_dim) on the device, as the reference's does
      * (src/slowar/kernels.cu:258); a compile-time 128 would be folded to the
@@ -148,8 +152,15 @@ typedef struct {
     s2p_dev_bf16* out;
     KvRef kv;
     int pos;                      /* MEGA_ATTN_FAST: position in the fast-AR cache (= pass index) */
-    int pad_[3];                  /* the kernel stages descriptors with 16-byte copies */
+    /* Flagged exchange (see mega.cu): the index of the stage that produces this stage's input
+     * vector (x for a GEMV, qkv for attention) as flagged words, or -1 when the input is plain
+     * bf16 that an earlier grid barrier has published; and what else is flagged. */
+    int x_from;
+    int io_flags;                 /* MEGA_Y_LL: the output is written as flagged words; MEGA_RESID_LL: the residual is read from them */
+    int pad_;                     /* the kernel stages descriptors with 16-byte copies */
 } MegaStage;
+#define MEGA_Y_LL 1
+#define MEGA_RESID_LL 2
 
 /* Ring geometry shared by the kernel and the host code that builds the copy commands. */
 #define MEGA_RING_SLOTS 4
@@ -202,6 +213,9 @@ typedef struct {
     int tp_rank, tp_world;
     unsigned char* tp_base[8];
     unsigned int bar_base;        /* barriers completed by earlier ticks (the counters are never reset) */
+    unsigned int seq_base;        /* stages run by earlier ticks: stage i of this tick flags its words with (seq_base + i + 1) & 0xFFFF */
+    int logc_from, loge_from;     /* stages that produce the sampler's flagged logits */
+    s2p_dev_bf16* logits_plain;   /* [4097] scratch: the sampler's logits unflagged (own CTA only) */
     unsigned int* barrier;        /* arena word counting barrier arrivals of all ranks' CTAs */
     int* status;                  /* device word, zero at launch; non-zero afterwards = a bounded wait gave up */
     TickBeginArgs begin;

@@ -10,7 +10,7 @@
 
 namespace s2p {
 
-enum PipeError { PIPE_OK = 0, PIPE_ERR_TMA_WAIT = 1, PIPE_ERR_GRID_BARRIER = 2 };
+enum PipeError { PIPE_OK = 0, PIPE_ERR_TMA_WAIT = 1, PIPE_ERR_GRID_BARRIER = 2, PIPE_ERR_FLAG_WAIT = 3 };
 
 constexpr unsigned PIPE_MBAR_TRIES = 1u << 20;   /* each try_wait already blocks for a hardware time slice */
 constexpr unsigned PIPE_GRID_SPINS = 1u << 22;   /* a few seconds of polling an L2 word */
@@ -58,6 +58,49 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
     atomicCAS(status, PIPE_OK, PIPE_ERR_TMA_WAIT);
     return false;
 }
+
+/* ---- flagged words -------------------------------------------------------------
+ * A value handed from one CTA (or GPU) to another without a barrier: a 32-bit word
+ * carrying a bf16 payload in its low half and a 16-bit tag in its high half.  The
+ * producer writes the word with one store; a consumer that reads the expected tag has
+ * the payload of the same store (a 32-bit store is single-copy atomic), so no fence
+ * and no separate flag are involved.  Tags count stage instances modulo 65536; every
+ * cell is rewritten at least once per frame (a few hundred stage instances), so a
+ * stale word can never carry the expected tag. */
+constexpr unsigned PIPE_FLAG_SPINS = 1u << 21;
+
+__device__ __forceinline__ uint32_t flag_word(__nv_bfloat16 v, unsigned tag) {
+    return (uint32_t)__bfloat16_as_ushort(v) | (tag << 16);
+}
+__device__ __forceinline__ uint32_t flag_ld1(const uint32_t* p) {
+    uint32_t w;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(w) : "l"(p) : "memory");
+    return w;
+}
+__device__ __forceinline__ uint4 flag_ld4(const uint4* p) {
+    uint4 q;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "l"(p) : "memory");
+    return q;
+}
+/* wait for one word / four consecutive words to carry `tag`; false (status set) on time-out */
+__device__ __forceinline__ bool flag_wait1(const uint32_t* p, unsigned tag, int* status, uint32_t& w) {
+    for (unsigned i = 0;; i++) {
+        w = flag_ld1(p);
+        if ((w >> 16) == tag) return true;
+        if (i > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); return false; }
+        if ((i & 63u) == 63u && status_peek(status) != PIPE_OK) return false;
+    }
+}
+__device__ __forceinline__ bool flag_wait4(const uint4* p, unsigned tag, int* status, uint4& q) {
+    for (unsigned i = 0;; i++) {
+        q = flag_ld4(p);
+        if (((q.x >> 16) == tag) & ((q.y >> 16) == tag) & ((q.z >> 16) == tag) & ((q.w >> 16) == tag)) return true;
+        if (i > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); return false; }
+        if ((i & 63u) == 63u && status_peek(status) != PIPE_OK) return false;
+    }
+}
+/* the payload of a flagged word as f32 */
+__device__ __forceinline__ float flag_payload(uint32_t w) { return __uint_as_float(w << 16); }
 
 /* Grid-wide barrier for a kernel whose CTAs are all resident (cooperative launch).
  * `counter` starts at 0 for the launch; the k-th barrier (k = 1, 2, ...) completes

@@ -42,6 +42,7 @@ struct s2p_model {
     /* persistent batch-1 tick: stage program in device memory, sync words, grid size */
     int mega_ok, mega_ctas, mega_n_stages, mega_built;
     int mega_barriers;          /* grid barriers of one tick */
+    int mega_logc_from, mega_loge_from; /* stages producing the sampler's logits */
     unsigned int mega_ticks;    /* persistent ticks issued so far */
     /* exchange arena (all buffers the persistent tick writes) and its mappings on the ranks of a
      * tensor-parallel group; tp_base[tp_rank] == tp_arena */

@@ -603,7 +603,7 @@ static int mega_gemv(const MegaLayout* lay, MegaStage* st, const s2p_linear* lin
 /* The buffers the persistent tick writes live in one allocation, the exchange arena, so that
  * tensor-parallel peers can address them at the same offsets in their mapping of it. */
 typedef struct {
-    s2p_dev_bf16 *x, *qkv, *attn, *ffn, *hidden, *logc, *loge, *fx, *fqkv, *fattn, *fhff, *flogits;
+    s2p_dev_bf16 *x, *qkv, *attn, *ffn, *hidden, *logc, *loge, *fx, *fqkv, *fattn, *fhff, *flogits, *logits_plain;
     unsigned long long* keys;
     unsigned int* barrier;
 } mega_arena;
@@ -614,18 +614,21 @@ static void arena_views(const s2p_model* m, mega_arena* a) {
 #define ARENA_TAKE(field, type, count) a->field = (type*)(p + off); off += (((size_t)(count) * sizeof(type)) + 255) & ~(size_t)255
     ARENA_TAKE(barrier, unsigned int, 1);
     ARENA_TAKE(keys, unsigned long long, 16);
-    ARENA_TAKE(x, s2p_dev_bf16, S2P_DIM);
-    ARENA_TAKE(qkv, s2p_dev_bf16, S2P_QKV_WIDTH);
-    ARENA_TAKE(attn, s2p_dev_bf16, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM);
-    ARENA_TAKE(ffn, s2p_dev_bf16, S2P_FFN_DIM);
+    /* flagged vectors: one 32-bit word (bf16 | tag << 16) per element */
+    ARENA_TAKE(x, s2p_dev_bf16, 2 * S2P_DIM);
+    ARENA_TAKE(qkv, s2p_dev_bf16, 2 * S2P_QKV_WIDTH);
+    ARENA_TAKE(attn, s2p_dev_bf16, 2 * S2P_SLOW_Q_HEADS * S2P_HEAD_DIM);
+    ARENA_TAKE(ffn, s2p_dev_bf16, 2 * S2P_FFN_DIM);
+    ARENA_TAKE(logc, s2p_dev_bf16, 2 * 4096);
+    ARENA_TAKE(loge, s2p_dev_bf16, 2 * 8);
+    ARENA_TAKE(fx, s2p_dev_bf16, 2 * S2P_DIM);
+    ARENA_TAKE(fqkv, s2p_dev_bf16, 2 * S2P_QKV_WIDTH);
+    ARENA_TAKE(fattn, s2p_dev_bf16, 2 * S2P_SLOW_Q_HEADS * S2P_HEAD_DIM);
+    ARENA_TAKE(fhff, s2p_dev_bf16, 2 * S2P_FFN_DIM);
+    /* plain bf16 */
     ARENA_TAKE(hidden, s2p_dev_bf16, S2P_DIM);
-    ARENA_TAKE(logc, s2p_dev_bf16, 4096);
-    ARENA_TAKE(loge, s2p_dev_bf16, 8);
-    ARENA_TAKE(fx, s2p_dev_bf16, S2P_DIM);
-    ARENA_TAKE(fqkv, s2p_dev_bf16, S2P_QKV_WIDTH);
-    ARENA_TAKE(fattn, s2p_dev_bf16, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM);
-    ARENA_TAKE(fhff, s2p_dev_bf16, S2P_FFN_DIM);
     ARENA_TAKE(flogits, s2p_dev_bf16, S2P_CB_SIZE);
+    ARENA_TAKE(logits_plain, s2p_dev_bf16, 4104);
 #undef ARENA_TAKE
     (void)off; /* < S2P_TP_ARENA_BYTES */
 }
@@ -654,21 +657,35 @@ static s2p_status mega_build(s2p_model* m) {
         }
         mega_layout(xb, &m->mega_lay);
     }
-    prog[n].type = MEGA_BEGIN; n++;
+    /* Stage outputs travel as flagged words (x_from = the producing stage); a grid barrier is
+     * kept only where plain memory is handed over: after the sampler (its token index) and after
+     * every arg-max stage (the packed keys). */
+    prog[n].type = MEGA_BEGIN; prog[n].flags = MEGA_NO_BARRIER; prog[n].x_from = -1; n++;
+    int last_x = 0, from;
     for (int l = 0; l < m->n_slow && ok; l++) {
         const s2p_layer* L = &m->slow[l];
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wqkv, 1, 0);
         st->x.base = A.x; st->norm_w = L->attn_norm.data; st->y = A.qkv;
+        st->x_from = last_x; st->io_flags = MEGA_Y_LL; st->flags = MEGA_NO_BARRIER;
+        from = n - 1;
         st = &prog[n++]; memset(st, 0, sizeof(*st));
         st->type = MEGA_ATTN_SLOW; st->qkv = A.qkv; st->q_norm = L->q_norm.data; st->k_norm = L->k_norm.data;
         st->out = A.attn; st->kv.bases = d.kv_bases; st->kv.sbases = d.kvs_bases;
+        st->x_from = from; st->flags = MEGA_NO_BARRIER;
         slow_kv_offsets(m, l, &st->kv);
+        from = n - 1;
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wo, 0, 1);
         st->x.base = A.attn; st->resid.base = A.x; st->y = A.x;
+        st->x_from = from; st->io_flags = MEGA_Y_LL | MEGA_RESID_LL; st->flags = MEGA_NO_BARRIER;
+        last_x = n - 1;
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->gate_up, 1, 2);
         st->x.base = A.x; st->norm_w = L->ffn_norm.data; st->y = A.ffn;
+        st->x_from = last_x; st->io_flags = MEGA_Y_LL; st->flags = MEGA_NO_BARRIER;
+        from = n - 1;
         st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->w2, 0, 1);
         st->x.base = A.ffn; st->resid.base = A.x; st->y = A.x;
+        st->x_from = from; st->io_flags = MEGA_Y_LL | MEGA_RESID_LL; st->flags = MEGA_NO_BARRIER;
+        last_x = n - 1;
     }
     /* tied head on the INT8 sidecar: the 4096 semantic rows, then the EOS row; the first of
      * the two also leaves the final-normed hidden state for the fast-AR */
@@ -686,9 +703,11 @@ static s2p_status mega_build(s2p_model* m) {
         if (((uintptr_t)st->lin.w & 15) || !m->embed_i8.data) ok = 0;
         st->x.base = A.x; st->norm_w = m->final_norm.data;
         st->y = part == 0 ? A.logc : A.loge;
-        if (part == 0) { st->normed_out = A.hidden; st->flags = MEGA_NO_BARRIER; }
+        st->x_from = last_x; st->io_flags = MEGA_Y_LL; st->flags = MEGA_NO_BARRIER; /* the sampler waits on the words */
+        if (part == 0) { st->normed_out = A.hidden; m->mega_logc_from = n - 1; }
+        else m->mega_loge_from = n - 1;
     }
-    st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_SAMPLE;
+    st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_SAMPLE; st->x_from = -1;
     for (int cb = 0; cb < S2P_NUM_CODEBOOKS && ok; cb++) {
         VecRef in;
         memset(&in, 0, sizeof(in));
@@ -701,27 +720,39 @@ static s2p_status mega_build(s2p_model* m) {
         VecRef fx;
         memset(&fx, 0, sizeof(fx));
         fx.base = A.fx;
+        int last_fx = -1; /* layer 0 of a pass reads a plain row (published by a barrier) */
         for (int l = 0; l < S2P_FAST_LAYERS && ok; l++) {
             const s2p_layer* L = &m->fast[l];
             const VecRef* src = l == 0 ? &in : &fx;
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wqkv, 1, 0);
             st->x = *src; st->norm_w = L->attn_norm.data; st->y = A.fqkv;
+            st->x_from = last_fx; st->io_flags = MEGA_Y_LL; st->flags = MEGA_NO_BARRIER;
+            from = n - 1;
             st = &prog[n++]; memset(st, 0, sizeof(*st));
             st->type = MEGA_ATTN_FAST; st->qkv = A.fqkv; st->out = A.fattn; st->pos = cb;
+            st->x_from = from; st->flags = MEGA_NO_BARRIER;
             fast_kv_ref(m, l, &st->kv);
+            from = n - 1;
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->wo, 0, 1);
             st->x.base = A.fattn; st->resid = *src; st->y = A.fx;
+            st->x_from = from; st->io_flags = MEGA_Y_LL | (l == 0 ? 0 : MEGA_RESID_LL); st->flags = MEGA_NO_BARRIER;
+            last_fx = n - 1;
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->gate_up, 1, 2);
             st->x = fx; st->norm_w = L->ffn_norm.data; st->y = A.fhff;
+            st->x_from = last_fx; st->io_flags = MEGA_Y_LL; st->flags = MEGA_NO_BARRIER;
+            from = n - 1;
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &L->w2, 0, 1);
             st->x.base = A.fhff; st->resid = fx; st->y = A.fx;
+            st->x_from = from; st->io_flags = MEGA_Y_LL | MEGA_RESID_LL; st->flags = MEGA_NO_BARRIER;
+            last_fx = n - 1;
         }
         if (cb > 0 && ok) {
             st = &prog[n++]; ok &= mega_gemv(&m->mega_lay, st, &m->fast_out, 1, 3);
             st->x = fx; st->norm_w = m->fast_norm.data; st->y = A.flogits; st->key = A.keys + (cb - 1);
+            st->x_from = last_fx; /* plain logits and packed keys out: the grid barrier stays */
         }
     }
-    st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_FINISH; st->flags = MEGA_NO_BARRIER;
+    st = &prog[n++]; memset(st, 0, sizeof(*st)); st->type = MEGA_FINISH; st->flags = MEGA_NO_BARRIER; st->x_from = -1;
     m->mega_built = 1;
     m->mega_barriers = 0;
     for (int i = 0; i < n; i++) m->mega_barriers += !(prog[i].flags & MEGA_NO_BARRIER);
@@ -832,6 +863,8 @@ static s2p_status tick_mega(s2p_model* m) {
     P.tp_rank = m->tp_rank; P.tp_world = m->tp_world;
     for (int r = 0; r < m->tp_world; r++) P.tp_base[r] = (unsigned char*)m->tp_base[r];
     P.bar_base = m->mega_ticks * (unsigned int)m->mega_barriers; /* wraps with the device counters */
+    P.seq_base = m->mega_ticks * (unsigned int)m->mega_n_stages;
+    P.logc_from = m->mega_logc_from; P.loge_from = m->mega_loge_from; P.logits_plain = A.logits_plain;
     m->mega_ticks++;
     if (!m->embed_i8_only) P.begin.embed = (const s2p_dev_bf16*)m->embed.data;
     P.begin.embed_i8 = (const int8_t*)m->embed_i8.data;

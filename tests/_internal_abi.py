@@ -19,7 +19,7 @@ class QkvPostArgs(C.Structure):
 class AttnArgs(C.Structure):
     _fields_ = [("q", _P), ("out", _P), ("q_heads", _I), ("kv_heads", _I), ("max_seq", _I), ("kv8", _I),
                 ("pos0", _I), ("pos_row_step", _I), ("pos_arr", _P), ("kv", KvRef), ("part", _P), ("counters", _P),
-                ("n_split_slots", _I), ("workers", _I), ("n_out_peers", _I), ("out_peer_delta", _P), ("head_dim", _I)]
+                ("n_split_slots", _I), ("workers", _I), ("n_out_peers", _I), ("out_peer_delta", _P), ("out_ll", _I), ("out_ll_tag", C.c_uint), ("head_dim", _I)]
 
 
 class SamplerState(C.Structure):
