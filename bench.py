@@ -238,17 +238,32 @@ def run_ours(args, rank, world):
     lib = capi.load_library()
     ctx_len = max(4096, ((args.prompt + args.steps + args.warmup + 64 + 63) // 64) * 64)
     eng, seed_used = None, args.seed
+    tp = bool(args.tp) and world > 1
+    if tp and args.batch != 1:
+        raise SystemExit("--tp shards the batch-1 tick")
+    who = 0 if tp else rank  # tensor-parallel ranks must issue identical calls: same prompt, same seed
     for attempt in range(8):  # a sampled EOS would end a session early: move to the next seed
         eng = Engine(lib, capi, ckpt, ctx_len, max(args.batch, 1))
-        rng = np.random.default_rng(1000 * rank + attempt)
+        if tp:  # exchange the arena handles and attach before any session exists
+            handle = (C.c_ubyte * 64)()
+            capi.check(lib.s2p_b200_model_tp_export(eng.m, handle), "s2p_b200_model_tp_export")
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+            allh = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(allh, mine)
+            blob = (C.c_ubyte * (64 * world))(*[int(v) for t in allh for v in t.cpu().tolist()])
+            capi.check(lib.s2p_b200_model_tp_attach(eng.m, rank, world, blob), "s2p_b200_model_tp_attach")
+            dist.barrier()
+        rng = np.random.default_rng(1000 * who + attempt)
         lens = [args.prompt] * args.batch if args.batch == 1 else list(rng.integers(256, 2049, size=args.batch))
-        prompts = [synth.random_prompt(int(n), 100 * rank + i) for i, n in enumerate(lens)]
-        eng.open_sessions(prompts, 0.8, 0.8, seed_used + 7919 * rank)
+        prompts = [synth.random_prompt(int(n), 100 * who + i) for i, n in enumerate(lens)]
+        eng.open_sessions(prompts, 0.8, 0.8, seed_used + 7919 * who)
         hit = eng.tick()  # first frame samples from the prefill state (not graph-captured)
         for _ in range(args.warmup):
             hit = hit or eng.tick()
         if not hit:
             break
+        if tp:
+            dist.barrier()  # no rank frees its arena while a peer's kernel may still store into it
         eng.close()
         seed_used += 1
     stats = capi.Stats()
@@ -275,6 +290,8 @@ def run_ours(args, rank, world):
         t = torch.tensor([step_wall, step_dev], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         step_wall, step_dev = float(t[0]), float(t[1])
+    if tp:
+        dist.barrier()
     if rank != 0:
         eng.close()
         return None
@@ -285,15 +302,15 @@ def run_ours(args, rank, world):
     traffic_model = algo + stats.kv_bytes_per_token * kv_tokens
     achieved = algo / (step_dev * 1e-3) / 1e9
     line = {
-        "metric": "decode ms/frame (B=%d)" % args.batch, "value": round(step_dev, 4), "unit": "ms/frame",
+        "metric": "decode ms/frame (B=%d)" % args.batch + (" TP=%d" % world if tp else ""), "value": round(step_dev, 4), "unit": "ms/frame",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_wall, 4),
-        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": args.mode,
+        "higher_is_better": False, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": args.mode,
         "data": "synthetic (seeded random-init checkpoint, uniform random prompt)",
         "config": {"workload": f"dual-AR decode, all-{args.mode.upper()} weights + INT8 KV, {args.layers}+4 layers, batch {args.batch} per GPU, "
                                f"{args.prompt}-token prompt, T=0.8 top-p=0.8 seed {seed_used}",
-                   "replicas": world, "ctx_len": ctx_len, "l2": "weights per frame (4.4-7.8 GB) exceed the 126 MB L2: every frame streams from HBM",
+                   "replicas": 1 if tp else world, "tensor_parallel": world if tp else 1, "ctx_len": ctx_len, "l2": "weights per frame (4.4-7.8 GB) exceed the 126 MB L2: every frame streams from HBM",
                    "eos_in_timed_region": bool(eos_in_timed)},
-        "frames_per_s": round(world * args.batch * 1e3 / step_wall, 1),
+        "frames_per_s": round((1 if tp else world) * args.batch * 1e3 / step_wall, 1),
         "e2e": {"value": round(step_wall, 4), "unit": "ms/frame", "h2d_bytes_per_step": int(stats.upload_bytes),
                 "d2h_bytes_per_step": int(stats.download_bytes)},
         "gpu_launches": int(stats.last_tick_kernels) * args.steps,
@@ -389,6 +406,8 @@ def main():
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-roofline", action="store_true")
+    ap.add_argument("--tp", action="store_true",
+                    help="with N > 1 ranks: one batch-1 session sharded over the N GPUs (tensor parallel) instead of N replicas")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

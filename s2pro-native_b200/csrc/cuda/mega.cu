@@ -656,6 +656,12 @@ extern "C" int mega_max_local_rows(const MegaLayout* lay, int K) {
     return fit < 2 * GEMV_WARPS ? fit : 2 * GEMV_WARPS; /* the fold takes two rows per warp */
 }
 
+/* host-side probe of the row partition (tests) */
+extern "C" void mega_geom_probe(int N, int swiglu, int rows_per_chunk, int cta, int n_cta, int out[4]) {
+    const MegaGeom g = mega_stage_geom(N, swiglu, rows_per_chunk, cta, n_cta);
+    out[0] = g.row0; out[1] = g.cnt; out[2] = g.rc; out[3] = g.n_chunks;
+}
+
 extern "C" cudaError_t mega_setup(int* n_cta_out) {
     cudaError_t e = cudaFuncSetAttribute(k_tick_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, MEGA_SMEM_MAX);
     if (e != cudaSuccess) return e;

@@ -241,6 +241,7 @@ typedef struct {
 /* layout for a model whose widest staged activation needs x_bytes */
 void mega_layout(int x_bytes, MegaLayout* out);
 int mega_max_local_rows(const MegaLayout* lay, int K); /* rows of one chunk the fold and the partial buffer can take */
+void mega_geom_probe(int N, int swiglu, int rows_per_chunk, int cta, int n_cta, int out[4]);
 cudaError_t mega_setup(int* n_cta_out);   /* once per device: attribute + occupancy check; grid size */
 cudaError_t mega_launch(const MegaParams* p, int n_cta, cudaStream_t st);
 
