@@ -416,6 +416,8 @@ def main():
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, which carries the one JSON line
         dist.init_process_group("nccl")
     line = (run_ours if args.impl == "ours" else run_reference)(args, rank, world)
     if line is not None:

@@ -168,32 +168,37 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         GemvStage g = {};
         g.K = K; g.x = s.x.base; g.x_index = s.x.index; g.x_key = s.x.key;
         g.norm_w = s.norm_w; g.eps = S2P_NORM_EPS; g.normed_out = s.normed_out;
-        if (s.x_from >= 0) {
-            /* the input arrives as flagged words from the CTAs (of all ranks) of stage x_from:
-             * wait for each word's tag instead of a grid barrier */
-            const uint4* xll = reinterpret_cast<const uint4*>(s.x.base);
-            const unsigned tag = (r.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
-            int* status = r.status;
-            auto load = [xll, tag, status, &ok](int v) -> uint4 {
-                uint4 a, b;
-                if (!flag_wait4(xll + 2 * v, tag, status, a) || !flag_wait4(xll + 2 * v + 1, tag, status, b)) {
-                    ok = false;
-                    return make_uint4(0, 0, 0, 0);
-                }
-                return make_uint4((a.x & 0xFFFFu) | (a.y << 16), (a.z & 0xFFFFu) | (a.w << 16), (b.x & 0xFFFFu) | (b.y << 16),
-                                  (b.z & 0xFFFFu) | (b.w << 16));
-            };
-            if (s.pro == PRO_NORM) stage_activation_from<WK, PRO_NORM>(g, load, xs, red, MEGA_WORKERS);
-            else stage_activation_from<WK, PRO_VEC>(g, load, xs, red, MEGA_WORKERS);
-        } else {
-            if (s.pro == PRO_NORM) stage_activation<WK, PRO_NORM>(g, xs, red, MEGA_WORKERS);
-            else stage_activation<WK, PRO_VEC>(g, xs, red, MEGA_WORKERS);
+        /* the input arrives as flagged words from the CTAs (of all ranks) of stage x_from - wait
+         * for each word's tag instead of a grid barrier - or is a plain bf16 row that an earlier
+         * grid barrier has published (x_from < 0) */
+        const bool ll = s.x_from >= 0;
+        const uint4* xsrc;
+        {
+            const __nv_bfloat16* x = s.x.base;
+            if (s.x.index) x += (size_t)__ldcg(s.x.index) * K;
+            else if (s.x.key) x += (size_t)key_index(__ldcg(s.x.key)) * K;
+            xsrc = reinterpret_cast<const uint4*>(x);
         }
+        const unsigned tag = (r.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
+        int* status = r.status;
+        auto load = [xsrc, ll, tag, status, &ok](int v) -> uint4 {
+            if (!ll) return __ldcg(xsrc + v);
+            uint4 a, b;
+            if (!flag_wait4(xsrc + 2 * v, tag, status, a) || !flag_wait4(xsrc + 2 * v + 1, tag, status, b)) {
+                ok = false;
+                return make_uint4(0, 0, 0, 0);
+            }
+            return make_uint4((a.x & 0xFFFFu) | (a.y << 16), (a.z & 0xFFFFu) | (a.w << 16), (b.x & 0xFFFFu) | (b.y << 16),
+                              (b.z & 0xFFFFu) | (b.w << 16));
+        };
+        if (s.pro == PRO_NORM) stage_activation_from<WK, PRO_NORM>(g, load, xs, red, MEGA_WORKERS);
+        else stage_activation_from<WK, PRO_VEC>(g, load, xs, red, MEGA_WORKERS);
     }
     if (!cta_sync_and(ok)) return false;
     if (trace && threadIdx.x == 0) trace[1] = clock64();
     unsigned long long best = 0ull;
     const unsigned q0 = r.consumed;
+    long long tacc[6] = {0, 0, 0, 0, 0, 0}; /* trace: cycles of thread 0 in stream wait, stream, fold wait, fold, fold chain, fold tree */
     const int pstride = T * 32;
 
     /* Every warp streams its share of each chunk's (row, tile) units into a partial buffer
@@ -221,6 +226,7 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         const int U = local_rows * T;
         int u = (int)((long long)U * warp / GEMV_WARPS);
         const int u_end = (int)((long long)U * (warp + 1) / GEMV_WARPS);
+#pragma unroll 1
         while (u < u_end) {
             const int tile = u / local_rows, lr0 = u - tile * local_rows;
             const int n = min(local_rows - lr0, u_end - u);
@@ -229,6 +235,7 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
             const unsigned char* wp = wsl + (size_t)lr0 * rb + (size_t)(tile * 32 + lane) * sizeof(tile_t);
             float* pp = part + ((size_t)lr0 * T + tile) * 32 + lane;
             int rr = 0;
+#pragma unroll 1
             for (; rr + 4 <= n; rr += 4) {
                 const tile_t t0 = *reinterpret_cast<const tile_t*>(wp);
                 const tile_t t1 = *reinterpret_cast<const tile_t*>(wp + rb);
@@ -257,7 +264,7 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         if (lane == 0) mbar_arrive(r.pfull + b); /* release: the partials are visible to whoever waits */
         if (trace && threadIdx.x == 0) {
             const long long c2 = clock64();
-            trace[4] += c1 - c0; trace[5] += c2 - c1;
+            tacc[0] += c1 - c0; tacc[1] += c2 - c1;
         }
         return true;
     };
@@ -310,7 +317,7 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
                 accB += __shfl_xor_sync(S2P_FULL_MASK, accB, off);
             }
             const long long f2 = trace ? clock64() : 0;
-            if (trace && threadIdx.x == 0) { trace[8] += f1 - c1; trace[9] += f2 - f1; }
+            if (trace && threadIdx.x == 0) { tacc[4] += f1 - c1; tacc[5] += f2 - f1; }
             if (WK == WK_INT8_CH) {
                 accA = __fmul_rn(accA, rscale_s[l0 + la]);
                 accB = __fmul_rn(accB, rscale_s[two ? ge.cnt + l0 + la : l0 + lb]);
@@ -339,22 +346,30 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
         if (lane == 0) mbar_arrive(r.pdone + b); /* this warp is done with the chunk's scales and partials */
         if (trace && threadIdx.x == 0) {
             const long long c2 = clock64();
-            trace[6] += c1 - c0; trace[7] += c2 - c1;
+            tacc[2] += c1 - c0; tacc[3] += c2 - c1;
         }
         return true;
     };
 
+    /* Odd warps alternate strictly (stream 0, fold 0, stream 1, fold 1, ...); even warps run one
+     * chunk ahead with the streaming (stream 0, stream 1, fold 0, stream 2, fold 1, ..., fold n-1).
+     * One loop over 2 n actions so that each body exists once in the kernel's code. */
     const bool fold_first = (warp & 1) != 0;
-    for (int j = 0; j < ge.n_chunks && ok; j++) {
-        if (fold_first) {
-            if (j > 0) ok = fold_chunk(j - 1);
-            if (ok) ok = stream_chunk(j);
-        } else {
-            ok = stream_chunk(j);
-            if (ok && j > 0) ok = fold_chunk(j - 1);
-        }
+    const int n = ge.n_chunks;
+#pragma unroll 1
+    for (int t = 0; t < 2 * n && ok; t++) {
+        bool do_stream;
+        int idx;
+        if (fold_first) { do_stream = !(t & 1); idx = t >> 1; }
+        else if (t == 0) { do_stream = true; idx = 0; }
+        else if (t & 1) { idx = (t + 1) >> 1; do_stream = idx < n; if (!do_stream) idx = n - 1; }
+        else { do_stream = false; idx = (t >> 1) - 1; }
+        ok = do_stream ? stream_chunk(idx) : fold_chunk(idx);
     }
-    if (ok) ok = fold_chunk(ge.n_chunks - 1);
+    if (trace && threadIdx.x == 0) {
+#pragma unroll
+        for (int i = 0; i < 6; i++) trace[4 + i] = (unsigned long long)tacc[i]; /* plain stores: no round trip on the traced path */
+    }
     if (s.epi == EPI_ARGMAX && lane == 0 && best) {
         atomicMax(s.key, best);
         for (int i = 0; i < g_tp.n; i++)
@@ -370,12 +385,9 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
 
 template <int WK>
 __device__ __forceinline__ bool gemv_dispatch_t(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
-    switch (s.lin.K) { /* the model's three input widths get fully unrolled tile loops */
-    case S2P_DIM: return gemv_chunks<WK, S2P_DIM / 512>(s, r, work, tr);
-    case S2P_SLOW_Q_HEADS * S2P_HEAD_DIM: return gemv_chunks<WK, S2P_SLOW_Q_HEADS * S2P_HEAD_DIM / 512>(s, r, work, tr);
-    case S2P_FFN_DIM: return gemv_chunks<WK, S2P_FFN_DIM / 512>(s, r, work, tr);
-    default: return gemv_chunks<WK, 0>(s, r, work, tr);
-    }
+    /* one body per weight kind (tile count at run time): the kernel's code has to stay within
+     * reach of the instruction caches, every stage switches between these bodies */
+    return gemv_chunks<WK, 0>(s, r, work, tr);
 }
 __device__ bool gemv_dispatch(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
     switch (s.lin.kind) {
@@ -553,7 +565,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         const MegaStage& s = st_buf[si & 1];
         stage_prefetch(si + 1); /* the other buffer held stage si - 1, which every thread has left */
         unsigned long long* tr = (P.trace && cta0) ? P.trace + (size_t)si * 16 : nullptr;
-        if (tr && tid == 0) { tr[0] = clock64(); tr[4] = tr[5] = tr[6] = tr[7] = tr[8] = tr[9] = 0; }
+        if (tr && tid == 0) { tr[0] = clock64(); }
         const unsigned my_tag = (P.seq_base + (unsigned)si + 1u) & 0xFFFFu;
         const unsigned in_tag = (P.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
         ring.tag = my_tag;
