@@ -988,7 +988,9 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
     S2P_CUDA_TRY(cudaEventRecord(m->ev1, st));
     S2P_CUDA_TRY(cudaStreamSynchronize(st));
     if (mega && *m->h_mega_status != 0) {
-        fprintf(stderr, "[s2pro] persistent tick kernel gave up on a bounded wait (code %d)\n", *m->h_mega_status);
+        fprintf(stderr, "[s2pro] persistent tick kernel gave up on a bounded wait (code %d); the frame is lost and later "
+                        "ticks use per-stage launches\n", *m->h_mega_status);
+        m->mega_ok = 0; /* its barrier counters and tags are no longer in step */
         return S2P_ERR_INTERNAL;
     }
     m->last_rows = nact; m->last_fused = fused; m->last_graph = steady; m->last_kernels = m->tick_kernels;
