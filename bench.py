@@ -48,7 +48,7 @@ def algorithmic_bytes_per_frame(mode, n_slow=36):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_tick_mega launch, from the ncu capture summarised in
 # profiles/k_tick_mega_int4_b1.md (36+4 layers, all-INT4, batch 1, ~540 cached positions)
-NCU_TRAFFIC_TICK_MEGA_INT4 = 4428316672
+NCU_TRAFFIC_TICK_MEGA_INT4 = 4426394112
 
 
 def ncu_traffic_per_launch(mode, layers, batch, stats):
@@ -148,6 +148,37 @@ class Engine:
         self.L.s2p_model_free(self.m)
 
 
+def stage_trace_summary(lib, model, sm_mhz):
+    """Per stage kind: microseconds CTA 0 spent staging its input (incl. waiting for it), working, and in the
+    stage-end synchronisation, from the SM-clock stamps of the last persistent tick."""
+    import numpy as np
+    cap = 1024
+    stamps = np.zeros((cap, 16), dtype=np.uint64)
+    kinds = np.zeros(cap, dtype=np.int32)
+    n = C.c_int(0)
+    rc = lib.s2p_b200_model_tick_trace(model, stamps.ctypes.data_as(C.c_void_p), kinds.ctypes.data_as(C.c_void_p), cap, C.byref(n))
+    if rc != 0:
+        return {"unavailable": int(rc)}
+    t = stamps[:n.value].astype(np.int64)
+    k = kinds[:n.value]
+    names = {0: "frame_start", 1: "gemv", 2: "attention_backbone", 3: "attention_fast", 4: "sampler", 5: "frame_end"}
+    us = 1.0 / sm_mhz
+    out = {"total_us": round(float(t[-1, 3] - t[0, 0]) * us, 1)}
+    for kind, name in names.items():
+        sel = t[k == kind]
+        if not len(sel):
+            continue
+        staged = np.where(sel[:, 1] > 0, sel[:, 1], sel[:, 0])
+        out[name] = {"stages": int(len(sel)), "input_us": round(float((staged - sel[:, 0]).sum()) * us, 1),
+                     "work_us": round(float((sel[:, 2] - staged).sum()) * us, 1),
+                     "sync_us": round(float((sel[:, 3] - sel[:, 2]).sum()) * us, 1)}
+    g = t[k == 1]
+    if len(g):
+        out["gemv_thread0"] = {"stream_wait_us": round(float(g[:, 4].sum()) * us, 1), "stream_us": round(float(g[:, 5].sum()) * us, 1),
+                               "fold_wait_us": round(float(g[:, 6].sum()) * us, 1), "fold_us": round(float(g[:, 7].sum()) * us, 1)}
+    return out
+
+
 def cpu_baseline(mode, seconds=12.0):
     """CPU port of the hot loop (oracle/, exact reference order) on a bounded sample:
     the four GEMVs of one backbone-shaped layer at batch 1, scaled to one frame."""
@@ -226,6 +257,8 @@ def run_ours(args, rank, world):
     capi = importlib.import_module("s2pro-native_b200.capi")
     synth = importlib.import_module("s2pro-native_b200.synth")
     set_mode_env(args.mode)
+    if args.stage_trace:
+        os.environ["S2P_TICK_TRACE"] = "1"
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     os.environ["S2P_DEVICE"] = str(local)
@@ -325,6 +358,8 @@ def run_ours(args, rank, world):
                      "algorithmic_bytes_per_frame": int(algo), "modelled_bytes_with_kv": int(traffic_model)},
         "clocks": sampler.summary(),
     }
+    if args.stage_trace:
+        line["stage_trace"] = stage_trace_summary(lib, eng.m, float(line["clocks"].get("sm_mhz") or 1965.0))
     eng.close()
     if not args.no_kernel_roofline:
         line["roofline_kernels"] = isolated_gemv_roofline(lib, torch, args.mode, peak)
@@ -406,6 +441,8 @@ def main():
     ap.add_argument("--seed", type=int, default=42)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-roofline", action="store_true")
+    ap.add_argument("--stage-trace", action="store_true",
+                    help="batch 1: add the persistent kernel's per-stage clock stamps (CTA 0) of the last frame, summed per stage kind")
     ap.add_argument("--tp", action="store_true",
                     help="with N > 1 ranks: one batch-1 session sharded over the N GPUs (tensor parallel) instead of N replicas")
     args = ap.parse_args()
