@@ -32,14 +32,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) k_gemv_stage(GemvStage g) {
     gemv_stage_cta<WK, PRO, EPI>(g, row0, cnt, smem);
 }
 
-/* Rows per pass that keep the CTA's shared memory within `budget` bytes. */
-int gemv_rows_per_pass(int wk, int rows_per_cta, int K, int gshift, int swiglu, size_t budget) {
+/* Rows per pass that keep the CTA's shared memory within `limit` bytes. */
+int gemv_rows_per_pass(int wk, int rows_per_cta, int K, int gshift, int swiglu, size_t limit) {
     int r = rows_per_cta;
-    while (r > 8 && gemv_smem_bytes(wk, r * (swiglu ? 2 : 1), K, gshift) > budget) r = (r + 1) / 2;
+    while (r > 8 && gemv_smem_bytes(wk, r * (swiglu ? 2 : 1), K, gshift) > limit) r = (r + 1) / 2;
     return r < 1 ? 1 : r;
 }
 
-constexpr size_t GEMV_SMEM_BUDGET = 200 * 1024;
+constexpr size_t GEMV_SMEM_LIMIT = 200 * 1024;
 
 /* Opt the kernel in to large dynamic shared memory, once per device. */
 template <int WK, int PRO, int EPI>
@@ -49,14 +49,14 @@ cudaError_t gemv_stage_setup() {
     cudaGetDevice(&dev);
     if (done_mask & (1 << (dev & 31))) return cudaSuccess;
     const cudaError_t e = cudaFuncSetAttribute(k_gemv_stage<WK, PRO, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)GEMV_SMEM_BUDGET);
+                                               (int)GEMV_SMEM_LIMIT);
     if (e == cudaSuccess) done_mask |= 1 << (dev & 31);
     return e;
 }
 
 template <int WK, int PRO, int EPI>
 cudaError_t launch_gemv_stage(GemvStage g, cudaStream_t stream) {
-    const size_t budget = GEMV_SMEM_BUDGET;
+    const size_t limit = GEMV_SMEM_LIMIT;
     {
         const cudaError_t e = gemv_stage_setup<WK, PRO, EPI>();
         if (e != cudaSuccess) return e;
@@ -65,7 +65,7 @@ cudaError_t launch_gemv_stage(GemvStage g, cudaStream_t stream) {
     int grid = device_sm_count();
     if (grid > units) grid = units;
     const int rows_per_cta = (units + grid - 1) / grid;
-    g.rows_per_pass = gemv_rows_per_pass(WK, rows_per_cta, g.K, g.gshift, EPI == EPI_SWIGLU, budget);
+    g.rows_per_pass = gemv_rows_per_pass(WK, rows_per_cta, g.K, g.gshift, EPI == EPI_SWIGLU, limit);
     const size_t smem = gemv_smem_bytes(WK, g.rows_per_pass * (EPI == EPI_SWIGLU ? 2 : 1), g.K, g.gshift);
     k_gemv_stage<WK, PRO, EPI><<<grid, GEMV_THREADS, smem, stream>>>(g);
     return cudaGetLastError();

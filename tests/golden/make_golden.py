@@ -2,9 +2,9 @@
 """Generates tests/golden/*.npz by IMPORTING the reference's own Python code
 (tools/qat_fastar.py: its bit-faithful port of the g32 quantiser, its INT8
 reference linear and its torch fast-AR model) and the reference's host sampler
-(src/slowar/sampling.c, compiled by oracle/Makefile into oracle/_ref).  Run in a
-container that has /root/reference; the outputs are committed so that the tests
-need neither.
+(src/slowar/sampling.c, compiled by oracle/Makefile into oracle/_ref).  Run where
+the reference checkout is available (S2P_REFERENCE points at it); the outputs are
+committed so that the tests need neither.
 
     python tests/golden/make_golden.py
 """
