@@ -219,6 +219,19 @@ s2p_status s2p_linear_prepare_int8_site(s2p_linear* lin, s2p_qsite site, cudaStr
  * is served in slices of 16 with results identical to one-row calls. */
 s2p_status s2p_linear_gemv_rows(const s2p_linear* lin, const void* x_bf16, void* y_bf16, int M, cudaStream_t stream) {
     const int N = lin->out_features, K = lin->in_features;
+    /* beyond the reference's 16-row GEMV the batch goes to the tensor cores in one launch
+     * (S2P_NO_TC=1 keeps the exact-order kernel, 16 rows at a time) */
+    if (M > S2P_INT8_GEMV_MAX_M && M <= 256 && K % 128 == 0 && !s2p_env_is_one("S2P_NO_TC") &&
+        (!lin->q_group || lin->q_group >= (lin->q_packed ? 32 : 16))) {
+        LinRef lr;
+        s2p_lin_ref(lin, &lr);
+        const cudaError_t ce = skinny_gemm_tc(&lr, x_bf16, M, y_bf16, stream);
+        if (ce != cudaSuccess) {
+            fprintf(stderr, "[s2pro] batched tensor-core linear (M=%d,N=%d,K=%d): %s\n", M, N, K, cudaGetErrorString(ce));
+            return S2P_ERR_CUDA;
+        }
+        return S2P_OK;
+    }
     for (int m0 = 0; m0 < M; m0 += S2P_INT8_GEMV_MAX_M) {
         const int mm = M - m0 < S2P_INT8_GEMV_MAX_M ? M - m0 : S2P_INT8_GEMV_MAX_M;
         const char* xs = (const char*)x_bf16 + (size_t)m0 * K * 2;

@@ -1,0 +1,55 @@
+"""The tensor-core batched decode linear (tcgen05, more than 16 rows) against the exact-order
+GEMV of this library, which is bit-identical to the reference's.  The two accumulate in
+different orders (and INT4 rounds code x scale to f16 once), so this is a tolerance check:
+bf16 outputs may differ by a rounding step, not more."""
+import ctypes as C
+
+import pytest
+
+from _internal_abi import LinRef
+from test_kernels_gpu import _quantised, dev, p, rnd
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+def exact(mine, kind, y, x, w, s, M, N, K):
+    for m0 in range(0, M, 16):
+        mm = min(16, M - m0)
+        ys, xs = y[m0:m0 + mm], x[m0:m0 + mm]
+        if kind == 0:
+            rc = mine.s2p_int8_gemv(p(ys), p(xs), p(w), p(s), mm, N, K, None)
+        elif kind == 1:
+            rc = mine.s2p_intq_gemv(p(ys), p(xs), p(w), p(s), mm, N, K, 32, None)
+        else:
+            rc = mine.s2p_int4p_gemv(p(ys), p(xs), p(w), p(s), mm, N, K, 32, None)
+        assert rc == 0
+
+
+@pytest.mark.parametrize("kind", [2, 0, 1])
+@pytest.mark.parametrize("M,N,K", [(32, 6144, 2560), (17, 2560, 4096), (128, 2560, 9728), (48, 4097, 2560), (256, 384, 512)])
+def test_tensor_core_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
+    dev()
+    testlib.skinny_gemm_tc.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    testlib.skinny_status.argtypes = [C.POINTER(C.c_int)]
+    w, s = _quantised(mine, N, K, kind, seed=11 + kind)
+    x = rnd(M, K, seed=5)
+    y_exact = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    y_tc = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    exact(mine, kind, y_exact, x, w, s, M, N, K)
+    lin = LinRef(kind, w.data_ptr(), s.data_ptr(), N, K, 0 if kind == 0 else 5)
+    assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y_tc), None) == 0
+    torch.cuda.synchronize()
+    st = C.c_int(-1)
+    assert testlib.skinny_status(C.byref(st)) == 0 and st.value == 0, "a bounded wait inside the kernel gave up"
+    a, b = y_tc.float(), y_exact.float()
+    assert torch.isfinite(a).all()
+    scale = float(b.abs().max())
+    diff = (a - b).abs()
+    mag = torch.maximum(a.abs(), b.abs()).clamp_min(2.0 ** -20)
+    step = torch.exp2(torch.floor(torch.log2(mag)) - 7)  # one bf16 step at that magnitude
+    # one rounding step of the output, plus the accumulated f16 rounding of code x scale (INT4 / grouped INT8)
+    assert bool((diff <= step + 2e-3 * scale).all()), f"max diff {float(diff.max())} at scale {scale}"
+    assert float((diff == 0).float().mean()) >= 0.8, "most outputs should round to the same bf16"
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+    assert float(cos) >= 0.99999
