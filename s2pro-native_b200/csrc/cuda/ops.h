@@ -131,6 +131,7 @@ cudaError_t gemv_setup_all(void); /* once per device, before any stream capture 
 /* batched decode linear on the tensor cores (skinny.cu): y[M, N] = x[M, K] · W^T, 1 <= M <= 256 */
 cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st);
 cudaError_t skinny_status(int* out);
+cudaError_t skinny_setup(int max_rows); /* once per device, outside stream capture: scratch for split-K launches */
 
 /* ---- persistent batch-1 decode tick (mega.cu) --------------------------------
  * The whole frame is one cooperative kernel that walks a list of stages; a grid

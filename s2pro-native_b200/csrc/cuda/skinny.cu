@@ -77,9 +77,12 @@ __device__ __forceinline__ uint4 sk_int8_chunk(uint32_t w0, uint32_t w1, __half2
 }
 
 template <int WK>
-__global__ void __launch_bounds__(SK_THREADS, 1) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
+__global__ void __launch_bounds__(SK_THREADS, 2) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
                                                              int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
-                                                             int NB, __nv_bfloat16* __restrict__ y) {
+                                                             int NB, __nv_bfloat16* __restrict__ y, float* __restrict__ partial,
+                                                             unsigned* __restrict__ arrivals) {
+    /* gridDim.y > 1: the K range is split over gridDim.y CTAs per row tile; each leaves its f32 partial in
+     * `partial`[split][batch row][weight row] and the last one to arrive adds them in split order */
     int* status = &g_sk_status;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int b_bytes = NB * SK_KC * 2;
@@ -109,49 +112,54 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_skinny_tc(const void* __restr
     /* instruction descriptor: D f32, A and B f16, both K-major, N = NB, M = 128 */
     const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(SK_BM >> 4) << 24);
 
-    const int nk = K / SK_KC;
+    const int nk_all = K / SK_KC, KS = gridDim.y, ks = blockIdx.y;
+    const int it_first = (int)((long long)nk_all * ks / KS), nk = (int)((long long)nk_all * (ks + 1) / KS) - it_first;
     bool ok = true;
+    /* this thread's packed words and scales of a slab, fetched one slab ahead (the global loads of
+     * slab i + 1 are in flight while slab i is converted and multiplied) */
+    constexpr int NLD = (WK == WK_INT4_PACK) ? 2 : 4;          /* 16-byte loads per thread per slab */
+    constexpr int WPL = (WK == WK_INT4_PACK) ? 32 : 16;        /* weights per load */
+    uint4 pk[NLD];
+    __half2 sc[NLD];
+    auto fetch = [&](int it) {
+        const int k0 = (it_first + it) * SK_KC;
+#pragma unroll
+        for (int i = 0; i < NLD; i++) {
+            const int idx = tid + SK_THREADS * i, row = idx & (SK_BM - 1), q = idx >> 7;
+            const int grow = n0 + row;
+            pk[i] = make_uint4(0, 0, 0, 0);
+            sc[i] = __float2half2_rn(WK == WK_INT4_PACK ? 0.f : 1.f);
+            if (grow < N) {
+                const int kq = k0 + q * WPL;
+                pk[i] = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(w) + (size_t)grow * row_bytes +
+                                                        (WK == WK_INT4_PACK ? (kq >> 1) : kq));
+                if (WK != WK_INT8_CH)
+                    sc[i] = __half2half2(static_cast<const __half*>(scales)[(size_t)grow * (K >> gshift) + (kq >> gshift)]);
+            }
+        }
+    };
+    fetch(0);
     for (int it = 0; it < nk && ok; it++) {
         const int s = it & 1;
         if (it >= 2) ok = mbar_wait_bounded(done + s, ((unsigned)(it >> 1) - 1u) & 1u, status); /* the MMAs that read this stage */
         if (!ok) break;
-        const int k0 = it * SK_KC;
+        const int k0 = (it_first + it) * SK_KC;
         uint4* A = reinterpret_cast<uint4*>(stage_a[s]);
         uint4* B = reinterpret_cast<uint4*>(stage_b[s]);
-        /* weights: A[k / 8][row] */
-        if (WK == WK_INT4_PACK) {
+        /* weights: A[k / 8][row] (rows beyond N: zero scale / zero codes) */
 #pragma unroll
-            for (int i = 0; i < 2; i++) {
-                const int idx = tid + SK_THREADS * i, row = idx & (SK_BM - 1), q = idx >> 7; /* q: which 32 weights of the slab */
-                const int grow = n0 + row;
-                uint4 pk = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u); /* code 0 */
-                __half2 sc2 = __float2half2_rn(0.f);
-                if (grow < N) {
-                    pk = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(w) + (size_t)grow * row_bytes +
-                                                         ((k0 + q * 32) >> 1));
-                    const __half sc = static_cast<const __half*>(scales)[(size_t)grow * (K >> gshift) + ((k0 + q * 32) >> gshift)];
-                    sc2 = __half2half2(sc);
-                }
-                const uint32_t ws[4] = {pk.x, pk.y, pk.z, pk.w};
+        for (int i = 0; i < NLD; i++) {
+            const int idx = tid + SK_THREADS * i, row = idx & (SK_BM - 1), q = idx >> 7;
+            if (WK == WK_INT4_PACK) {
+                const uint32_t ws[4] = {pk[i].x, pk[i].y, pk[i].z, pk[i].w};
 #pragma unroll
-                for (int j = 0; j < 4; j++) A[(q * 4 + j) * SK_BM + row] = sk_int4_chunk(ws[j], sc2);
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int idx = tid + SK_THREADS * i, row = idx & (SK_BM - 1), q = idx >> 7; /* q: which 16 codes of the slab */
-                const int grow = n0 + row;
-                uint4 pk = make_uint4(0, 0, 0, 0);
-                __half2 sc2 = __float2half2_rn(1.f);
-                if (grow < N) {
-                    pk = *reinterpret_cast<const uint4*>(static_cast<const unsigned char*>(w) + (size_t)grow * row_bytes + k0 + q * 16);
-                    if (WK == WK_INT8_GRP)
-                        sc2 = __half2half2(static_cast<const __half*>(scales)[(size_t)grow * (K >> gshift) + ((k0 + q * 16) >> gshift)]);
-                }
-                A[(q * 2) * SK_BM + row] = sk_int8_chunk<WK == WK_INT8_GRP>(pk.x, pk.y, sc2);
-                A[(q * 2 + 1) * SK_BM + row] = sk_int8_chunk<WK == WK_INT8_GRP>(pk.z, pk.w, sc2);
+                for (int j = 0; j < 4; j++) A[(q * 4 + j) * SK_BM + row] = sk_int4_chunk(ws[j], sc[i]);
+            } else {
+                A[(q * 2) * SK_BM + row] = sk_int8_chunk<WK == WK_INT8_GRP>(pk[i].x, pk[i].y, sc[i]);
+                A[(q * 2 + 1) * SK_BM + row] = sk_int8_chunk<WK == WK_INT8_GRP>(pk[i].z, pk[i].w, sc[i]);
             }
         }
+        if (it + 1 < nk) fetch(it + 1);
         /* activations: B[k / 8][batch row], rows beyond the batch are zero */
         for (int c = tid; c < NB * (SK_KC / 8); c += SK_THREADS) {
             const int n = c % NB, kc = c / NB;
@@ -212,9 +220,31 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_skinny_tc(const void* __restr
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     const int m = col0 + j;
-                    if (m < M) y[(size_t)m * N + grow] = f2bf(__fmul_rn(__uint_as_float(v[j]), rs));
+                    if (m < M) {
+                        if (KS == 1) y[(size_t)m * N + grow] = f2bf(__fmul_rn(__uint_as_float(v[j]), rs));
+                        else partial[((size_t)ks * M + m) * N + grow] = __uint_as_float(v[j]);
+                    }
                 }
             }
+        }
+    }
+    if (KS > 1) {
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = ok && (atomicAdd(arrivals + blockIdx.x, 1u) == (unsigned)(KS - 1));
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            for (int e = tid; e < SK_BM * M; e += SK_THREADS) {
+                const int m = e / SK_BM, grow = n0 + (e % SK_BM);
+                if (grow >= N) continue;
+                float acc = 0.f;
+                for (int q = 0; q < KS; q++) acc += __ldcg(partial + ((size_t)q * M + m) * N + grow);
+                if (WK == WK_INT8_CH) acc = __fmul_rn(acc, static_cast<const float*>(scales)[grow]);
+                y[(size_t)m * N + grow] = f2bf(acc);
+            }
+            if (tid == 0) arrivals[blockIdx.x] = 0u;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -223,6 +253,32 @@ __global__ void __launch_bounds__(SK_THREADS, 1) k_skinny_tc(const void* __restr
 }
 
 static size_t sk_smem_bytes(int NB) { return 2 * ((size_t)SK_A_BYTES + (size_t)NB * SK_KC * 2) + 64; }
+
+/* scratch for split-K launches: partials [SK_MAX_SPLIT][rows][SK_SPLIT_MAX_N] f32 and one arrival counter per row tile */
+constexpr int SK_MAX_SPLIT = 8;
+constexpr int SK_SPLIT_MAX_N = 6144;
+static float* g_partial[64];
+static unsigned* g_arrivals[64];
+static int g_partial_rows[64];
+
+/* once per device, outside stream capture: room for split-K launches with up to `max_rows` batch rows */
+extern "C" cudaError_t skinny_setup(int max_rows) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || max_rows < 1) return cudaErrorInvalidValue;
+    if (g_partial_rows[dev] >= max_rows) return cudaSuccess;
+    if (g_partial[dev]) cudaFree(g_partial[dev]);
+    g_partial[dev] = nullptr;
+    g_partial_rows[dev] = 0;
+    if ((e = cudaMalloc((void**)&g_partial[dev], (size_t)SK_MAX_SPLIT * max_rows * SK_SPLIT_MAX_N * sizeof(float))) != cudaSuccess) return e;
+    if (!g_arrivals[dev]) {
+        if ((e = cudaMalloc((void**)&g_arrivals[dev], 256 * sizeof(unsigned))) != cudaSuccess) return e;
+        if ((e = cudaMemset(g_arrivals[dev], 0, 256 * sizeof(unsigned))) != cudaSuccess) return e;
+    }
+    g_partial_rows[dev] = max_rows;
+    return cudaSuccess;
+}
 
 template <int WK>
 static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st) {
@@ -234,8 +290,20 @@ static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, c
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    k_skinny_tc<WK><<<(lin->N + SK_BM - 1) / SK_BM, SK_THREADS, smem, st>>>(lin->w, lin->scales, lin->N, lin->K, lin->gshift,
-                                                                           (const __nv_bfloat16*)x, M, NB, (__nv_bfloat16*)y);
+    const int tiles = (lin->N + SK_BM - 1) / SK_BM;
+    int dev = 0, split = 1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    /* few row tiles and a long K: split K over several CTAs so the whole GPU streams the matrix */
+    if (dev >= 0 && dev < 64 && g_partial_rows[dev] >= M && lin->N <= SK_SPLIT_MAX_N && tiles <= 74 && tiles <= 256) {
+        split = 148 / tiles;
+        if (split > SK_MAX_SPLIT) split = SK_MAX_SPLIT;
+        if (split > lin->K / SK_KC) split = lin->K / SK_KC;
+        if (split < 1) split = 1;
+    }
+    k_skinny_tc<WK><<<dim3((unsigned)tiles, (unsigned)split), SK_THREADS, smem, st>>>(
+        lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, NB, (__nv_bfloat16*)y,
+        split > 1 ? g_partial[dev] : nullptr, split > 1 ? g_arrivals[dev] : nullptr);
     return cudaGetLastError();
 }
 

@@ -142,8 +142,10 @@ static s2p_status lin_apply(s2p_model* m, const s2p_linear* lin, const void* x, 
     return s2p_linear_forward(lin, x, y, rows, m->mode, m->stream);
 }
 
+/* CTAs per (row, kv head) of the split-K decode attention: enough CTAs in total (about 2048) that a
+ * long context is walked by several workers even when the batch alone would fill the GPU */
 static int attn_workers_for(int rows) {
-    int w = 296 / (rows * S2P_SLOW_KV_HEADS);
+    int w = 2048 / (rows * S2P_SLOW_KV_HEADS);
     return w < 1 ? 1 : (w > 16 ? 16 : w);
 }
 

@@ -38,18 +38,30 @@ def test_tensor_core_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
     y_tc = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
     exact(mine, kind, y_exact, x, w, s, M, N, K)
     lin = LinRef(kind, w.data_ptr(), s.data_ptr(), N, K, 0 if kind == 0 else 5)
-    assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y_tc), None) == 0
-    torch.cuda.synchronize()
-    st = C.c_int(-1)
-    assert testlib.skinny_status(C.byref(st)) == 0 and st.value == 0, "a bounded wait inside the kernel gave up"
-    a, b = y_tc.float(), y_exact.float()
-    assert torch.isfinite(a).all()
-    scale = float(b.abs().max())
-    diff = (a - b).abs()
-    mag = torch.maximum(a.abs(), b.abs()).clamp_min(2.0 ** -20)
-    step = torch.exp2(torch.floor(torch.log2(mag)) - 7)  # one bf16 step at that magnitude
-    # one rounding step of the output, plus the accumulated f16 rounding of code x scale (INT4 / grouped INT8)
-    assert bool((diff <= step + 2e-3 * scale).all()), f"max diff {float(diff.max())} at scale {scale}"
-    assert float((diff == 0).float().mean()) >= 0.8, "most outputs should round to the same bf16"
-    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
-    assert float(cos) >= 0.99999
+    testlib.skinny_setup.argtypes = [C.c_int]
+    a0 = None
+    for with_split_scratch in (False, True):  # single pass over K, then K split over several CTAs where rows are few
+        if with_split_scratch:
+            assert testlib.skinny_setup(256) == 0
+        y_tc.fill_(float("nan"))
+        assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y_tc), None) == 0
+        torch.cuda.synchronize()
+        st = C.c_int(-1)
+        assert testlib.skinny_status(C.byref(st)) == 0 and st.value == 0, "a bounded wait inside the kernel gave up"
+        a, b = y_tc.float(), y_exact.float()
+        assert torch.isfinite(a).all()
+        scale = float(b.abs().max())
+        diff = (a - b).abs()
+        mag = torch.maximum(a.abs(), b.abs()).clamp_min(2.0 ** -20)
+        step = torch.exp2(torch.floor(torch.log2(mag)) - 7)  # one bf16 step at that magnitude
+        # one rounding step of the output, plus the accumulated f16 rounding of code x scale (INT4 / grouped INT8)
+        assert bool((diff <= step + 2e-3 * scale).all()), f"max diff {float(diff.max())} at scale {scale}"
+        assert float((diff == 0).float().mean()) >= 0.8, "most outputs should round to the same bf16"
+        cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+        assert float(cos) >= 0.99999
+        # the same launch again gives the same bits (the split partials are added in a fixed order)
+        y2 = torch.empty_like(y_tc)
+        assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y2), None) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(y2.view(torch.int16), y_tc.view(torch.int16))
+        a0 = a
