@@ -138,7 +138,30 @@ __global__ void __launch_bounds__(SK_THREADS, 2) k_skinny_tc(const void* __restr
             }
         }
     };
+    /* the first two 16-byte units of this thread's share of the activation slab travel with them
+     * (that is the whole share for batches up to 32 rows) */
+    uint4 xb[2];
+    auto fetch_x = [&](int it) {
+        const int k0 = (it_first + it) * SK_KC;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int c = tid + SK_THREADS * i, n = c % NB, kc = c / NB;
+            xb[i] = make_uint4(0, 0, 0, 0);
+            if (c < NB * (SK_KC / 8) && n < M) xb[i] = *reinterpret_cast<const uint4*>(x + (size_t)n * K + k0 + kc * 8);
+        }
+    };
+    auto to_f16 = [](const uint4& v) -> uint4 {
+        const uint32_t vs[4] = {v.x, v.y, v.z, v.w};
+        uint32_t os[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __half2 h = __floats2half2_rn(bf_lo(vs[j]), bf_hi(vs[j]));
+            os[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        return make_uint4(os[0], os[1], os[2], os[3]);
+    };
     fetch(0);
+    fetch_x(0);
     for (int it = 0; it < nk && ok; it++) {
         const int s = it & 1;
         if (it >= 2) ok = mbar_wait_bounded(done + s, ((unsigned)(it >> 1) - 1u) & 1u, status); /* the MMAs that read this stage */
@@ -160,23 +183,19 @@ __global__ void __launch_bounds__(SK_THREADS, 2) k_skinny_tc(const void* __restr
             }
         }
         if (it + 1 < nk) fetch(it + 1);
-        /* activations: B[k / 8][batch row], rows beyond the batch are zero */
-        for (int c = tid; c < NB * (SK_KC / 8); c += SK_THREADS) {
+        /* activations: B[k / 8][batch row], rows beyond the batch are zero (bf16 zero = f16 zero) */
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int c = tid + SK_THREADS * i;
+            if (c < NB * (SK_KC / 8)) B[(c / NB) * NB + (c % NB)] = to_f16(xb[i]);
+        }
+        for (int c = tid + 2 * SK_THREADS; c < NB * (SK_KC / 8); c += SK_THREADS) {
             const int n = c % NB, kc = c / NB;
             uint4 o = make_uint4(0, 0, 0, 0);
-            if (n < M) {
-                const uint4 v = *reinterpret_cast<const uint4*>(x + (size_t)n * K + k0 + kc * 8);
-                const uint32_t vs[4] = {v.x, v.y, v.z, v.w};
-                uint32_t os[4];
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const __half2 h = __floats2half2_rn(bf_lo(vs[j]), bf_hi(vs[j]));
-                    os[j] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-                o = make_uint4(os[0], os[1], os[2], os[3]);
-            }
+            if (n < M) o = to_f16(*reinterpret_cast<const uint4*>(x + (size_t)n * K + k0 + kc * 8));
             B[kc * NB + n] = o;
         }
+        if (it + 1 < nk) fetch_x(it + 1);
         fence_proxy_async_smem(); /* these generic-proxy stores are read by the tensor core (async proxy) */
         __syncthreads();
         if (tid == 0) {
