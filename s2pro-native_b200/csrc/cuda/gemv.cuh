@@ -29,9 +29,7 @@
  *  - the activation vector is staged once per CTA in shared memory in the lane
  *    order the units read it (bf16 pairs for INT4, f32 for INT8);
  *  - activations, residuals and indices written by other SMs are read with
- *    L1-bypassing loads, so the same code is correct inside a persistent kernel;
- *  - a CTA can prefetch its slice of the NEXT stage's weights into L2 while it
- *    waits at a stage boundary (weight addresses never depend on activations).
+ *    L1-bypassing loads, so the same code is correct inside a persistent kernel.
  */
 #pragma once
 #include "common.cuh"
@@ -261,27 +259,6 @@ __device__ __forceinline__ void stage_activation(const GemvStage& g, unsigned ch
     else if (g.x_key) x += (size_t)key_index(__ldcg(g.x_key)) * g.K;
     const uint4* xsrc = reinterpret_cast<const uint4*>(x);
     stage_activation_from<WK, PRO>(g, [xsrc](int v) { return __ldcg(xsrc + v); }, xs, red, nthreads);
-}
-
-/* Ask L2 for this CTA's slice of a stage's weights and scales (no registers held,
- * nothing waits on it). */
-template <int WK, int EPI>
-__device__ __forceinline__ void gemv_prefetch_l2(const GemvStage& g, int row0, int cnt) {
-    if (cnt <= 0) return;
-    const size_t row_bytes = (WK == WK_INT4_PACK) ? (size_t)(g.K >> 1) : (size_t)g.K;
-    const size_t sc_row = (WK == WK_INT8_CH) ? 4 : (size_t)(g.K >> g.gshift) * 2;
-    const int regions = (EPI == EPI_SWIGLU) ? 2 : 1;
-    for (int r = 0; r < regions; r++) {
-        const size_t first = (size_t)row0 + (r ? (size_t)(g.N >> 1) : 0);
-        const char* wp = static_cast<const char*>(g.w) + first * row_bytes;
-        const size_t wlines = ((size_t)cnt * row_bytes + 127) >> 7;
-        for (size_t i = threadIdx.x; i < wlines; i += blockDim.x)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(wp + (i << 7)));
-        const char* sp = static_cast<const char*>(g.scales) + first * sc_row;
-        const size_t slines = ((size_t)cnt * sc_row + 127) >> 7;
-        for (size_t i = threadIdx.x; i < slines; i += blockDim.x)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(sp + (i << 7)));
-    }
 }
 
 /* ---- the stage ------------------------------------------------------------

@@ -102,30 +102,8 @@ __device__ __forceinline__ bool flag_wait4(const uint4* p, unsigned tag, int* st
 /* the payload of a flagged word as f32 */
 __device__ __forceinline__ float flag_payload(uint32_t w) { return __uint_as_float(w << 16); }
 
-/* Grid-wide barrier for a kernel whose CTAs are all resident (cooperative launch).
- * `counter` starts at 0 for the launch; the k-th barrier (k = 1, 2, ...) completes
- * when it reaches k * n_cta.  Called by every thread of the CTA. */
-__device__ __forceinline__ bool grid_barrier(unsigned* counter, unsigned target, int* status) {
-    __shared__ int ok_s;
-    S2P_CTA_SYNC();
-    if (threadIdx.x == 0) {
-        int ok = 1;
-        /* release: publishes this CTA's stores (ordered before it by the CTA barrier above) */
-        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
-        unsigned spins = 0, seen;
-        for (;;) {
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-            if (seen >= target) break;
-            if (++spins > PIPE_GRID_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_GRID_BARRIER); ok = 0; break; }
-            if ((spins & 255u) == 0u && status_peek(status) != PIPE_OK) { ok = 0; break; }
-        }
-        ok_s = ok && status_peek(status) == PIPE_OK;
-    }
-    S2P_CTA_SYNC();
-    return ok_s != 0;
-}
-
-/* The same barrier across the persistent kernels of several GPUs: thread 0 of every CTA
+/* Grid-wide barrier of a persistent kernel whose CTAs are all resident (cooperative launch),
+ * also across the persistent kernels of several GPUs: thread 0 of every CTA
  * publishes its CTA's stores system-wide and adds one to the counter in the own exchange arena
  * and in every peer's (the same cell, peer_delta[i] bytes away), then polls the own counter.
  * The counters are never reset: `target` is the running total (barriers so far, this one
