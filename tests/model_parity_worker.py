@@ -131,6 +131,25 @@ def main():
     o1, _ = run(L, s1, 4); o2, _ = run(L, s2, 4)
     result["chunked_prefill_same_frames"] = o1 == o2
     L.s2p_session_destroy(s1); L.s2p_session_destroy(s2)
+    # KV-prefix reuse (the scheduler's prefix cache, src/sched/scheduler.c:384-391): save the cache of a prompt prefix,
+    # load it into a fresh session, prefill only the rest; frames must equal a full prefill, here and in the reference
+    k = (2 * prompt_len) // 3
+    prefix_frames = {}
+    for name in ("ref", "persistent"):
+        L, m = models[name]
+        sa = session(L, m, 0.8, 7); prefill(L, sa, ids[:k])
+        blob = kvblob(L, m, sa, k)
+        sb = session(L, m, 0.8, 7)
+        rc = L.s2p_session_kv_load(sb, C.c_void_p(blob.data_ptr()), k)
+        assert rc == 0, rc
+        prefill(L, sb, ids[k:])
+        sc = session(L, m, 0.8, 7); prefill(L, sc, ids)
+        ob, _ = run(L, sb, 6); oc, _ = run(L, sc, 6)
+        prefix_frames[name] = (ob, oc)
+        for x in (sa, sb, sc):
+            L.s2p_session_destroy(x)
+    result["kv_prefix_equals_full_prefill"] = prefix_frames["persistent"][0] == prefix_frames["persistent"][1]
+    result["kv_prefix_equals_reference"] = prefix_frames["persistent"][0] == prefix_frames["ref"][0]
     print("RESULT " + json.dumps(result))
 
 

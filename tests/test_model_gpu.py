@@ -40,6 +40,8 @@ def check(res):
             assert run["general"]["tick"][1] == 0
     assert res["batch3_identical"] == 12
     assert res["chunked_prefill_same_frames"]
+    assert res["kv_prefix_equals_full_prefill"], "kv_save -> kv_load -> prefill of the rest differs from a full prefill"
+    assert res["kv_prefix_equals_reference"], "prefix-reuse frames differ from the reference's"
 
 
 @pytest.mark.parametrize("mode", ["int8", "int4"])
