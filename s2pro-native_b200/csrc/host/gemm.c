@@ -220,8 +220,16 @@ s2p_status s2p_linear_prepare_int8_site(s2p_linear* lin, s2p_qsite site, cudaStr
 s2p_status s2p_linear_gemv_rows(const s2p_linear* lin, const void* x_bf16, void* y_bf16, int M, cudaStream_t stream) {
     const int N = lin->out_features, K = lin->in_features;
     /* beyond the reference's 16-row GEMV the batch goes to the tensor cores in one launch
-     * (S2P_NO_TC=1 keeps the exact-order kernel, 16 rows at a time) */
-    if (M > S2P_INT8_GEMV_MAX_M && M <= 256 && K % 128 == 0 && !s2p_env_is_one("S2P_NO_TC") &&
+     * (S2P_NO_TC=1 keeps the exact-order kernel, 16 rows at a time; S2P_TC_MIN_ROWS=n, 2 <= n <= 16,
+     * sends batches of n rows and more there too, giving up bit-equality with the reference's
+     * batched GEMV for them) */
+    static int tc_min_rows = 0;
+    if (!tc_min_rows) {
+        const char* e = getenv("S2P_TC_MIN_ROWS");
+        const int v = e ? atoi(e) : 0;
+        tc_min_rows = (v >= 2 && v <= S2P_INT8_GEMV_MAX_M) ? v : S2P_INT8_GEMV_MAX_M + 1;
+    }
+    if (M >= tc_min_rows && M <= 256 && K % 128 == 0 && !s2p_env_is_one("S2P_NO_TC") &&
         (!lin->q_group || lin->q_group >= (lin->q_packed ? 32 : 16))) {
         LinRef lr;
         s2p_lin_ref(lin, &lr);

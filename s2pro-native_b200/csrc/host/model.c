@@ -234,7 +234,7 @@ s2p_status s2p_model_load(const char* model_dir, const s2p_model_opts* opts, s2p
     s2p_qcache* qc = NULL;
     if ((rc = s2p_gemm_init(m->ctx_len)) != S2P_OK) goto fail;
     if (gemv_setup_all() != cudaSuccess) { rc = S2P_ERR_CUDA; goto fail; }
-    if (m->max_sessions > S2P_INT8_GEMV_MAX_M && skinny_setup(m->max_sessions) != cudaSuccess) { rc = S2P_ERR_OOM; goto fail; }
+    if (m->max_sessions > 1 && skinny_setup(m->max_sessions) != cudaSuccess) { rc = S2P_ERR_OOM; goto fail; }
     if (m->fused_b1 && !s2p_env_is_one("S2P_NO_MEGA")) {
         if (mega_setup(&m->mega_ctas) == cudaSuccess && cudaMalloc(&m->tp_arena, S2P_TP_ARENA_BYTES) == cudaSuccess &&
             cudaMemset(m->tp_arena, 0, S2P_TP_ARENA_BYTES) == cudaSuccess) {
