@@ -135,7 +135,11 @@ template <int WK, int TT> /* TT: K / 512 known at compile time (loops unroll), o
 __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* trace) {
     typedef typename LaneTile<WK>::type tile_t;
     const MegaGeom ge = mega_stage_geom(s.lin.N, s.epi == EPI_SWIGLU, s.rows_per_chunk, r.cta, r.n_cta);
-    if (ge.cnt <= 0) return true; /* uniform over the CTA */
+    if (ge.cnt <= 0) { /* uniform over the CTA; leave as a GEMV stage always does: copies landed, warps together */
+        asm volatile("cp.async.wait_all;" ::: "memory");
+        S2P_CTA_SYNC();
+        return true;
+    }
     const int K = s.lin.K, T = TT ? TT : (K >> 9), gshift = s.lin.gshift;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int SW = (s.epi == EPI_SWIGLU) ? 2 : 1;
@@ -376,7 +380,9 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
             atomicMax_system(reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(s.key) + g_tp.delta[i]), best);
     }
     r.consumed = q0 + (unsigned)ge.n_chunks;
-    /* a warp that gave up skipped its remaining chunks: everyone leaves with the same verdict */
+    /* a warp that gave up skipped its remaining chunks: everyone leaves with the same verdict.  The
+     * barrier also publishes the next stage's descriptor (staged by asynchronous copies). */
+    asm volatile("cp.async.wait_all;" ::: "memory");
     if (!cta_sync_and(ok)) return false;
     /* every chunk so far is folded by every warp: all their slots are free */
     if (threadIdx.x == MEGA_ISSUER) ring_issue_upto(r, r.consumed + MEGA_SLOTS);
@@ -563,6 +569,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
     bool ok = true;
     for (int si = 0; si < P.n_stages && ok; si++) {
         const MegaStage& s = st_buf[si & 1];
+        /* what is needed after the stage's last barrier is read now: past that barrier a faster
+         * thread may already be staging stage si + 2 over this descriptor */
+        const int no_barrier = s.flags & MEGA_NO_BARRIER, stage_type = s.type;
         stage_prefetch(si + 1); /* the other buffer held stage si - 1, which every thread has left */
         unsigned long long* tr = (P.trace && cta0) ? P.trace + (size_t)si * 16 : nullptr;
         if (tr && tid == 0) { tr[0] = clock64(); }
@@ -635,10 +644,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
             P.trace[(size_t)P.n_stages * 16 + (size_t)si * n_local + blockIdx.x] = gt;
         }
         asm volatile("cp.async.wait_all;" ::: "memory"); /* the next descriptor; the barrier below publishes it */
-        const int no_barrier = s.flags & MEGA_NO_BARRIER;
         /* without a grid barrier the next stage still reuses the work area: wait for this
          * CTA's slowest warp */
-        if (no_barrier) S2P_CTA_SYNC();
+        if (no_barrier && stage_type != MEGA_GEMV) S2P_CTA_SYNC(); /* a GEMV stage ends with its own barrier */
         if (ok && !no_barrier) {
             n_bar++;
             ok = grid_barrier_tp(P.barrier, g_tp.delta, g_tp.n, (P.bar_base + n_bar) * (unsigned)n_cta, P.status);

@@ -129,7 +129,7 @@ cudaError_t tick_finish_keys(const unsigned long long* keys, int rows, int32_t* 
 cudaError_t gemv_setup_all(void); /* once per device, before any stream capture */
 
 /* batched decode linear on the tensor cores (skinny.cu): y[M, N] = x[M, K] · W^T, 1 <= M <= 256 */
-cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st);
+cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st);
 cudaError_t skinny_status(int* out);
 cudaError_t skinny_setup(int max_rows); /* once per device, outside stream capture: scratch for split-K launches */
 

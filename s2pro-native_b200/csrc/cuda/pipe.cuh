@@ -13,7 +13,7 @@ namespace s2p {
 enum PipeError { PIPE_OK = 0, PIPE_ERR_TMA_WAIT = 1, PIPE_ERR_GRID_BARRIER = 2, PIPE_ERR_FLAG_WAIT = 3 };
 
 constexpr unsigned PIPE_MBAR_TRIES = 1u << 20;   /* each try_wait already blocks for a hardware time slice */
-constexpr unsigned PIPE_GRID_SPINS = 1u << 22;   /* a few seconds of polling an L2 word */
+constexpr unsigned PIPE_GRID_SPINS = 1u << 23;   /* a few seconds of polling an L2 word */
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -67,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
  * and no separate flag are involved.  Tags count stage instances modulo 65536; every
  * cell is rewritten at least once per frame (a few hundred stage instances), so a
  * stale word can never carry the expected tag. */
-constexpr unsigned PIPE_FLAG_SPINS = 1u << 21;
+constexpr unsigned PIPE_FLAG_SPINS = 1u << 23; /* a few seconds of polling: long enough for a peer GPU whose host was descheduled */
 
 __device__ __forceinline__ uint32_t flag_word(__nv_bfloat16 v, unsigned tag) {
     return (uint32_t)__bfloat16_as_ushort(v) | (tag << 16);

@@ -16,8 +16,8 @@ constexpr int SMP_TOPK = 30;
 
 template <int NT> struct SamplerSmem {
     float cand[SMP_N_CAND];
-    float wv[NT / 32];
-    int wi[NT / 32];
+    float wtop_v[(NT / 32) * SMP_TOPK];  /* every warp's own top-30 */
+    int wtop_i[(NT / 32) * SMP_TOPK];
     float tv[SMP_TOPK];
     int ti[SMP_TOPK];
     float sh_temp, sh_topp;
@@ -47,8 +47,6 @@ __device__ void sampler_cta(const __nv_bfloat16* lrow, const __nv_bfloat16* eos_
     constexpr int SMP_THREADS = NT;
     constexpr int SMP_PER_THREAD = (SMP_N_CAND + NT - 1) / NT;
     float* cand = sm.cand;
-    float* wv = sm.wv;
-    int* wi = sm.wi;
     float* tv = sm.tv;
     int* ti = sm.ti;
     float& sh_temp = sm.sh_temp;
@@ -98,42 +96,73 @@ __device__ void sampler_cta(const __nv_bfloat16* lrow, const __nv_bfloat16* eos_
     }
     S2P_CTA_SYNC();
 
-    /* top-30: candidates i = tid + 256 j live in registers */
-    float mine[SMP_PER_THREAD];
-#pragma unroll
-    for (int j = 0; j < SMP_PER_THREAD; j++) {
-        const int i = tid + j * SMP_THREADS;
-        mine[j] = i < SMP_N_CAND ? cand[i] : -INFINITY;
-    }
-    for (int k = 0; k < SMP_TOPK; k++) {
-        float bv = -INFINITY;
-        int bi = SMP_N_CAND;
+    /* top-30 in two warp-level passes without block-wide rounds: every warp selects the 30 best of
+     * its own candidates (i = tid + NT j, held in registers) with shuffles only; warp 0 then selects
+     * the 30 best of the warps' winners.  (value desc, index asc) is a total order, so the result
+     * is the block-wide top-30 in order. */
+    const int lane = tid & 31, warp = tid >> 5;
+    constexpr int NW = SMP_THREADS / 32;
+    float* wtv = sm.wtop_v;
+    int* wti = sm.wtop_i;
+    {
+        float mine[SMP_PER_THREAD];
 #pragma unroll
         for (int j = 0; j < SMP_PER_THREAD; j++) {
             const int i = tid + j * SMP_THREADS;
-            if (i < SMP_N_CAND && better(mine[j], i, bv, bi)) { bv = mine[j]; bi = i; }
+            mine[j] = i < SMP_N_CAND ? cand[i] : -INFINITY;
         }
+        for (int k = 0; k < SMP_TOPK; k++) {
+            float bv = -INFINITY;
+            int bi = SMP_N_CAND;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ov = __shfl_xor_sync(S2P_FULL_MASK, bv, off);
-            const int oi = __shfl_xor_sync(S2P_FULL_MASK, bi, off);
-            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            for (int j = 0; j < SMP_PER_THREAD; j++) {
+                const int i = tid + j * SMP_THREADS;
+                if (i < SMP_N_CAND && better(mine[j], i, bv, bi)) { bv = mine[j]; bi = i; }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(S2P_FULL_MASK, bv, off);
+                const int oi = __shfl_xor_sync(S2P_FULL_MASK, bi, off);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) { wtv[warp * SMP_TOPK + k] = bv; wti[warp * SMP_TOPK + k] = bi; }
+            if (bi < SMP_N_CAND && (bi % SMP_THREADS) == tid) { /* the owner retires the winner */
+#pragma unroll
+                for (int j = 0; j < SMP_PER_THREAD; j++)
+                    if (tid + j * SMP_THREADS == bi) mine[j] = -INFINITY;
+            }
         }
-        if ((tid & 31) == 0) { wv[tid >> 5] = bv; wi[tid >> 5] = bi; }
-        S2P_CTA_SYNC();
-        bv = wv[0]; bi = wi[0];
-#pragma unroll
-        for (int w = 1; w < SMP_THREADS / 32; w++)
-            if (better(wv[w], wi[w], bv, bi)) { bv = wv[w]; bi = wi[w]; }
-        if (tid == 0) { tv[k] = bv; ti[k] = bi; }
-        /* the owner retires the winner */
-        if (bi < SMP_N_CAND && (bi % SMP_THREADS) == tid) {
-#pragma unroll
-            for (int j = 0; j < SMP_PER_THREAD; j++)
-                if (tid + j * SMP_THREADS == bi) mine[j] = -INFINITY;
-        }
-        S2P_CTA_SYNC();
     }
+    S2P_CTA_SYNC();
+    if (warp == 0) {
+        constexpr int PER2 = (NW * SMP_TOPK + 31) / 32;
+        float v2[PER2];
+        int i2[PER2];
+#pragma unroll
+        for (int j = 0; j < PER2; j++) {
+            const int e = lane + 32 * j;
+            v2[j] = e < NW * SMP_TOPK ? wtv[e] : -INFINITY;
+            i2[j] = e < NW * SMP_TOPK ? wti[e] : SMP_N_CAND;
+        }
+        for (int k = 0; k < SMP_TOPK; k++) {
+            float bv = -INFINITY;
+            int bi = SMP_N_CAND;
+#pragma unroll
+            for (int j = 0; j < PER2; j++)
+                if (i2[j] < SMP_N_CAND && better(v2[j], i2[j], bv, bi)) { bv = v2[j]; bi = i2[j]; }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(S2P_FULL_MASK, bv, off);
+                const int oi = __shfl_xor_sync(S2P_FULL_MASK, bi, off);
+                if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+            }
+            if (lane == 0) { tv[k] = bv; ti[k] = bi; }
+#pragma unroll
+            for (int j = 0; j < PER2; j++)
+                if (i2[j] == bi) i2[j] = SMP_N_CAND; /* retired: an index never matches again */
+        }
+    }
+    S2P_CTA_SYNC();
     if (tid == 0) {
     int choice = 0;
     if (!greedy) {

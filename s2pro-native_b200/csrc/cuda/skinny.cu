@@ -79,8 +79,9 @@ __device__ __forceinline__ uint4 sk_int8_chunk(uint32_t w0, uint32_t w1, __half2
 template <int WK>
 __global__ void __launch_bounds__(SK_THREADS, 2) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
                                                              int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
-                                                             int NB, __nv_bfloat16* __restrict__ y, float* __restrict__ partial,
-                                                             unsigned* __restrict__ arrivals) {
+                                                             int NB, __nv_bfloat16* y, const __nv_bfloat16* resid,
+                                                             float* __restrict__ partial, unsigned* __restrict__ arrivals) {
+    /* resid (may alias y): y = bf16(f32(resid) + f32(bf16(product))), the residual add of the decode layers */
     /* gridDim.y > 1: the K range is split over gridDim.y CTAs per row tile; each leaves its f32 partial in
      * `partial`[split][batch row][weight row] and the last one to arrive adds them in split order */
     int* status = &g_sk_status;
@@ -240,7 +241,11 @@ __global__ void __launch_bounds__(SK_THREADS, 2) k_skinny_tc(const void* __restr
                 for (int j = 0; j < 32; j++) {
                     const int m = col0 + j;
                     if (m < M) {
-                        if (KS == 1) y[(size_t)m * N + grow] = f2bf(__fmul_rn(__uint_as_float(v[j]), rs));
+                        if (KS == 1) {
+                            __nv_bfloat16 o = f2bf(__fmul_rn(__uint_as_float(v[j]), rs));
+                            if (resid) o = f2bf(__fadd_rn(bf2f(resid[(size_t)m * N + grow]), bf2f(o)));
+                            y[(size_t)m * N + grow] = o;
+                        }
                         else partial[((size_t)ks * M + m) * N + grow] = __uint_as_float(v[j]);
                     }
                 }
@@ -261,7 +266,9 @@ __global__ void __launch_bounds__(SK_THREADS, 2) k_skinny_tc(const void* __restr
                 float acc = 0.f;
                 for (int q = 0; q < KS; q++) acc += __ldcg(partial + ((size_t)q * M + m) * N + grow);
                 if (WK == WK_INT8_CH) acc = __fmul_rn(acc, static_cast<const float*>(scales)[grow]);
-                y[(size_t)m * N + grow] = f2bf(acc);
+                __nv_bfloat16 o = f2bf(acc);
+                if (resid) o = f2bf(__fadd_rn(bf2f(resid[(size_t)m * N + grow]), bf2f(o)));
+                y[(size_t)m * N + grow] = o;
             }
             if (tid == 0) arrivals[blockIdx.x] = 0u;
         }
@@ -300,7 +307,7 @@ extern "C" cudaError_t skinny_setup(int max_rows) {
 }
 
 template <int WK>
-static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st) {
+static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
     const int NB = (M + 15) & ~15;
     const size_t smem = sk_smem_bytes(NB);
     static bool attr_set = false;
@@ -322,19 +329,19 @@ static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, c
     }
     k_skinny_tc<WK><<<dim3((unsigned)tiles, (unsigned)split), SK_THREADS, smem, st>>>(
         lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, NB, (__nv_bfloat16*)y,
-        split > 1 ? g_partial[dev] : nullptr, split > 1 ? g_arrivals[dev] : nullptr);
+        (const __nv_bfloat16*)resid, split > 1 ? g_partial[dev] : nullptr, split > 1 ? g_arrivals[dev] : nullptr);
     return cudaGetLastError();
 }
 
-/* y[M, N] (bf16) = x[M, K] (bf16) · W^T for 1 <= M <= 256.  K must be a multiple of 128, the
- * group size of grouped kinds at least 32 (INT4) / 16 (INT8 codes). */
-extern "C" cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st) {
+/* y[M, N] (bf16) = x[M, K] (bf16) · W^T for 1 <= M <= 256, plus `resid` [M, N] when given (it may be y
+ * itself).  K must be a multiple of 128, the group size of grouped kinds at least 32 (INT4) / 16 (INT8 codes). */
+extern "C" cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
     if (!lin || !x || !y || M < 1 || M > 256 || lin->K % SK_KC) return cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)lin->w) & 15) return cudaErrorInvalidValue;
     switch (lin->kind) {
-    case WK_INT8_CH: return sk_launch<WK_INT8_CH>(lin, x, M, y, st);
-    case WK_INT8_GRP: return lin->gshift >= 4 ? sk_launch<WK_INT8_GRP>(lin, x, M, y, st) : cudaErrorInvalidValue;
-    case WK_INT4_PACK: return lin->gshift >= 5 ? sk_launch<WK_INT4_PACK>(lin, x, M, y, st) : cudaErrorInvalidValue;
+    case WK_INT8_CH: return sk_launch<WK_INT8_CH>(lin, x, M, y, resid, st);
+    case WK_INT8_GRP: return lin->gshift >= 4 ? sk_launch<WK_INT8_GRP>(lin, x, M, y, resid, st) : cudaErrorInvalidValue;
+    case WK_INT4_PACK: return lin->gshift >= 5 ? sk_launch<WK_INT4_PACK>(lin, x, M, y, resid, st) : cudaErrorInvalidValue;
     }
     return cudaErrorInvalidValue;
 }

@@ -217,23 +217,43 @@ s2p_status s2p_linear_prepare_int8_site(s2p_linear* lin, s2p_qsite site, cudaStr
 
 /* GEMV for decode-sized M of any count: rows are independent products, so M > 16
  * is served in slices of 16 with results identical to one-row calls. */
-s2p_status s2p_linear_gemv_rows(const s2p_linear* lin, const void* x_bf16, void* y_bf16, int M, cudaStream_t stream) {
-    const int N = lin->out_features, K = lin->in_features;
-    /* beyond the reference's 16-row GEMV the batch goes to the tensor cores in one launch
-     * (S2P_NO_TC=1 keeps the exact-order kernel, 16 rows at a time; S2P_TC_MIN_ROWS=n, 2 <= n <= 16,
-     * sends batches of n rows and more there too, giving up bit-equality with the reference's
-     * batched GEMV for them) */
+/* 1 when M decode rows of this linear go to the tensor-core kernel */
+int s2p_linear_rows_on_tc(const s2p_linear* lin, int M) {
+    const int K = lin->in_features;
     static int tc_min_rows = 0;
     if (!tc_min_rows) {
         const char* e = getenv("S2P_TC_MIN_ROWS");
         const int v = e ? atoi(e) : 0;
         tc_min_rows = (v >= 2 && v <= S2P_INT8_GEMV_MAX_M) ? v : S2P_INT8_GEMV_MAX_M + 1;
     }
-    if (M >= tc_min_rows && M <= 256 && K % 128 == 0 && !s2p_env_is_one("S2P_NO_TC") &&
-        (!lin->q_group || lin->q_group >= (lin->q_packed ? 32 : 16))) {
+    return M >= tc_min_rows && M <= 256 && K % 128 == 0 && !s2p_env_is_one("S2P_NO_TC") &&
+           (!lin->q_group || lin->q_group >= (lin->q_packed ? 32 : 16));
+}
+
+/* y += x · Wᵀ in one launch (the residual add of a decode layer fused into the batched linear); only
+ * where s2p_linear_rows_on_tc says so */
+s2p_status s2p_linear_tc_add(const s2p_linear* lin, const void* x_bf16, void* y_inout_bf16, int M, cudaStream_t stream) {
+    LinRef lr;
+    s2p_lin_ref(lin, &lr);
+    const cudaError_t ce = skinny_gemm_tc(&lr, x_bf16, M, y_inout_bf16, y_inout_bf16, stream);
+    if (ce != cudaSuccess) {
+        fprintf(stderr, "[s2pro] batched tensor-core linear (M=%d,N=%d,K=%d): %s\n", M, lin->out_features, lin->in_features,
+                cudaGetErrorString(ce));
+        return S2P_ERR_CUDA;
+    }
+    return S2P_OK;
+}
+
+s2p_status s2p_linear_gemv_rows(const s2p_linear* lin, const void* x_bf16, void* y_bf16, int M, cudaStream_t stream) {
+    const int N = lin->out_features, K = lin->in_features;
+    /* beyond the reference's 16-row GEMV the batch goes to the tensor cores in one launch
+     * (S2P_NO_TC=1 keeps the exact-order kernel, 16 rows at a time; S2P_TC_MIN_ROWS=n, 2 <= n <= 16,
+     * sends batches of n rows and more there too, giving up bit-equality with the reference's
+     * batched GEMV for them) */
+    if (s2p_linear_rows_on_tc(lin, M)) {
         LinRef lr;
         s2p_lin_ref(lin, &lr);
-        const cudaError_t ce = skinny_gemm_tc(&lr, x_bf16, M, y_bf16, stream);
+        const cudaError_t ce = skinny_gemm_tc(&lr, x_bf16, M, y_bf16, NULL, stream);
         if (ce != cudaSuccess) {
             fprintf(stderr, "[s2pro] batched tensor-core linear (M=%d,N=%d,K=%d): %s\n", M, N, K, cudaGetErrorString(ce));
             return S2P_ERR_CUDA;

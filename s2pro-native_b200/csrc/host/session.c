@@ -137,13 +137,25 @@ typedef struct {
 } layer_ctx;
 
 static s2p_status lin_apply(s2p_model* m, const s2p_linear* lin, const void* x, void* y, int rows, int decode) {
-    m->tick_kernels += decode ? (rows + S2P_INT8_GEMV_MAX_M - 1) / S2P_INT8_GEMV_MAX_M : 2;
+    m->tick_kernels += !decode ? 2 : (m->mode == S2P_GEMM_INT8 && lin->int8_ready && s2p_linear_rows_on_tc(lin, rows))
+                                         ? 1 : (rows + S2P_INT8_GEMV_MAX_M - 1) / S2P_INT8_GEMV_MAX_M;
     if (decode && m->mode == S2P_GEMM_INT8 && lin->int8_ready) return s2p_linear_gemv_rows(lin, x, y, rows, m->stream);
     return s2p_linear_forward(lin, x, y, rows, m->mode, m->stream);
 }
 
 /* CTAs per (row, kv head) of the split-K decode attention: enough CTAs in total (about 2048) that a
  * long context is walked by several workers even when the batch alone would fill the GPU */
+/* x += in · Wᵀ: one launch where the batch runs on the tensor cores, else linear into `proj` and the add kernel */
+static s2p_status lin_add(s2p_model* m, const s2p_linear* lin, const void* in, void* x, void* proj, int rows, int decode) {
+    if (decode && m->mode == S2P_GEMM_INT8 && lin->int8_ready && s2p_linear_rows_on_tc(lin, rows)) {
+        m->tick_kernels += 1;
+        return s2p_linear_tc_add(lin, in, x, rows, m->stream);
+    }
+    S2P_TRY(lin_apply(m, lin, in, proj, rows, decode));
+    S2P_LAUNCH(m, add_inplace(x, proj, (int64_t)rows * lin->out_features, m->stream));
+    return S2P_OK;
+}
+
 static int attn_workers_for(int rows) {
     int w = 2048 / (rows * S2P_SLOW_KV_HEADS);
     return w < 1 ? 1 : (w > 16 ? 16 : w);
@@ -178,13 +190,11 @@ static s2p_status layer_general(s2p_model* m, const s2p_layer* L, const layer_ct
     } else {
         S2P_LAUNCH(m, attn_single(&aa, rows, st));
     }
-    S2P_TRY(lin_apply(m, &L->wo, attn, proj, rows, c->decode));
-    S2P_LAUNCH(m, add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
+    S2P_TRY(lin_add(m, &L->wo, attn, x, proj, rows, c->decode));
     S2P_LAUNCH(m, rms_norm(x, L->ffn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
     S2P_TRY(lin_apply(m, &L->gate_up, norm, gu, rows, c->decode));
     S2P_LAUNCH(m, silu_mul(gu, hff, rows, S2P_FFN_DIM, st));
-    S2P_TRY(lin_apply(m, &L->w2, hff, proj, rows, c->decode));
-    S2P_LAUNCH(m, add_inplace(x, proj, (int64_t)rows * S2P_DIM, st));
+    S2P_TRY(lin_add(m, &L->w2, hff, x, proj, rows, c->decode));
     return S2P_OK;
 }
 

@@ -30,7 +30,7 @@ def exact(mine, kind, y, x, w, s, M, N, K):
 @pytest.mark.parametrize("M,N,K", [(32, 6144, 2560), (17, 2560, 4096), (128, 2560, 9728), (48, 4097, 2560), (256, 384, 512)])
 def test_tensor_core_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
     dev()
-    testlib.skinny_gemm_tc.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    testlib.skinny_gemm_tc.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
     testlib.skinny_status.argtypes = [C.POINTER(C.c_int)]
     w, s = _quantised(mine, N, K, kind, seed=11 + kind)
     x = rnd(M, K, seed=5)
@@ -44,7 +44,7 @@ def test_tensor_core_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
         if with_split_scratch:
             assert testlib.skinny_setup(256) == 0
         y_tc.fill_(float("nan"))
-        assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y_tc), None) == 0
+        assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y_tc), None, None) == 0
         torch.cuda.synchronize()
         st = C.c_int(-1)
         assert testlib.skinny_status(C.byref(st)) == 0 and st.value == 0, "a bounded wait inside the kernel gave up"
@@ -61,7 +61,14 @@ def test_tensor_core_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
         assert float(cos) >= 0.99999
         # the same launch again gives the same bits (the split partials are added in a fixed order)
         y2 = torch.empty_like(y_tc)
-        assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y2), None) == 0
+        assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y2), None, None) == 0
         torch.cuda.synchronize()
         assert torch.equal(y2.view(torch.int16), y_tc.view(torch.int16))
+        # fused residual add, in place: y = bf16(f32(r) + f32(bf16(product)))
+        r = rnd(M, N, seed=77)
+        y3 = r.clone()
+        assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(y3), p(y3), None) == 0
+        torch.cuda.synchronize()
+        want = (r.float() + y_tc.float()).to(torch.bfloat16)
+        assert torch.equal(y3.view(torch.int16), want.view(torch.int16))
         a0 = a
