@@ -327,6 +327,8 @@ def run_ours(args, rank, world):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
+    if args.profile_region:
+        torch.cuda.profiler.start()
     t0 = time.perf_counter()
     eos_in_timed = False
     for _ in range(args.steps):
@@ -335,6 +337,8 @@ def run_ours(args, rank, world):
         dev_ms.append(stats.last_tick_device_ms)
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
+    if args.profile_region:
+        torch.cuda.profiler.stop()
     sampler.stop_flag = True
     sampler.join(timeout=2)
     lib.s2p_b200_model_stats(eng.m, C.byref(stats))
@@ -437,7 +441,7 @@ def run_reference(args, rank, world):
         eng.close()
         base.update({"value": round(step, 4), "ms_per_step": round(step, 4),
                      "config": {"workload": f"dual-AR decode, all-{args.mode.upper()} weights + INT8 KV, {args.layers}+4 layers, batch {args.batch}, "
-                                            (f"{args.prompt}-token prompt" if args.batch == 1 else f"prompts 256-2048 tokens after a shared {args.shared_prefix}-token KV prefix") + f", T=0.8 top-p=0.8 seed {seed_used}",
+                                            + (f"{args.prompt}-token prompt" if args.batch == 1 else f"prompts 256-2048 tokens after a shared {args.shared_prefix}-token KV prefix") + f", T=0.8 top-p=0.8 seed {seed_used}",
                                 "arm": "reference CUDA path rebuilt unchanged for sm_100a (oracle/_ref), same GPU, same API calls"},
                      "cpu_baseline": {"value": round(step, 4), "unit": "ms/frame", "cores": 1, "kind": "reference",
                                       "sample": "the reference has no CPU decode path; this is its CUDA path on the GPU, one host thread issuing"},
@@ -464,6 +468,8 @@ def main():
                     help="batch > 1: tokens of a KV prefix prefilled once and loaded into every session (0 = none)")
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--seed", type=int, default=42)
+    ap.add_argument("--profile-region", action="store_true",
+                    help="bracket the timed steps with the CUDA profiler start/stop calls (for ncu --profile-from-start off)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernel-roofline", action="store_true")
     ap.add_argument("--stage-trace", action="store_true",

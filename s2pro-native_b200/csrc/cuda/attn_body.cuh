@@ -20,8 +20,9 @@ template <bool KV8> struct AttnSmem {
     alignas(16) unsigned char vtile[64 * TS];  /* V rows of the split */
     alignas(8) __half ssc[64 * 4];             /* their group scales (INT8 cache) */
     alignas(8) __half vssc[64 * 4];
-    float sq[4][128];
+    alignas(16) float sq[4][128];
     float sc[4][64];
+    alignas(16) float scv[64 * 4 * 4];         /* [position][value group][head]: probability x value scale */
     float red[4][128];
     float hm[4], hs[4];
     int s_last;
@@ -168,20 +169,33 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
         if (tid < 256 && t4 < cnt) {
             d = 0.f;
             if (!KV8) {
-                const __nv_bfloat162* kr = reinterpret_cast<const __nv_bfloat162*>(tile + t4 * TS);
+                const uint32_t* kw = reinterpret_cast<const uint32_t*>(tile + t4 * TS);
+                const float4* q4 = reinterpret_cast<const float4*>(sq[g4]);
 #pragma unroll 8
-                for (int e = 0; e < 64; e++) {
-                    const float2 kf = __bfloat1622float2(kr[e]);
-                    d = __fmaf_rn(sq[g4][2 * e], kf.x, d);
-                    d = __fmaf_rn(sq[g4][2 * e + 1], kf.y, d);
+                for (int e = 0; e < 32; e++) {
+                    const uint32_t w0 = kw[2 * e], w1 = kw[2 * e + 1];
+                    const float4 qv = q4[e];
+                    d = __fmaf_rn(qv.x, bf_lo(w0), d);
+                    d = __fmaf_rn(qv.y, bf_hi(w0), d);
+                    d = __fmaf_rn(qv.z, bf_lo(w1), d);
+                    d = __fmaf_rn(qv.w, bf_hi(w1), d);
                 }
             } else {
-                const int8_t* kr = reinterpret_cast<const int8_t*>(tile + t4 * TS);
+                /* four codes per shared-memory word, four query values per load; the chain order is unchanged */
+                const uint32_t* kw = reinterpret_cast<const uint32_t*>(tile + t4 * TS);
+                const float4* q4 = reinterpret_cast<const float4*>(sq[g4]);
 #pragma unroll
                 for (int gi = 0; gi < 4; gi++) {
                     float pp = 0.f;
-#pragma unroll 8
-                    for (int e = 0; e < 32; e++) pp = __fmaf_rn(sq[g4][gi * 32 + e], (float)kr[gi * 32 + e], pp);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const uint32_t w = kw[gi * 8 + e];
+                        const float4 qv = q4[gi * 8 + e];
+                        pp = __fmaf_rn(qv.x, (float)(int8_t)(w & 0xFFu), pp);
+                        pp = __fmaf_rn(qv.y, (float)(int8_t)((w >> 8) & 0xFFu), pp);
+                        pp = __fmaf_rn(qv.z, (float)(int8_t)((w >> 16) & 0xFFu), pp);
+                        pp = __fmaf_rn(qv.w, (float)(int8_t)(w >> 24), pp);
+                    }
                     d = __fmaf_rn(pp, __half2float(ssc[t4 * 4 + gi]), d);
                 }
             }
@@ -201,21 +215,34 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
             const float x = warp_tree_sum(sc[g4][t4] + sc[g4][t4 + 32]);
             if (t4 == 0) { hm[g4] = m; hs[g4] = x; }
         }
+        /* meanwhile the weights of the value sum, per (position, value group, head): the probability,
+         * for the INT8 cache times the group's scale (the product the value chain multiplies by) */
+        for (int i = tid; i < 64 * 4 * 4; i += 512) {
+            const int g = i & 3, grp = (i >> 2) & 3, j = i >> 4;
+            sm.scv[i] = KV8 ? __fmul_rn(sc[g][j], __half2float(vssc[j * 4 + grp])) : sc[g][j];
+        }
         S2P_CTA_SYNC();
-        {
-            const int g = tid >> 7, dd = tid & 127;
-            float acc = 0.f;
-            if (!KV8) {
-                for (int j = 0; j < cnt; j++)
-                    acc = __fmaf_rn(sc[g][j], bf2f(reinterpret_cast<const __nv_bfloat16*>(vtile + j * TS)[dd]), acc);
-            } else {
-                for (int j = 0; j < cnt; j++)
-                    acc = __fmaf_rn(__fmul_rn(sc[g][j], __half2float(vssc[j * 4 + (dd >> 5)])),
-                                    (float)reinterpret_cast<const int8_t*>(vtile + j * TS)[dd], acc);
+        if (tid < 128) { /* one thread per value dimension carries the chains of the four heads: a value is read and converted once */
+            const int dd = tid;
+            const float4* wv = reinterpret_cast<const float4*>(sm.scv) + (dd >> 5);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll 4
+            for (int j = 0; j < cnt; j++) {
+                const float vf = KV8 ? (float)reinterpret_cast<const int8_t*>(vtile + j * TS)[dd]
+                                     : bf2f(reinterpret_cast<const __nv_bfloat16*>(vtile + j * TS)[dd]);
+                const float4 wj = wv[j * 4];
+                a0 = __fmaf_rn(wj.x, vf, a0);
+                a1 = __fmaf_rn(wj.y, vf, a1);
+                a2 = __fmaf_rn(wj.z, vf, a2);
+                a3 = __fmaf_rn(wj.w, vf, a3);
             }
-            float* ph = a.part + (((size_t)row * QH + kvh * 4 + g) * a.n_split_slots + spl) * 130;
-            if (dd == 0) { ph[0] = hm[g]; ph[1] = hs[g]; }
-            ph[2 + dd] = acc;
+            const float accs[4] = {a0, a1, a2, a3};
+#pragma unroll
+            for (int g = 0; g < 4; g++) {
+                float* ph = a.part + (((size_t)row * QH + kvh * 4 + g) * a.n_split_slots + spl) * 130;
+                if (dd == 0) { ph[0] = hm[g]; ph[1] = hs[g]; }
+                ph[2 + dd] = accs[g];
+            }
         }
         S2P_CTA_SYNC(); /* tile, sc, hm/hs are rewritten by the next split */
     }

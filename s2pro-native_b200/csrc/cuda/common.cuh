@@ -23,6 +23,9 @@
 #endif
 
 __device__ __forceinline__ float bf_bits_to_f32(uint32_t hi16) { return __uint_as_float(hi16 << 16); }
+/* the two bf16 of a 32-bit word (lower address first) */
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ __nv_bfloat16 f2bf(float v) { return __float2bfloat16(v); } /* RNE */
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }

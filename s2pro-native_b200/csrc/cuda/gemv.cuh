@@ -173,8 +173,6 @@ template <> struct LaneX<WK_INT8_GRP> : LaneX<WK_INT8_CH> {};
  * bf16, eight to a uint4 at index (i*2 + (j>>3))*32 + l; INT8 keeps f32, four to a
  * float4 at index (i*4 + (j>>2))*32 + l.  Eight consecutive k (one 16-byte vector
  * of the source) therefore land in one uint4 or two float4. */
-__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
-__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 template <int WK>
 __device__ __forceinline__ void xs_store_vec8(unsigned char* xs, int v, const uint4& q) {

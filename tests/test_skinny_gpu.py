@@ -27,7 +27,7 @@ def exact(mine, kind, y, x, w, s, M, N, K):
 
 
 @pytest.mark.parametrize("kind", [2, 0, 1])
-@pytest.mark.parametrize("M,N,K", [(32, 6144, 2560), (17, 2560, 4096), (128, 2560, 9728), (48, 4097, 2560), (256, 384, 512)])
+@pytest.mark.parametrize("M,N,K", [(32, 6144, 2560), (32, 19456, 2560), (17, 2560, 4096), (128, 2560, 9728), (48, 4097, 2560), (256, 384, 512)])
 def test_tensor_core_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
     dev()
     testlib.skinny_gemm_tc.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
