@@ -16,10 +16,11 @@ namespace s2p {
 template <bool KV8> struct AttnSmem {
     static constexpr int VB = KV8 ? 128 : 256; /* payload bytes per cached vector */
     static constexpr int TS = VB + 4;          /* staged row stride (skewed) */
-    alignas(16) unsigned char tile[64 * TS];   /* K rows of the split */
-    alignas(16) unsigned char vtile[64 * TS];  /* V rows of the split */
-    alignas(8) __half ssc[64 * 4];             /* their group scales (INT8 cache) */
-    alignas(8) __half vssc[64 * 4];
+    static constexpr int NBUF = KV8 ? 2 : 1;   /* INT8 cache: the next split is copied while this one is worked on */
+    alignas(16) unsigned char tile[NBUF][64 * TS];   /* K rows of a split */
+    alignas(16) unsigned char vtile[NBUF][64 * TS];  /* V rows of a split */
+    alignas(8) __half ssc[NBUF][64 * 4];             /* their group scales (INT8 cache) */
+    alignas(8) __half vssc[NBUF][64 * 4];
     alignas(16) float sq[4][128];
     float sc[4][64];
     alignas(16) float scv[64 * 4 * 4];         /* [position][value group][head]: probability x value scale */
@@ -47,10 +48,11 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
     constexpr int VB = AttnSmem<KV8>::VB;
     constexpr int TS = AttnSmem<KV8>::TS;
 
-    unsigned char* tile = sm.tile;
-    unsigned char* vtile = sm.vtile;
-    __half* ssc = sm.ssc;
-    __half* vssc = sm.vssc;
+    constexpr int NBUF = AttnSmem<KV8>::NBUF;
+    unsigned char* tile = sm.tile[0]; /* buffer 0 takes the worker's first split (and the appended row) */
+    unsigned char* vtile = sm.vtile[0];
+    __half* ssc = sm.ssc[0];
+    __half* vssc = sm.vssc[0];
     float (*sq)[128] = sm.sq;
     float (*sc)[64] = sm.sc;
     float (*red)[128] = sm.red;
@@ -70,7 +72,11 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
 
     /* Start the copies of a split's K and V rows (and scales) into shared memory; they run
      * while the caller does something else.  `skip` (or -1): a row the caller writes itself. */
-    auto fetch_split = [&](int spl, int skip) {
+    auto fetch_split = [&](int spl, int skip, int buf) {
+        unsigned char* tile = sm.tile[buf];
+        unsigned char* vtile = sm.vtile[buf];
+        __half* ssc = sm.ssc[buf];
+        __half* vssc = sm.vssc[buf];
         const int start = spl << 6;
         const int cnt = min(64, len - start);
         for (int i = tid; i < cnt * (VB / 4); i += 512) {
@@ -91,7 +97,7 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
     /* the first split of this worker is on its way before the query is prepared; the new
      * position's row, if it falls into that split, is written below by this CTA itself */
     const bool pre_has_new = PREP && wk == n_active - 1;
-    if (wk < n_active) fetch_split(wk, pre_has_new ? pos : -1);
+    if (wk < n_active) fetch_split(wk, pre_has_new ? pos : -1, 0);
 
     {   /* queries of the four heads sharing this kv head, pre-scaled */
         const int g = tid >> 7, t = tid & 127;
@@ -156,11 +162,25 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
     }
     S2P_CTA_SYNC();
 
+    int cur = 0;
     for (int spl = wk; spl < n_active; spl += workers) {
         const int start = spl << 6;
         const int cnt = min(64, len - start);
-        if (spl != wk) fetch_split(spl, -1); /* later splits: this CTA's own append, if any, is already visible */
-        asm volatile("cp.async.wait_all;" ::: "memory");
+        /* later splits: this CTA's own append, if any, is already visible */
+        if (NBUF == 2) {
+            /* the other buffer was last read before the barrier that ended the previous round */
+            if (spl + workers < n_active) {
+                fetch_split(spl + workers, -1, cur ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_all;" ::: "memory");
+            }
+            tile = sm.tile[cur]; vtile = sm.vtile[cur]; ssc = sm.ssc[cur]; vssc = sm.vssc[cur];
+            cur ^= 1;
+        } else {
+            if (spl != wk) fetch_split(spl, -1, 0);
+            asm volatile("cp.async.wait_all;" ::: "memory");
+        }
         S2P_CTA_SYNC();
 
         /* scores: thread (head g4, position t4), one chain each */

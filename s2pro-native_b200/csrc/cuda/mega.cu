@@ -44,7 +44,7 @@ constexpr int MEGA_PART_BYTES_DEFAULT = 19456;  /* 152 (row, tile) units: 30 row
 /* shared memory: ring slots | work area (x | partial buffers | red) | tail.  Attention and the
  * sampler overlay the work area. */
 constexpr int MEGA_MIN_WORK = 19456 + MEGA_PARTS * MEGA_PART_BYTES_DEFAULT;
-static_assert(sizeof(AttnSmem<false>) <= MEGA_MIN_WORK, "attention scratch must fit the work area");
+static_assert(sizeof(AttnSmem<false>) <= MEGA_MIN_WORK && sizeof(AttnSmem<true>) <= MEGA_MIN_WORK, "attention scratch must fit the work area");
 static_assert(sizeof(SamplerSmem<MEGA_WORKERS>) <= MEGA_MIN_WORK, "sampler scratch must fit the work area");
 static_assert(sizeof(MegaCopyCmd) == 64, "one copy command per 64-byte line");
 

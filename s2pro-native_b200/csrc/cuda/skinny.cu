@@ -29,7 +29,7 @@
 namespace s2p {
 
 constexpr int SK_BM = 128;
-constexpr int SK_MAX_SPLIT = 8;
+constexpr int SK_MAX_SPLIT = 10;
 
 /* 0 unless a bounded wait inside a launch gave up (read back by skinny_status) */
 __device__ int g_sk_status;
@@ -74,16 +74,19 @@ __device__ __forceinline__ uint4 sk_int8_chunk(uint32_t w0, uint32_t w1, __half2
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-/* 16-byte asynchronous copy into shared memory; `valid` false writes zeros without reading */
-__device__ __forceinline__ void sk_cp16(void* dst, const void* src, bool valid) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 16 : 0) : "memory");
+/* 16-byte asynchronous copy into shared memory, past L1 */
+__device__ __forceinline__ void sk_cp16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
-/* 4-, 8- or 16-byte copy of group scales (bytes is uniform over the launch) */
-__device__ __forceinline__ void sk_cp_small(void* dst, const void* src, int bytes, bool valid) {
+/* 4, 8, 16 or 32 bytes of group scales (bytes is uniform over the launch) */
+__device__ __forceinline__ void sk_cp_scales(void* dst, const void* src, int bytes) {
     const uint32_t d = smem_u32(dst);
-    if (bytes == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(src), "r"(valid ? 4 : 0) : "memory");
-    else if (bytes == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(d), "l"(src), "r"(valid ? 8 : 0) : "memory");
-    else asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(valid ? 16 : 0) : "memory");
+    if (bytes == 4) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+    else if (bytes == 8) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(d), "l"(src) : "memory");
+    else {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+        if (bytes == 32) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + 16), "l"(static_cast<const char*>(src) + 16) : "memory");
+    }
 }
 /* wait until at most n of this thread's copy groups are pending (n is uniform, 0..7) */
 __device__ __forceinline__ void sk_cp_wait(int n) {
@@ -99,18 +102,24 @@ __device__ __forceinline__ void sk_cp_wait(int n) {
     }
 }
 
-template <int WK, int NT> struct SkGeom {
-    static constexpr int KC = NT / 4;                                     /* K extent of a slab: one or two 16-byte units of codes per thread */
+constexpr int SK_SUPER_K = 256; /* K extent of one weight copy round: 128 (INT4) or 256 (INT8) contiguous bytes per row */
+
+template <int WK, int NT, int KCP> struct SkGeom {
+    static constexpr int KC = KCP;                                        /* K extent of a converted slab: NT / 4 gives one (INT4) or two (INT8) 16-byte units of codes per thread */
+    static constexpr int SPS = SK_SUPER_K / KC;                           /* slabs per weight copy round */
     static constexpr int UPR = (WK == WK_INT4_PACK) ? KC / 32 : KC / 16;  /* 16-byte units of packed codes per row and slab */
-    static constexpr int PITCH = UPR * 16;
-    static constexpr int SWZ_SHIFT = UPR == 2 ? 2 : (UPR == 4 ? 1 : 0);   /* 8 / UPR consecutive rows share a swizzle value */
-    static constexpr int W_BYTES = SK_BM * PITCH;
-    static constexpr int SC_ROW = 16;                                     /* room per row for the copied scales */
+    static constexpr int UPRS = UPR * SPS;                                /* ... per row and copy round: 8 or 16 */
+    static constexpr int PITCHS = UPRS * 16;
+    static constexpr int WS_BYTES = SK_BM * PITCHS;
+    static constexpr int SC_ROW = 32;                                     /* room per row for the round's scales */
     static constexpr int SC_BYTES = (WK == WK_INT8_CH) ? 0 : SK_BM * SC_ROW;
+    static constexpr int SUP_BYTES = WS_BYTES + SC_BYTES;
     static constexpr int WPU = (WK == WK_INT4_PACK) ? 32 : 16;            /* weights per 16-byte unit */
-    static constexpr int NLD = UPR * SK_BM / NT;                          /* units per thread and slab: 1 (INT4) or 2 (INT8) */
+    static constexpr int NLD = UPR * SK_BM / NT;                          /* units converted per thread and slab: 1 (INT4) or 2 (INT8) */
+    static constexpr int NCP = UPRS * SK_BM / NT;                         /* units copied per thread and round */
+    static constexpr int RSTEP = NT / UPRS;                               /* rows between a thread's copies */
     static constexpr int A_BYTES = SK_BM * KC * 2;                        /* converted stage */
-    static_assert(UPR == 2 || UPR == 4 || UPR == 8, "swizzle covers 2, 4 or 8 units per row");
+    static_assert(NT % SK_BM == 0 && NT % UPRS == 0, "thread -> (row, unit) maps assume this");
 };
 
 /* bf16 x 8 -> f16 x 8 for the B tile.  INT4 slabs keep the order their conversion produces
@@ -133,32 +142,41 @@ template <int WK> __device__ __forceinline__ uint4 sk_x_unit(const uint4& v) {
                       *reinterpret_cast<uint32_t*>(&h[3]));
 }
 
-template <int WK, int NT>
+template <int WK, int NT, int KCP>
 __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
                                                             int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
-                                                            int lgNB, int D, __nv_bfloat16* y, const __nv_bfloat16* resid,
+                                                            int lgNB, int D, int DW, int n_split_tiles, int KS,
+                                                            __nv_bfloat16* y, const __nv_bfloat16* resid,
                                                             float* __restrict__ partial, unsigned* __restrict__ arrivals) {
     /* resid (may alias y): y = bf16(f32(resid) + f32(bf16(product))), the residual add of the decode layers */
-    /* gridDim.y > 1: the K range is split over gridDim.y CTAs per row tile; each leaves its f32 partial in
-     * `partial`[split][batch row][weight row] and the last one to arrive adds them in split order */
-    /* D: depth of the ring of raw slabs (packed codes, scales, activations) that asynchronous copies
-     * fill D - 1 slabs ahead of the conversion: what keeps enough bytes in flight to stream from HBM */
+    /* The last n_split_tiles row tiles have their K range split over KS CTAs each; those CTAs come first
+     * in the grid (short pieces first, whole tiles after them: the tail of the grid stays balanced).  Each
+     * piece leaves its f32 partial in `partial`[split tile][piece][batch row][128] and the last piece of a
+     * tile to arrive adds them in piece order. */
+    /* Two rings of raw data are filled by asynchronous copies ahead of the conversion: DW copy rounds of
+     * weights and scales (256 k each), D slabs of activations.  They keep enough bytes in flight to stream
+     * from HBM, in runs DRAM serves well. */
     /* Everything a thread needs per slab (source pointers, offsets inside a ring slot and a stage) is
      * worked out once; the loop only advances pointers: the conversion is bound by instruction issue. */
-    typedef SkGeom<WK, NT> G;
+    typedef SkGeom<WK, NT, KCP> G;
     constexpr int KC = G::KC;
     int* status = &g_sk_status;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int NB = 1 << lgNB;
     const int b_bytes = NB * KC * 2;
     const int x_units = NB * (KC / 8);
-    const int slot_bytes = G::W_BYTES + G::SC_BYTES + x_units * 16;
-    const int ring_bytes = D * slot_bytes;
-    unsigned char* ring = smem + 2 * (G::A_BYTES + b_bytes);
-    uint64_t* done = reinterpret_cast<uint64_t*>(ring + ring_bytes);
+    const int x_bytes = x_units * 16;
+    unsigned char* xring = smem + 2 * (G::A_BYTES + b_bytes);
+    unsigned char* wring = xring + D * x_bytes;
+    uint64_t* done = reinterpret_cast<uint64_t*>(wring + DW * G::SUP_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int n0 = blockIdx.x * SK_BM;
+    const int n_tiles = (N + SK_BM - 1) / SK_BM, n_pieces = n_split_tiles * KS;
+    const bool piece = (int)blockIdx.x < n_pieces;
+    const int stile = piece ? (int)blockIdx.x / KS : 0;                     /* index among the split tiles */
+    const int ks = piece ? (int)blockIdx.x % KS : 0, ksn = piece ? KS : 1;  /* this CTA's piece of how many */
+    const int tile = piece ? n_tiles - n_split_tiles + stile : (int)blockIdx.x - n_pieces;
+    const int n0 = tile * SK_BM;
     const size_t row_bytes = (WK == WK_INT4_PACK) ? (size_t)(K >> 1) : (size_t)K;
     int ncols = 32;
     while (ncols < NB) ncols <<= 1;
@@ -173,71 +191,67 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
         mbar_init_fence();
     }
 
-    const int nk_all = K / KC, KS = gridDim.y, ks = blockIdx.y;
-    const int it_first = (int)((long long)nk_all * ks / KS), nk = (int)((long long)nk_all * (ks + 1) / KS) - it_first;
-    /* scales travel as aligned pieces of at least 4 bytes: cpy elements starting at a multiple of cpy */
-    const int nsc = KC >> gshift, cpy = nsc < 2 ? 2 : nsc;
+    /* the K range of this CTA, in whole copy rounds */
+    const int nsup_all = K / SK_SUPER_K;
+    const int sup_first = nsup_all * ks / ksn, nsup = nsup_all * (ks + 1) / ksn - sup_first;
+    const int it_first = sup_first * G::SPS, nk = nsup * G::SPS;
 
-    /* ---- copy side: UPR neighbouring threads read one row's run of codes; the unit index inside a slot is
-     * XOR-swizzled so that 8 consecutive rows read back without bank conflicts */
-    const unsigned char* wsrc[G::NLD];
-    int wdst[G::NLD];
-    bool wvalid[G::NLD];
+    /* ---- copy side.  Weights: UPRS neighbouring threads read one row's contiguous run of a whole round
+     * (128 or 256 bytes: DRAM serves whole lines of a row at a time instead of 32-byte pieces of many rows);
+     * the unit index inside the row is XOR-swizzled so that 8 consecutive rows read back without bank
+     * conflicts.  Rows beyond N (last tile) repeat row N - 1: their outputs are never stored. */
+    const int cp_c = tid % G::UPRS, cp_row0 = tid / G::UPRS;
+    const unsigned char* wsrc = static_cast<const unsigned char*>(w) + (size_t)sup_first * (G::PITCHS) + cp_c * 16;
+    const __half* sc_src = nullptr;
+    const int sc_elems = SK_SUPER_K >> gshift; /* scales per row and round: 2 .. 16 */
+    if (WK != WK_INT8_CH && tid < SK_BM)
+        sc_src = static_cast<const __half*>(scales) + (size_t)min(n0 + tid, N - 1) * (K >> gshift) + (size_t)sup_first * sc_elems;
+    int w_wslot = 0, w_issued = 0;
+    auto issue_w = [&]() {
+        unsigned char* sup = wring + w_wslot;
 #pragma unroll
-    for (int i = 0; i < G::NLD; i++) {
-        const int idx = tid + NT * i, row = idx / G::UPR, c = idx % G::UPR, grow = n0 + row;
-        wvalid[i] = grow < N;
-        wsrc[i] = static_cast<const unsigned char*>(w);
-        if (wvalid[i]) wsrc[i] += (size_t)grow * row_bytes + (size_t)it_first * (WK == WK_INT4_PACK ? KC / 2 : KC) + c * 16;
-        wdst[i] = row * G::PITCH + ((c ^ ((row >> G::SWZ_SHIFT) & (G::UPR - 1))) << 4);
-    }
-    const bool sc_copier = WK != WK_INT8_CH && tid < SK_BM;
-    const bool sc_valid = sc_copier && n0 + tid < N;
-    const __half* sc_row = static_cast<const __half*>(scales);
-    if (sc_valid) sc_row += (size_t)(n0 + tid) * (K >> gshift);
-    /* activations: unit c = [k / 8][batch row] sits in the slot where the B tile wants it; c = tid + NT u */
-    const int xn = tid & (NB - 1);
-    const bool x_valid = xn < M;
+        for (int i = 0; i < G::NCP; i++) {
+            const int row = cp_row0 + i * G::RSTEP;
+            sk_cp16(sup + row * G::PITCHS + ((cp_c ^ (row & 7)) << 4), wsrc + (size_t)min(n0 + row, N - 1) * row_bytes);
+        }
+        wsrc += G::PITCHS;
+        if (sc_src) {
+            sk_cp_scales(sup + G::WS_BYTES + tid * G::SC_ROW, sc_src, sc_elems * 2);
+            sc_src += sc_elems;
+        }
+        w_issued++;
+        w_wslot += G::SUP_BYTES;
+        if (w_wslot == DW * G::SUP_BYTES) w_wslot = 0;
+    };
+    /* activations, slab by slab: unit c = [k / 8][batch row] sits in the slot where the B tile wants it;
+     * c = tid + NT u; rows beyond the batch repeat row M - 1 (their columns are never stored) */
     const int x_mine = tid < x_units ? (x_units + NT - 1 - tid) / NT : 0; /* units of this thread */
     const int x_step = (NT >> lgNB) * 8;                                   /* elements between them (NB <= NT) */
-    const __nv_bfloat16* xsrc = x;
-    if (x_valid) xsrc += (size_t)xn * K + (size_t)it_first * KC + (tid >> lgNB) * 8;
-    const int xdst = G::W_BYTES + G::SC_BYTES + tid * 16;
-
-    int w_slot = 0, issued = 0; /* byte offset of the slot the next copy fills; slabs issued so far */
-    auto issue = [&]() {
-        unsigned char* slot = ring + w_slot;
-#pragma unroll
-        for (int i = 0; i < G::NLD; i++) {
-            sk_cp16(slot + wdst[i], wsrc[i], wvalid[i]);
-            if (wvalid[i]) wsrc[i] += (WK == WK_INT4_PACK ? KC / 2 : KC);
-        }
-        if (sc_copier) {
-            const int e0 = (((it_first + issued) * KC) >> gshift) & ~(cpy - 1);
-            sk_cp_small(slot + G::W_BYTES + tid * G::SC_ROW, sc_row + (sc_valid ? e0 : 0), cpy * 2, sc_valid);
-        }
-        for (int u = 0; u < x_mine; u++) sk_cp16(slot + xdst + u * (NT * 16), xsrc + (x_valid ? u * x_step : 0), x_valid);
-        if (x_valid) xsrc += KC;
-        issued++;
-        w_slot += slot_bytes;
-        if (w_slot == ring_bytes) w_slot = 0;
+    const __nv_bfloat16* xsrc = x + (size_t)min(tid & (NB - 1), M - 1) * K + (size_t)it_first * KC + (tid >> lgNB) * 8;
+    int x_wslot = 0, x_issued = 0;
+    auto issue_x = [&]() {
+        unsigned char* slot = xring + x_wslot + tid * 16;
+        for (int u = 0; u < x_mine; u++) sk_cp16(slot + u * (NT * 16), xsrc + u * x_step);
+        xsrc += KC;
+        x_issued++;
+        x_wslot += x_bytes;
+        if (x_wslot == D * x_bytes) x_wslot = 0;
     };
-    /* one copy group per slab, also when it is empty, so the group count tells which slabs have landed */
-    for (int j = 0; j < D - 1; j++) {
-        if (j < nk) issue();
+    /* One copy group per slab round, empty ones included, so that the group count tells what has landed:
+     * round v carries the activations of slab v + D - 1 and, when v is a multiple of SPS, the weights of
+     * copy round v / SPS + DW - 1.  With D <= SPS (DW - 1) + 1 (the host's choice), "at most D - 2 groups
+     * pending" at the end of round v means slab v + 1 is complete, weights included. */
+    for (int v = -G::SPS * (DW - 1); v < 0; v++) {
+        if (v + D - 1 >= 0 && x_issued < nk) issue_x();
+        if ((-v) % G::SPS == 0 && w_issued < nsup) issue_w();
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
 
-    /* ---- conversion side: thread -> (row, unit q) of the slab; constant offsets into a slot and a stage */
-    int rd_off[G::NLD], a_off[G::NLD], q_of[G::NLD], sc_off;
-#pragma unroll
-    for (int i = 0; i < G::NLD; i++) {
-        const int idx = tid + NT * i, row = idx & (SK_BM - 1), q = idx >> 7;
-        rd_off[i] = row * G::PITCH + ((q ^ ((row >> G::SWZ_SHIFT) & (G::UPR - 1))) << 4);
-        a_off[i] = (q * (G::WPU / 8) * SK_BM + row) * 16;
-        q_of[i] = q;
-    }
-    sc_off = G::W_BYTES + (tid & (SK_BM - 1)) * G::SC_ROW;
+    /* ---- conversion side: thread -> (row, unit q) of the slab; constant offsets into a copy round and a stage */
+    const int cv_row = tid & (SK_BM - 1), cv_q0 = tid >> 7; /* units q0 + i NT / 128 */
+    const int rd_row = cv_row * G::PITCHS, rd_x = cv_row & 7;
+    const int a_off0 = (cv_q0 * (G::WPU / 8) * SK_BM + cv_row) * 16;
+    const int sc_off = G::WS_BYTES + cv_row * G::SC_ROW;
 
     sk_cp_wait(D - 2); /* slab 0 */
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -250,28 +264,26 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
     const uint64_t desc_b0 = sk_smem_desc(smem_u32(smem + 2 * G::A_BYTES), (uint32_t)NB * 16, 128);
 
     bool ok = true;
-    int r_slot = 0;
+    int x_rslot = 0, w_rslot = 0, j_in = 0; /* read offsets into the rings; slab index inside the copy round */
     for (int it = 0; it < nk && ok; it++) {
         const int s = it & 1;
-        /* the slot the next copy fills was read by every thread before the barrier that ended the last round */
-        if (issued < nk) issue();
+        /* the slots the next copies fill were read by every thread before the barrier that ended the last round */
+        if (x_issued < nk) issue_x();
+        if (j_in == 0 && w_issued < nsup) issue_w();
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (it >= 2) ok = mbar_wait_bounded(done + s, ((unsigned)(it >> 1) - 1u) & 1u, status); /* the MMAs that read this stage */
         if (!ok) break;
-        const unsigned char* slot = ring + r_slot;
+        const unsigned char* sup = wring + w_rslot;
         unsigned char* A = smem + s * G::A_BYTES;
         unsigned char* B = smem + 2 * G::A_BYTES + s * b_bytes;
-        const int kg = ((it_first + it) * KC) >> gshift; /* first scale group of the slab */
-        /* weights: A[k / 8][row] (rows beyond N: zero codes, zero scale) */
+        /* weights: A[k / 8][row] */
 #pragma unroll
         for (int i = 0; i < G::NLD; i++) {
-            const uint4 pk = *reinterpret_cast<const uint4*>(slot + rd_off[i]);
+            const int q = cv_q0 + i * (NT / SK_BM), c = j_in * G::UPR + q;
+            const uint4 pk = *reinterpret_cast<const uint4*>(sup + rd_row + ((c ^ rd_x) << 4));
             __half2 sc2 = __float2half2_rn(1.f);
-            if (WK != WK_INT8_CH) {
-                const int e = kg + ((q_of[i] * G::WPU) >> gshift) - (kg & ~(cpy - 1));
-                sc2 = __half2half2(reinterpret_cast<const __half*>(slot + sc_off)[e]);
-            }
-            uint4* Au = reinterpret_cast<uint4*>(A + a_off[i]);
+            if (WK != WK_INT8_CH) sc2 = __half2half2(reinterpret_cast<const __half*>(sup + sc_off)[(c * G::WPU) >> gshift]);
+            uint4* Au = reinterpret_cast<uint4*>(A + a_off0 + i * ((NT / SK_BM) * (G::WPU / 8) * SK_BM * 16));
             if (WK == WK_INT4_PACK) {
                 const uint32_t ws[4] = {pk.x, pk.y, pk.z, pk.w};
 #pragma unroll
@@ -281,11 +293,16 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
                 Au[SK_BM] = sk_int8_chunk<WK == WK_INT8_GRP>(pk.z, pk.w, sc2);
             }
         }
-        /* activations: B[k / 8][batch row]; rows beyond the batch were zero-filled (bf16 zero = f16 zero) */
+        /* activations: B[k / 8][batch row] */
         for (int u = 0; u < x_mine; u++)
-            *reinterpret_cast<uint4*>(B + (tid + u * NT) * 16) = sk_x_unit<WK>(*reinterpret_cast<const uint4*>(slot + xdst + u * (NT * 16)));
-        r_slot += slot_bytes;
-        if (r_slot == ring_bytes) r_slot = 0;
+            *reinterpret_cast<uint4*>(B + (tid + u * NT) * 16) = sk_x_unit<WK>(*reinterpret_cast<const uint4*>(xring + x_rslot + (tid + u * NT) * 16));
+        x_rslot += x_bytes;
+        if (x_rslot == D * x_bytes) x_rslot = 0;
+        if (++j_in == G::SPS) {
+            j_in = 0;
+            w_rslot += G::SUP_BYTES;
+            if (w_rslot == DW * G::SUP_BYTES) w_rslot = 0;
+        }
         sk_cp_wait(D - 2);        /* this thread's share of slab it + 1; the barrier makes everyone's visible */
         fence_proxy_async_smem(); /* these generic-proxy stores are read by the tensor core (async proxy) */
         __syncthreads();
@@ -334,22 +351,22 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
                 for (int j = 0; j < 32; j++) {
                     const int m = col0 + j;
                     if (m < M) {
-                        if (KS == 1) {
+                        if (!piece) {
                             __nv_bfloat16 o = f2bf(__fmul_rn(__uint_as_float(v[j]), rs));
                             if (resid) o = f2bf(__fadd_rn(bf2f(resid[(size_t)m * N + grow]), bf2f(o)));
                             y[(size_t)m * N + grow] = o;
                         }
-                        else partial[((size_t)ks * M + m) * N + grow] = __uint_as_float(v[j]);
+                        else partial[(((size_t)stile * KS + ks) * M + m) * SK_BM + (grow - n0)] = __uint_as_float(v[j]);
                     }
                 }
             }
         }
     }
-    if (KS > 1) {
+    if (piece) {
         __shared__ int s_last;
         __threadfence();
         __syncthreads();
-        if (tid == 0) s_last = ok && (atomicAdd(arrivals + blockIdx.x, 1u) == (unsigned)(KS - 1));
+        if (tid == 0) s_last = ok && (atomicAdd(arrivals + stile, 1u) == (unsigned)(KS - 1));
         __syncthreads();
         if (s_last) {
             __threadfence();
@@ -362,7 +379,7 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
                     const bool live = e < SK_BM * M && grow < N;
 #pragma unroll
                     for (int q = 0; q < SK_MAX_SPLIT; q++)
-                        v[u][q] = (live && q < KS) ? __ldcg(partial + ((size_t)q * M + m) * N + grow) : 0.f;
+                        v[u][q] = (live && q < KS) ? __ldcg(partial + (((size_t)stile * KS + q) * M + m) * SK_BM + (e & (SK_BM - 1))) : 0.f;
                 }
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
@@ -378,7 +395,7 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
                     y[(size_t)m * N + grow] = o;
                 }
             }
-            if (tid == 0) arrivals[blockIdx.x] = 0u;
+            if (tid == 0) arrivals[stile] = 0u;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -390,8 +407,9 @@ constexpr size_t SK_SMEM_ONE = 226 * 1024; /* one CTA per SM */
 constexpr size_t SK_SMEM_TWO = 111 * 1024; /* two, each with its static kilobyte and the system's */
 constexpr int SK_MAX_DEPTH = 8;
 
-/* scratch for split-K launches: partials [SK_MAX_SPLIT][rows][SK_SPLIT_MAX_N] f32 and one arrival counter per row tile */
-constexpr int SK_SPLIT_MAX_N = 6144;
+/* scratch for split-K launches: f32 partials [split tile][piece][batch row][128] and one arrival counter per split tile */
+constexpr int SK_SCRATCH_FLOATS_PER_ROW = 8 * 6144; /* per batch row: eight pieces of a 6144-row matrix */
+constexpr int SK_MAX_SPLIT_TILES = 256;
 static float* g_partial[64];
 static unsigned* g_arrivals[64];
 static int g_partial_rows[64];
@@ -406,7 +424,7 @@ extern "C" cudaError_t skinny_setup(int max_rows) {
     if (g_partial[dev]) cudaFree(g_partial[dev]);
     g_partial[dev] = nullptr;
     g_partial_rows[dev] = 0;
-    if ((e = cudaMalloc((void**)&g_partial[dev], (size_t)SK_MAX_SPLIT * max_rows * SK_SPLIT_MAX_N * sizeof(float))) != cudaSuccess) return e;
+    if ((e = cudaMalloc((void**)&g_partial[dev], (size_t)SK_SCRATCH_FLOATS_PER_ROW * max_rows * sizeof(float))) != cudaSuccess) return e;
     if (!g_arrivals[dev]) {
         if ((e = cudaMalloc((void**)&g_arrivals[dev], 256 * sizeof(unsigned))) != cudaSuccess) return e;
         if ((e = cudaMemset(g_arrivals[dev], 0, 256 * sizeof(unsigned))) != cudaSuccess) return e;
@@ -415,35 +433,55 @@ extern "C" cudaError_t skinny_setup(int max_rows) {
     return cudaSuccess;
 }
 
-/* shared memory of a launch: two converted stages, D raw slabs, barriers */
-template <int WK, int NT> static size_t sk_fixed_bytes(int NB) {
-    return 2 * ((size_t)SkGeom<WK, NT>::A_BYTES + (size_t)NB * SkGeom<WK, NT>::KC * 2) + 64;
+/* shared memory of a launch: two converted stages, D slabs of raw activations, DW copy rounds of raw weights, barriers */
+template <int WK, int NT, int KCP> static size_t sk_fixed_bytes(int NB) {
+    return 2 * ((size_t)SkGeom<WK, NT, KCP>::A_BYTES + (size_t)NB * SkGeom<WK, NT, KCP>::KC * 2) + 64;
 }
-template <int WK, int NT> static size_t sk_slot_bytes(int NB) {
-    return (size_t)SkGeom<WK, NT>::W_BYTES + SkGeom<WK, NT>::SC_BYTES + (size_t)NB * (SkGeom<WK, NT>::KC / 8) * 16;
+/* ring depths that fit `budget` bytes; false if not even the shallowest does */
+template <int WK, int NT, int KCP> static bool sk_depths(int NB, size_t budget, int min_d, int* D, int* DW) {
+    typedef SkGeom<WK, NT, KCP> G;
+    const size_t fixed = sk_fixed_bytes<WK, NT, KCP>(NB), xslot = (size_t)NB * G::KC * 2;
+    for (int dw = 3; dw >= 2; dw--) {
+        if (fixed + (size_t)dw * G::SUP_BYTES + (size_t)min_d * xslot > budget) continue;
+        int d = (int)((budget - fixed - (size_t)dw * G::SUP_BYTES) / xslot);
+        if (d > G::SPS * (dw - 1) + 1) d = G::SPS * (dw - 1) + 1; /* what the kernel's group counting needs */
+        if (d > SK_MAX_DEPTH) d = SK_MAX_DEPTH;
+        if (d < min_d) continue;
+        *D = d; *DW = dw;
+        return true;
+    }
+    return false;
 }
 
-template <int WK, int NT>
-static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, int lgNB, int tiles, int split, void* y, const void* resid,
+template <int WK, int NT, int KCP>
+static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, int lgNB, int tiles, int S, int KS, void* y, const void* resid,
                                 float* partial, unsigned* arrivals, cudaStream_t st) {
+    typedef SkGeom<WK, NT, KCP> G;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    /* ring depth: what the shared memory of the SM allows beside the stages (shared by two CTAs of 256 threads) */
     const int NB = 1 << lgNB;
-    const size_t fixed = sk_fixed_bytes<WK, NT>(NB), slot = sk_slot_bytes<WK, NT>(NB);
-    int D = 0;
-    if (NT == 256 && fixed < SK_SMEM_TWO) D = (int)((SK_SMEM_TWO - fixed) / slot);
-    if (D < 4) D = fixed < SK_SMEM_ONE ? (int)((SK_SMEM_ONE - fixed) / slot) : 0;
-    if (D > SK_MAX_DEPTH) D = SK_MAX_DEPTH;
-    if (D < 2) return cudaErrorInvalidValue;
-    k_skinny_tc<WK, NT><<<dim3((unsigned)tiles, (unsigned)split), NT, fixed + (size_t)D * slot, st>>>(
-        lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, lgNB, D, (__nv_bfloat16*)y,
+    int D = 0, DW = 0;
+    /* two CTAs of 256 threads per SM if rings of useful depth fit in half the shared memory, else one */
+    if (!(NT == 256 && sk_depths<WK, NT, KCP>(NB, SK_SMEM_TWO, 3, &D, &DW)) && !sk_depths<WK, NT, KCP>(NB, SK_SMEM_ONE, 2, &D, &DW))
+        return cudaErrorInvalidValue;
+    const size_t smem = sk_fixed_bytes<WK, NT, KCP>(NB) + (size_t)D * NB * G::KC * 2 + (size_t)DW * G::SUP_BYTES;
+    k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)(tiles - S + S * KS)), NT, smem, st>>>(
+        lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, lgNB, D, DW, S, KS, (__nv_bfloat16*)y,
         (const __nv_bfloat16*)resid, partial, arrivals);
     return cudaGetLastError();
+}
+
+/* launch policy (skinny_tune): CTAs the split aims at, and the kernel shape: 0 = 256 threads, 64-k slabs (two
+ * CTAs per SM fit); 1 = 512 threads, 128-k slabs; 2 = 256 threads, 128-k slabs (fewest instructions per weight) */
+static int g_sk_target_ctas = 148;
+static int g_sk_shape = 1;
+extern "C" void skinny_tune(int target_ctas, int shape) {
+    g_sk_target_ctas = target_ctas < 1 ? 1 : target_ctas;
+    g_sk_shape = shape;
 }
 
 template <int WK>
@@ -451,42 +489,64 @@ static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, c
     int lgNB = 4; /* the batch is padded to a power of two: the MMA's N */
     while ((1 << lgNB) < M) lgNB++;
     const int tiles = (lin->N + SK_BM - 1) / SK_BM;
-    int dev = 0, split = 1;
+    int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    /* few row tiles and a long K: split K over several CTAs so the whole GPU streams the matrix */
-    if (dev >= 0 && dev < 64 && g_partial_rows[dev] >= M && lin->N <= SK_SPLIT_MAX_N && tiles <= 74 && tiles <= 256) {
-        split = 148 / tiles;
-        if (split > SK_MAX_SPLIT) split = SK_MAX_SPLIT;
-        if (split > lin->K / 128) split = lin->K / 128;
-        if (split < 1) split = 1;
+    /* S of the row tiles have their K range split into KS pieces:
+     *  - few tiles: all of them, until the grid fills the GPU;
+     *  - a few more tiles than SMs: the surplus ones, so that no SM is left with two whole tiles while the
+     *    others idle (the pieces run first, the whole tiles fill in behind them). */
+    int S = 0, KS = 1;
+    if (dev >= 0 && dev < 64 && g_partial_rows[dev] >= M) {
+        int max_ks = lin->K / SK_SUPER_K;
+        if (max_ks > SK_MAX_SPLIT) max_ks = SK_MAX_SPLIT;
+        if (tiles * 2 <= g_sk_target_ctas) {
+            S = tiles;
+            KS = g_sk_target_ctas / tiles < max_ks ? g_sk_target_ctas / tiles : max_ks;
+        } else if (tiles > 148 && tiles < 2 * 148) {
+            S = tiles - 148;
+            KS = max_ks;
+        }
+        const size_t cap = (size_t)SK_SCRATCH_FLOATS_PER_ROW * g_partial_rows[dev];
+        while (KS > 1 && (size_t)S * KS * M * SK_BM > cap) KS--;
+        if (KS <= 1 || S > SK_MAX_SPLIT_TILES) { S = 0; KS = 1; }
     }
-    float* partial = split > 1 ? g_partial[dev] : nullptr;
-    unsigned* arrivals = split > 1 ? g_arrivals[dev] : nullptr;
-    /* at most one CTA per SM: 512 threads each (16 warps hide the conversion's latencies); more CTAs than SMs:
-     * 256 threads, two CTAs per SM */
-    const size_t fixed512 = sk_fixed_bytes<WK, 512>(1 << lgNB), slot512 = sk_slot_bytes<WK, 512>(1 << lgNB);
-    if (tiles * split <= 148 && lin->K % 128 == 0 && fixed512 + 4 * slot512 <= SK_SMEM_ONE) /* and a ring of 4 slabs or more */
-        return sk_launch_nt<WK, 512>(lin, x, M, lgNB, tiles, split, y, resid, partial, arrivals, st);
-    return sk_launch_nt<WK, 256>(lin, x, M, lgNB, tiles, split, y, resid, partial, arrivals, st);
+    float* partial = S ? g_partial[dev] : nullptr;
+    unsigned* arrivals = S ? g_arrivals[dev] : nullptr;
+    int d = 0, dw = 0;
+    if (lin->K % 128 == 0) {
+        if (g_sk_shape == 1 && sk_depths<WK, 512, 128>(1 << lgNB, SK_SMEM_ONE, 3, &d, &dw))
+            return sk_launch_nt<WK, 512, 128>(lin, x, M, lgNB, tiles, S, KS, y, resid, partial, arrivals, st);
+        if (g_sk_shape == 2 && sk_depths<WK, 256, 128>(1 << lgNB, SK_SMEM_ONE, 3, &d, &dw))
+            return sk_launch_nt<WK, 256, 128>(lin, x, M, lgNB, tiles, S, KS, y, resid, partial, arrivals, st);
+    }
+    return sk_launch_nt<WK, 256, 64>(lin, x, M, lgNB, tiles, S, KS, y, resid, partial, arrivals, st);
 }
 
 /* y[M, N] (bf16) = x[M, K] (bf16) · W^T for 1 <= M <= 256, plus `resid` [M, N] when given (it may be y
- * itself).  K must be a multiple of 64, the group size of grouped kinds at least 32 (INT4) / 16 (INT8 codes). */
+ * itself).  K must be a multiple of 256, the group size of grouped kinds a power of two from 32 (INT4) / 16 (INT8
+ * codes) to 128. */
 extern "C" cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
-    if (!lin || !x || !y || M < 1 || M > 256 || lin->K % 64) return cudaErrorInvalidValue;
+    if (!lin || !x || !y || M < 1 || M > 256 || lin->K % SK_SUPER_K) return cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)lin->w) & 15) return cudaErrorInvalidValue;
-    if (lin->kind != WK_INT8_CH) { /* the scales of a slab are copied as an aligned piece of 4 to 16 bytes */
-        if (lin->gshift < 3 || ((uintptr_t)lin->scales & 15)) return cudaErrorInvalidValue;
-        const int nsc = 128 >> lin->gshift, cpy = nsc < 2 ? 2 : nsc; /* the wider of the two slab sizes */
-        if ((lin->K >> lin->gshift) % cpy) return cudaErrorInvalidValue;
+    if (lin->kind != WK_INT8_CH) /* a round's scales (256 / group of them) are copied as 4 to 32 aligned bytes */
+        if (lin->gshift < 4 || lin->gshift > 7 || ((uintptr_t)lin->scales & 15)) return cudaErrorInvalidValue;
+    if (lin->kind == WK_INT4_PACK && lin->gshift < 5) return cudaErrorInvalidValue;
+    /* the MMA's N is the batch padded to a power of two, at most 128: a larger batch takes two launches */
+    for (int m0 = 0; m0 < M; m0 += 128) {
+        const int mm = M - m0 < 128 ? M - m0 : 128;
+        const void* xs = static_cast<const char*>(x) + (size_t)m0 * lin->K * 2;
+        void* ys = static_cast<char*>(y) + (size_t)m0 * lin->N * 2;
+        const void* rs = resid ? static_cast<const char*>(resid) + (size_t)m0 * lin->N * 2 : nullptr;
+        cudaError_t e = cudaErrorInvalidValue;
+        switch (lin->kind) {
+        case WK_INT8_CH: e = sk_launch<WK_INT8_CH>(lin, xs, mm, ys, rs, st); break;
+        case WK_INT8_GRP: e = sk_launch<WK_INT8_GRP>(lin, xs, mm, ys, rs, st); break;
+        case WK_INT4_PACK: e = sk_launch<WK_INT4_PACK>(lin, xs, mm, ys, rs, st); break;
+        }
+        if (e != cudaSuccess) return e;
     }
-    switch (lin->kind) {
-    case WK_INT8_CH: return sk_launch<WK_INT8_CH>(lin, x, M, y, resid, st);
-    case WK_INT8_GRP: return lin->gshift >= 4 ? sk_launch<WK_INT8_GRP>(lin, x, M, y, resid, st) : cudaErrorInvalidValue;
-    case WK_INT4_PACK: return lin->gshift >= 5 ? sk_launch<WK_INT4_PACK>(lin, x, M, y, resid, st) : cudaErrorInvalidValue;
-    }
-    return cudaErrorInvalidValue;
+    return cudaSuccess;
 }
 
 /* status word of the launches so far on the current device (0 = no wait ever gave up); synchronises */

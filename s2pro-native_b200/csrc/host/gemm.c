@@ -217,14 +217,11 @@ s2p_status s2p_linear_prepare_int8_site(s2p_linear* lin, s2p_qsite site, cudaStr
 
 /* GEMV for decode-sized M of any count: rows are independent products, so M > 16
  * is served in slices of 16 with results identical to one-row calls. */
-/* the tensor-core kernel copies a K slab's group scales (64 / group of them) as one aligned piece of
- * 4 to 16 bytes: the row's scale count must be a multiple of the piece */
+/* the tensor-core kernel copies the group scales of 256 k at a time, as 4 to 32 aligned bytes */
 static int tc_scales_ok(const s2p_linear* lin) {
     const int g = lin->q_group;
     if (!g) return 1;
-    if (g < (lin->q_packed ? 32 : 16) || (g & (g - 1))) return 0;
-    const int nsc = 64 / g, cpy = nsc < 2 ? 2 : nsc;
-    return (lin->in_features / g) % cpy == 0;
+    return g >= (lin->q_packed ? 32 : 16) && g <= 128 && !(g & (g - 1));
 }
 
 /* 1 when M decode rows of this linear go to the tensor-core kernel */
@@ -236,7 +233,7 @@ int s2p_linear_rows_on_tc(const s2p_linear* lin, int M) {
         const int v = e ? atoi(e) : 0;
         tc_min_rows = (v >= 2 && v <= S2P_INT8_GEMV_MAX_M) ? v : S2P_INT8_GEMV_MAX_M + 1;
     }
-    return M >= tc_min_rows && M <= 256 && K % 128 == 0 && !s2p_env_is_one("S2P_NO_TC") &&
+    return M >= tc_min_rows && M <= 256 && K % 256 == 0 && !s2p_env_is_one("S2P_NO_TC") &&
            tc_scales_ok(lin);
 }
 

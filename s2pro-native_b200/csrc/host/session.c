@@ -157,6 +157,13 @@ static s2p_status lin_add(s2p_model* m, const s2p_linear* lin, const void* in, v
 }
 
 static int attn_workers_for(int rows) {
+    static int forced = -1; /* S2P_ATTN_WORKERS=n (1..16) overrides the choice */
+    if (forced < 0) {
+        const char* e = getenv("S2P_ATTN_WORKERS");
+        const int v = e ? atoi(e) : 0;
+        forced = (v >= 1 && v <= 16) ? v : 0;
+    }
+    if (forced) return forced;
     int w = 2048 / (rows * S2P_SLOW_KV_HEADS);
     return w < 1 ? 1 : (w > 16 ? 16 : w);
 }
