@@ -23,10 +23,10 @@
 namespace s2p {
 
 
-template <bool KV8, bool PREP>
+template <bool KV8, bool PREP, int HPT>
 __global__ void __launch_bounds__(512) k_attn_decode(AttnArgs a, AttnPrep pz) {
     __shared__ AttnSmem<KV8> sm;
-    attn_decode_cta<KV8, PREP>(a, pz, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.z, sm);
+    attn_decode_cta<KV8, PREP, HPT>(a, pz, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.z, sm);
 }
 
 cudaError_t launch_attn_decode(const AttnArgs& a, const AttnPrep* prep, int rows, cudaStream_t st) {
@@ -34,13 +34,15 @@ cudaError_t launch_attn_decode(const AttnArgs& a, const AttnPrep* prep, int rows
     if (a.q_heads != a.kv_heads * 4 || !a.part || !a.counters || a.workers < 1) return cudaErrorInvalidValue;
     dim3 grid((unsigned)rows, (unsigned)a.kv_heads, (unsigned)a.workers);
     AttnPrep pz = {};
+    /* one score chain per thread (HPT 1): sharing a key's conversion between the heads of a position
+     * (HPT 2 or 4) measured slower on a lockstep batch of 32, fewer warps being busy in the score phase */
     if (prep) {
         pz = *prep;
-        if (a.kv8) k_attn_decode<true, true><<<grid, 512, 0, st>>>(a, pz);
-        else k_attn_decode<false, true><<<grid, 512, 0, st>>>(a, pz);
+        if (a.kv8) k_attn_decode<true, true, 1><<<grid, 512, 0, st>>>(a, pz);
+        else k_attn_decode<false, true, 1><<<grid, 512, 0, st>>>(a, pz);
     } else {
-        if (a.kv8) k_attn_decode<true, false><<<grid, 512, 0, st>>>(a, pz);
-        else k_attn_decode<false, false><<<grid, 512, 0, st>>>(a, pz);
+        if (a.kv8) k_attn_decode<true, false, 1><<<grid, 512, 0, st>>>(a, pz);
+        else k_attn_decode<false, false, 1><<<grid, 512, 0, st>>>(a, pz);
     }
     return cudaGetLastError();
 }

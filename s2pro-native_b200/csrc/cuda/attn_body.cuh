@@ -42,7 +42,7 @@ __device__ __forceinline__ float prep_load(const AttnPrep& pz, size_t idx) {
     return ldcg_bf(pz.qkv + idx);
 }
 
-template <bool KV8, bool PREP>
+template <bool KV8, bool PREP, int HPT>
 __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, int kvh, int wk, int workers,
                                 AttnSmem<KV8>& sm) {
     constexpr int VB = AttnSmem<KV8>::VB;
@@ -183,53 +183,75 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
         }
         S2P_CTA_SYNC();
 
-        /* scores: thread (head g4, position t4), one chain each */
-        const int g4 = (tid >> 6) & 3, t4 = tid & 63;
-        float d = -INFINITY;
-        if (tid < 256 && t4 < cnt) {
-            d = 0.f;
+        /* scores: thread (head group, position t4) carries the chains of HPT heads of its position, so a
+         * cached key is read and converted once for them (HPT 1: lowest latency; 4: fewest instructions) */
+        constexpr int QT = 256 / HPT;
+        const int g4 = (tid >> 6) & 3, t4 = tid & 63, gq = (tid >> 6) * HPT;
+        float d[HPT];
+#pragma unroll
+        for (int h = 0; h < HPT; h++) d[h] = -INFINITY;
+        if (tid < QT && t4 < cnt) {
+#pragma unroll
+            for (int h = 0; h < HPT; h++) d[h] = 0.f;
+            const uint32_t* kw = reinterpret_cast<const uint32_t*>(tile + t4 * TS);
             if (!KV8) {
-                const uint32_t* kw = reinterpret_cast<const uint32_t*>(tile + t4 * TS);
-                const float4* q4 = reinterpret_cast<const float4*>(sq[g4]);
-#pragma unroll 8
+#pragma unroll 4
                 for (int e = 0; e < 32; e++) {
                     const uint32_t w0 = kw[2 * e], w1 = kw[2 * e + 1];
-                    const float4 qv = q4[e];
-                    d = __fmaf_rn(qv.x, bf_lo(w0), d);
-                    d = __fmaf_rn(qv.y, bf_hi(w0), d);
-                    d = __fmaf_rn(qv.z, bf_lo(w1), d);
-                    d = __fmaf_rn(qv.w, bf_hi(w1), d);
+                    const float k0 = bf_lo(w0), k1 = bf_hi(w0), k2 = bf_lo(w1), k3 = bf_hi(w1);
+#pragma unroll
+                    for (int h = 0; h < HPT; h++) {
+                        const float4 qv = reinterpret_cast<const float4*>(sq[gq + h])[e];
+                        d[h] = __fmaf_rn(qv.x, k0, d[h]);
+                        d[h] = __fmaf_rn(qv.y, k1, d[h]);
+                        d[h] = __fmaf_rn(qv.z, k2, d[h]);
+                        d[h] = __fmaf_rn(qv.w, k3, d[h]);
+                    }
                 }
             } else {
                 /* four codes per shared-memory word, four query values per load; the chain order is unchanged */
-                const uint32_t* kw = reinterpret_cast<const uint32_t*>(tile + t4 * TS);
-                const float4* q4 = reinterpret_cast<const float4*>(sq[g4]);
 #pragma unroll
                 for (int gi = 0; gi < 4; gi++) {
-                    float pp = 0.f;
+                    float pp[HPT];
+#pragma unroll
+                    for (int h = 0; h < HPT; h++) pp[h] = 0.f;
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
                         const uint32_t w = kw[gi * 8 + e];
-                        const float4 qv = q4[gi * 8 + e];
-                        pp = __fmaf_rn(qv.x, (float)(int8_t)(w & 0xFFu), pp);
-                        pp = __fmaf_rn(qv.y, (float)(int8_t)((w >> 8) & 0xFFu), pp);
-                        pp = __fmaf_rn(qv.z, (float)(int8_t)((w >> 16) & 0xFFu), pp);
-                        pp = __fmaf_rn(qv.w, (float)(int8_t)(w >> 24), pp);
+                        const float k0 = (float)(int8_t)(w & 0xFFu), k1 = (float)(int8_t)((w >> 8) & 0xFFu);
+                        const float k2 = (float)(int8_t)((w >> 16) & 0xFFu), k3 = (float)(int8_t)(w >> 24);
+#pragma unroll
+                        for (int h = 0; h < HPT; h++) {
+                            const float4 qv = reinterpret_cast<const float4*>(sq[gq + h])[gi * 8 + e];
+                            pp[h] = __fmaf_rn(qv.x, k0, pp[h]);
+                            pp[h] = __fmaf_rn(qv.y, k1, pp[h]);
+                            pp[h] = __fmaf_rn(qv.z, k2, pp[h]);
+                            pp[h] = __fmaf_rn(qv.w, k3, pp[h]);
+                        }
                     }
-                    d = __fmaf_rn(pp, __half2float(ssc[t4 * 4 + gi]), d);
+                    const float ks = __half2float(ssc[t4 * 4 + gi]);
+#pragma unroll
+                    for (int h = 0; h < HPT; h++) d[h] = __fmaf_rn(pp[h], ks, d[h]);
                 }
             }
         }
-        if (tid < 256) { /* split max per head: two warps of 32 slots each */
-            const float mx = warp_tree_max(d);
-            if ((tid & 31) == 0) red[0][tid >> 5] = mx;
+        if (tid < QT) { /* split max per head: two warps of 32 slots each */
+#pragma unroll
+            for (int h = 0; h < HPT; h++) {
+                const float mx = warp_tree_max(d[h]);
+                if ((tid & 31) == 0) red[0][(gq + h) * 2 + ((tid >> 5) & 1)] = mx;
+            }
         }
         S2P_CTA_SYNC();
-        float m = 0.f;
-        if (tid < 256) {
-            m = fmaxf(red[0][2 * g4], red[0][2 * g4 + 1]);
-            sc[g4][t4] = (t4 < cnt) ? expf(d - m) : 0.f;
+        if (tid < QT) {
+#pragma unroll
+            for (int h = 0; h < HPT; h++) {
+                const float mh = fmaxf(red[0][2 * (gq + h)], red[0][2 * (gq + h) + 1]);
+                sc[gq + h][t4] = (t4 < cnt) ? expf(d[h] - mh) : 0.f;
+            }
         }
+        float m = 0.f;
+        if (tid < 256) m = fmaxf(red[0][2 * g4], red[0][2 * g4 + 1]);
         S2P_CTA_SYNC();
         if (tid < 256 && t4 < 32) { /* exp-sum: pairs (t, t+32), then 16..1 */
             const float x = warp_tree_sum(sc[g4][t4] + sc[g4][t4 + 32]);

@@ -600,10 +600,10 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
                 const AttnPrep pz = {s.qkv, s.q_norm, s.k_norm, P.eps, P.rope_base,
                                      reinterpret_cast<const uint32_t*>(s.qkv), in_tag, P.status};
                 if (P.kv8)
-                    attn_decode_cta<true, true>(a, pz, 0, cta / workers, cta % workers, workers,
+                    attn_decode_cta<true, true, 1>(a, pz, 0, cta / workers, cta % workers, workers,
                                                 *reinterpret_cast<AttnSmem<true>*>(work));
                 else
-                    attn_decode_cta<false, true>(a, pz, 0, cta / workers, cta % workers, workers,
+                    attn_decode_cta<false, true, 1>(a, pz, 0, cta / workers, cta % workers, workers,
                                                  *reinterpret_cast<AttnSmem<false>*>(work));
             }
             break;

@@ -181,8 +181,21 @@ def test_single_pass_attention(libs, kv8, pos0, rows):
 @pytest.mark.parametrize("kv8", [0, 1])
 @pytest.mark.parametrize("lens", [[1], [63], [64], [65], [200, 7, 713], [1024]])
 def test_split_k_decode_attention(libs, kv8, lens):
+    _split_k_decode_attention(libs, kv8, lens, 1088, (1, 3, 16))
+
+
+@pytest.mark.parametrize("kv8", [1, 0])
+def test_split_k_decode_attention_batch_of_32(libs, kv8):
+    """A lockstep batch: 32 rows with contexts of 1300-3100 positions (the shared 1024-token prefix plus
+    256-2048 own tokens), 8 workers per (row, kv head) as the batched tick launches it (the grid is large
+    enough for the variant in which one thread scores all four heads of a position)."""
+    lens = [int(v) for v in np.random.default_rng(7).integers(1300, 3101, size=32)]
+    _split_k_decode_attention(libs, kv8, lens, 3136, (8,))
+
+
+def _split_k_decode_attention(libs, kv8, lens, max_seq, workers_list):
     _, tl, ref = libs
-    rows, max_seq = len(lens), 1088
+    rows = len(lens)
     caches = []
     for r in range(rows):
         kvbuf, kvs, kvref, k, v = _filled_cache(max_seq, kv8, 40 + 2 * r)
@@ -205,7 +218,7 @@ def test_split_k_decode_attention(libs, kv8, lens):
     else:
         assert ref.s2pk_attention_decode(p(q), p(kptr), p(vptr), p(o_ref), rows, QH, KVH, HD, p(pos), max_seq, max_len, p(part), None) == 0
     torch.cuda.synchronize()
-    for workers in (1, 3, 16):
+    for workers in workers_list:
         o = torch.zeros_like(q)
         ctr = torch.zeros(rows * KVH, dtype=torch.int32, device="cuda")
         base = ptr_t([c[0].data_ptr() for c in caches]); sbase = ptr_t([c[1].data_ptr() for c in caches])
