@@ -104,22 +104,21 @@ __device__ __forceinline__ void sk_cp_wait(int n) {
 
 constexpr int SK_SUPER_K = 256; /* K extent of one weight copy round: 128 (INT4) or 256 (INT8) contiguous bytes per row */
 
+constexpr int SK_STAGES = 3; /* converted [A | B] stages between the converting warps and the MMA warp */
+
 template <int WK, int NT, int KCP> struct SkGeom {
-    static constexpr int KC = KCP;                                        /* K extent of a converted slab: NT / 4 gives one (INT4) or two (INT8) 16-byte units of codes per thread */
+    static constexpr int KC = KCP;                                        /* K extent of a converted slab */
     static constexpr int SPS = SK_SUPER_K / KC;                           /* slabs per weight copy round */
     static constexpr int UPR = (WK == WK_INT4_PACK) ? KC / 32 : KC / 16;  /* 16-byte units of packed codes per row and slab */
-    static constexpr int UPRS = UPR * SPS;                                /* ... per row and copy round: 8 or 16 */
-    static constexpr int PITCHS = UPRS * 16;
-    static constexpr int WS_BYTES = SK_BM * PITCHS;
-    static constexpr int SC_ROW = 32;                                     /* room per row for the round's scales */
-    static constexpr int SC_BYTES = (WK == WK_INT8_CH) ? 0 : SK_BM * SC_ROW;
-    static constexpr int SUP_BYTES = WS_BYTES + SC_BYTES;
+    static constexpr int PITCHS = UPR * SPS * 16;                         /* bytes of a row per copy round */
     static constexpr int WPU = (WK == WK_INT4_PACK) ? 32 : 16;            /* weights per 16-byte unit */
-    static constexpr int NLD = UPR * SK_BM / NT;                          /* units converted per thread and slab: 1 (INT4) or 2 (INT8) */
-    static constexpr int NCP = UPRS * SK_BM / NT;                         /* units copied per thread and round */
-    static constexpr int RSTEP = NT / UPRS;                               /* rows between a thread's copies */
+    static constexpr int NLD = UPR * SK_BM / NT;                          /* units converted per thread and slab */
+    static constexpr int NCP = NLD * SPS;                                 /* units copied per thread and round */
+    static constexpr int WS_BYTES = NCP * NT * 16;                        /* raw codes of a round: [unit of the thread][thread] */
+    static constexpr int SC_BYTES = (WK == WK_INT8_CH) ? 0 : NCP * NT * 4; /* one 4-byte pair of scales per unit */
+    static constexpr int SUP_BYTES = WS_BYTES + SC_BYTES;
     static constexpr int A_BYTES = SK_BM * KC * 2;                        /* converted stage */
-    static_assert(NT % SK_BM == 0 && NT % UPRS == 0, "thread -> (row, unit) maps assume this");
+    static_assert(NT % SK_BM == 0 && NLD >= 1, "thread -> (row, unit) map assumes this");
 };
 
 /* bf16 x 8 -> f16 x 8 for the B tile.  INT4 slabs keep the order their conversion produces
@@ -143,34 +142,40 @@ template <int WK> __device__ __forceinline__ uint4 sk_x_unit(const uint4& v) {
 }
 
 template <int WK, int NT, int KCP>
-__global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
-                                                            int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
-                                                            int lgNB, int D, int DW, int n_split_tiles, int KS,
-                                                            __nv_bfloat16* y, const __nv_bfloat16* resid,
-                                                            float* __restrict__ partial, unsigned* __restrict__ arrivals) {
+__global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
+                                                          int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
+                                                          int lgNB, int D, int DW, int n_split_tiles, int KS,
+                                                          __nv_bfloat16* y, const __nv_bfloat16* resid,
+                                                          float* __restrict__ partial, unsigned* __restrict__ arrivals) {
     /* resid (may alias y): y = bf16(f32(resid) + f32(bf16(product))), the residual add of the decode layers */
     /* The last n_split_tiles row tiles have their K range split over KS CTAs each; those CTAs come first
      * in the grid (short pieces first, whole tiles after them: the tail of the grid stays balanced).  Each
      * piece leaves its f32 partial in `partial`[split tile][piece][batch row][128] and the last piece of a
      * tile to arrive adds them in piece order. */
-    /* Two rings of raw data are filled by asynchronous copies ahead of the conversion: DW copy rounds of
-     * weights and scales (256 k each), D slabs of activations.  They keep enough bytes in flight to stream
-     * from HBM, in runs DRAM serves well. */
-    /* Everything a thread needs per slab (source pointers, offsets inside a ring slot and a stage) is
-     * worked out once; the loop only advances pointers: the conversion is bound by instruction issue. */
+    /* Roles: NT converting threads and one MMA warp, coupled only by mbarriers.
+     *  - A converting thread copies, converts and stores its own (row, unit) of every slab: raw codes and
+     *    scales travel by asynchronous copies into thread-private places of two rings (DW copy rounds of
+     *    weights of 256 k, D slabs of activations), so no thread waits for another's copy; a stage is
+     *    handed over by one arrival per warp on full[stage] and taken back on done[stage], which the
+     *    tensor core signals when the MMAs that read the stage have completed.
+     *  - The MMA warp waits for full[stage], issues the stage's MMAs and commits them to done[stage].
+     * Copies, conversion and MMAs of different slabs overlap; nothing in the loop is a CTA-wide barrier. */
     typedef SkGeom<WK, NT, KCP> G;
-    constexpr int KC = G::KC;
+    constexpr int KC = G::KC, NST = SK_STAGES;
     int* status = &g_sk_status;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int NB = 1 << lgNB;
     const int b_bytes = NB * KC * 2;
     const int x_units = NB * (KC / 8);
     const int x_bytes = x_units * 16;
-    unsigned char* xring = smem + 2 * (G::A_BYTES + b_bytes);
+    unsigned char* stage_b0 = smem + NST * G::A_BYTES;
+    unsigned char* xring = stage_b0 + NST * b_bytes;
     unsigned char* wring = xring + D * x_bytes;
-    uint64_t* done = reinterpret_cast<uint64_t*>(wring + DW * G::SUP_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 2);
+    uint64_t* full = reinterpret_cast<uint64_t*>(wring + DW * G::SUP_BYTES);
+    uint64_t* done = full + NST;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + NST);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool mma_warp = warp == NT / 32;
     const int n_tiles = (N + SK_BM - 1) / SK_BM, n_pieces = n_split_tiles * KS;
     const bool piece = (int)blockIdx.x < n_pieces;
     const int stile = piece ? (int)blockIdx.x / KS : 0;                     /* index among the split tiles */
@@ -186,150 +191,164 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
-        mbar_init(done, 1);
-        mbar_init(done + 1, 1);
+        for (int i = 0; i < NST; i++) {
+            mbar_init(full + i, NT / 32);
+            mbar_init(done + i, 1);
+        }
         mbar_init_fence();
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
     /* the K range of this CTA, in whole copy rounds */
     const int nsup_all = K / SK_SUPER_K;
     const int sup_first = nsup_all * ks / ksn, nsup = nsup_all * (ks + 1) / ksn - sup_first;
     const int it_first = sup_first * G::SPS, nk = nsup * G::SPS;
-
-    /* ---- copy side.  Weights: UPRS neighbouring threads read one row's contiguous run of a whole round
-     * (128 or 256 bytes: DRAM serves whole lines of a row at a time instead of 32-byte pieces of many rows);
-     * the unit index inside the row is XOR-swizzled so that 8 consecutive rows read back without bank
-     * conflicts.  Rows beyond N (last tile) repeat row N - 1: their outputs are never stored. */
-    const int cp_c = tid % G::UPRS, cp_row0 = tid / G::UPRS;
-    const unsigned char* wsrc = static_cast<const unsigned char*>(w) + (size_t)sup_first * (G::PITCHS) + cp_c * 16;
-    const __half* sc_src = nullptr;
-    const int sc_elems = SK_SUPER_K >> gshift; /* scales per row and round: 2 .. 16 */
-    if (WK != WK_INT8_CH && tid < SK_BM)
-        sc_src = static_cast<const __half*>(scales) + (size_t)min(n0 + tid, N - 1) * (K >> gshift) + (size_t)sup_first * sc_elems;
-    int w_wslot = 0, w_issued = 0;
-    auto issue_w = [&]() {
-        unsigned char* sup = wring + w_wslot;
-#pragma unroll
-        for (int i = 0; i < G::NCP; i++) {
-            const int row = cp_row0 + i * G::RSTEP;
-            sk_cp16(sup + row * G::PITCHS + ((cp_c ^ (row & 7)) << 4), wsrc + (size_t)min(n0 + row, N - 1) * row_bytes);
-        }
-        wsrc += G::PITCHS;
-        if (sc_src) {
-            sk_cp_scales(sup + G::WS_BYTES + tid * G::SC_ROW, sc_src, sc_elems * 2);
-            sc_src += sc_elems;
-        }
-        w_issued++;
-        w_wslot += G::SUP_BYTES;
-        if (w_wslot == DW * G::SUP_BYTES) w_wslot = 0;
-    };
-    /* activations, slab by slab: unit c = [k / 8][batch row] sits in the slot where the B tile wants it;
-     * c = tid + NT u; rows beyond the batch repeat row M - 1 (their columns are never stored) */
-    const int x_mine = tid < x_units ? (x_units + NT - 1 - tid) / NT : 0; /* units of this thread */
-    const int x_step = (NT >> lgNB) * 8;                                   /* elements between them (NB <= NT) */
-    const __nv_bfloat16* xsrc = x + (size_t)min(tid & (NB - 1), M - 1) * K + (size_t)it_first * KC + (tid >> lgNB) * 8;
-    int x_wslot = 0, x_issued = 0;
-    auto issue_x = [&]() {
-        unsigned char* slot = xring + x_wslot + tid * 16;
-        for (int u = 0; u < x_mine; u++) sk_cp16(slot + u * (NT * 16), xsrc + u * x_step);
-        xsrc += KC;
-        x_issued++;
-        x_wslot += x_bytes;
-        if (x_wslot == D * x_bytes) x_wslot = 0;
-    };
-    /* One copy group per slab round, empty ones included, so that the group count tells what has landed:
-     * round v carries the activations of slab v + D - 1 and, when v is a multiple of SPS, the weights of
-     * copy round v / SPS + DW - 1.  With D <= SPS (DW - 1) + 1 (the host's choice), "at most D - 2 groups
-     * pending" at the end of round v means slab v + 1 is complete, weights included. */
-    for (int v = -G::SPS * (DW - 1); v < 0; v++) {
-        if (v + D - 1 >= 0 && x_issued < nk) issue_x();
-        if ((-v) % G::SPS == 0 && w_issued < nsup) issue_w();
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-
-    /* ---- conversion side: thread -> (row, unit q) of the slab; constant offsets into a copy round and a stage */
-    const int cv_row = tid & (SK_BM - 1), cv_q0 = tid >> 7; /* units q0 + i NT / 128 */
-    const int rd_row = cv_row * G::PITCHS, rd_x = cv_row & 7;
-    const int a_off0 = (cv_q0 * (G::WPU / 8) * SK_BM + cv_row) * 16;
-    const int sc_off = G::WS_BYTES + cv_row * G::SC_ROW;
-
-    sk_cp_wait(D - 2); /* slab 0 */
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-    /* instruction descriptor: D f32, A and B f16, both K-major, N = NB, M = 128 */
-    const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(SK_BM >> 4) << 24);
-    const uint64_t desc_a0 = sk_smem_desc(smem_u32(smem), SK_BM * 16, 128);
-    const uint64_t desc_b0 = sk_smem_desc(smem_u32(smem + 2 * G::A_BYTES), (uint32_t)NB * 16, 128);
-
     bool ok = true;
-    int x_rslot = 0, w_rslot = 0, j_in = 0; /* read offsets into the rings; slab index inside the copy round */
-    for (int it = 0; it < nk && ok; it++) {
-        const int s = it & 1;
-        /* the slots the next copies fill were read by every thread before the barrier that ended the last round */
-        if (x_issued < nk) issue_x();
-        if (j_in == 0 && w_issued < nsup) issue_w();
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (it >= 2) ok = mbar_wait_bounded(done + s, ((unsigned)(it >> 1) - 1u) & 1u, status); /* the MMAs that read this stage */
-        if (!ok) break;
-        const unsigned char* sup = wring + w_rslot;
-        unsigned char* A = smem + s * G::A_BYTES;
-        unsigned char* B = smem + 2 * G::A_BYTES + s * b_bytes;
-        /* weights: A[k / 8][row] */
+
+    if (!mma_warp) {
+        /* ---- this thread's row and units: unit q0 + i NT / 128 of every slab (i < NLD); rows beyond N (last
+         * tile) repeat row N - 1: their outputs are never stored */
+        const int cv_row = tid & (SK_BM - 1), cv_q0 = tid >> 7;
+        const int grow_c = min(n0 + cv_row, N - 1);
+        const unsigned char* wsrc = static_cast<const unsigned char*>(w) + (size_t)grow_c * row_bytes + (size_t)sup_first * G::PITCHS;
+        const int sc_round = SK_SUPER_K >> gshift; /* scales per row and round */
+        const __half* sc_src = nullptr;
+        if (WK != WK_INT8_CH) sc_src = static_cast<const __half*>(scales) + (size_t)grow_c * (K >> gshift) + (size_t)sup_first * sc_round;
+        int w_wslot = 0, w_issued = 0;
+        auto issue_w = [&]() {
+            unsigned char* sup = wring + w_wslot + tid * 16;
 #pragma unroll
-        for (int i = 0; i < G::NLD; i++) {
-            const int q = cv_q0 + i * (NT / SK_BM), c = j_in * G::UPR + q;
-            const uint4 pk = *reinterpret_cast<const uint4*>(sup + rd_row + ((c ^ rd_x) << 4));
-            __half2 sc2 = __float2half2_rn(1.f);
-            if (WK != WK_INT8_CH) sc2 = __half2half2(reinterpret_cast<const __half*>(sup + sc_off)[(c * G::WPU) >> gshift]);
-            uint4* Au = reinterpret_cast<uint4*>(A + a_off0 + i * ((NT / SK_BM) * (G::WPU / 8) * SK_BM * 16));
-            if (WK == WK_INT4_PACK) {
-                const uint32_t ws[4] = {pk.x, pk.y, pk.z, pk.w};
+            for (int j = 0; j < G::SPS; j++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) Au[j * SK_BM] = sk_int4_chunk(ws[j], sc2);
-            } else {
-                Au[0] = sk_int8_chunk<WK == WK_INT8_GRP>(pk.x, pk.y, sc2);
-                Au[SK_BM] = sk_int8_chunk<WK == WK_INT8_GRP>(pk.z, pk.w, sc2);
+                for (int i = 0; i < G::NLD; i++) {
+                    const int c = j * G::UPR + cv_q0 + i * (NT / SK_BM), u = j * G::NLD + i;
+                    sk_cp16(sup + u * (NT * 16), wsrc + c * 16);
+                    if (WK != WK_INT8_CH) /* the aligned pair of scales holding the unit's */
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(wring + w_wslot + G::WS_BYTES + (u * NT + tid) * 4)),
+                                     "l"(sc_src + (((c * G::WPU) >> gshift) & ~1)) : "memory");
+                }
+            wsrc += G::PITCHS;
+            if (WK != WK_INT8_CH) sc_src += sc_round;
+            w_issued++;
+            w_wslot += G::SUP_BYTES;
+            if (w_wslot == DW * G::SUP_BYTES) w_wslot = 0;
+        };
+        /* activations, slab by slab: unit c = [k / 8][batch row] sits in the slot where the B tile wants it;
+         * c = tid + NT u; rows beyond the batch repeat row M - 1 (their columns are never stored) */
+        const int x_mine = tid < x_units ? (x_units + NT - 1 - tid) / NT : 0; /* units of this thread */
+        const int x_step = (NT >> lgNB) * 8;                                   /* elements between them (NB <= NT) */
+        const __nv_bfloat16* xsrc = x + (size_t)min(tid & (NB - 1), M - 1) * K + (size_t)it_first * KC + (tid >> lgNB) * 8;
+        int x_wslot = 0, x_issued = 0;
+        auto issue_x = [&]() {
+            unsigned char* slot = xring + x_wslot + tid * 16;
+            for (int u = 0; u < x_mine; u++) sk_cp16(slot + u * (NT * 16), xsrc + u * x_step);
+            xsrc += KC;
+            x_issued++;
+            x_wslot += x_bytes;
+            if (x_wslot == D * x_bytes) x_wslot = 0;
+        };
+        /* One copy group per slab round, empty ones included, so that the group count tells what has landed:
+         * round v carries the activations of slab v + D - 1 and, when v is a multiple of SPS, the weights of
+         * copy round v / SPS + DW - 1.  With D <= SPS (DW - 1) + 1 (the host's choice), "at most D - 2 groups
+         * pending" at the end of round v means this thread's share of slab v + 1 has landed, weights included. */
+        for (int v = -G::SPS * (DW - 1); v < 0; v++) {
+            if (v + D - 1 >= 0 && x_issued < nk) issue_x();
+            if ((-v) % G::SPS == 0 && w_issued < nsup) issue_w();
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        sk_cp_wait(D - 2); /* slab 0 */
+
+        const int a_off0 = (cv_q0 * (G::WPU / 8) * SK_BM + cv_row) * 16;
+        int x_rslot = 0, w_rslot = 0, j_in = 0; /* read offsets into the rings; slab index inside the copy round */
+        int s = 0;                              /* stage of slab it, and whether it has been used before */
+        unsigned done_parity = 1;               /* parity of the completion of done[s] that frees the stage: it / NST - 1 */
+        for (int it = 0; it < nk; it++) {
+            /* the places the next copies fill were read by this thread one round ago */
+            if (x_issued < nk) issue_x();
+            if (j_in == 0 && w_issued < nsup) issue_w();
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            if (it >= NST) ok = mbar_wait_bounded(done + s, done_parity, status); /* the MMAs that read this stage */
+            if (!ok) break;
+            const unsigned char* sup = wring + w_rslot;
+            unsigned char* A = smem + s * G::A_BYTES;
+            unsigned char* B = stage_b0 + s * b_bytes;
+            /* weights: A[k / 8][row] */
+#pragma unroll
+            for (int i = 0; i < G::NLD; i++) {
+                const int u = j_in * G::NLD + i;
+                const uint4 pk = *reinterpret_cast<const uint4*>(sup + (u * NT + tid) * 16);
+                __half2 sc2 = __float2half2_rn(1.f);
+                if (WK != WK_INT8_CH) {
+                    const int c = j_in * G::UPR + cv_q0 + i * (NT / SK_BM);
+                    sc2 = __half2half2(reinterpret_cast<const __half*>(sup + G::WS_BYTES + (u * NT + tid) * 4)[((c * G::WPU) >> gshift) & 1]);
+                }
+                uint4* Au = reinterpret_cast<uint4*>(A + a_off0 + i * ((NT / SK_BM) * (G::WPU / 8) * SK_BM * 16));
+                if (WK == WK_INT4_PACK) {
+                    const uint32_t ws[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+                    for (int j = 0; j < 4; j++) Au[j * SK_BM] = sk_int4_chunk(ws[j], sc2);
+                } else {
+                    Au[0] = sk_int8_chunk<WK == WK_INT8_GRP>(pk.x, pk.y, sc2);
+                    Au[SK_BM] = sk_int8_chunk<WK == WK_INT8_GRP>(pk.z, pk.w, sc2);
+                }
             }
+            /* activations: B[k / 8][batch row] */
+            for (int u = 0; u < x_mine; u++)
+                *reinterpret_cast<uint4*>(B + (tid + u * NT) * 16) = sk_x_unit<WK>(*reinterpret_cast<const uint4*>(xring + x_rslot + (tid + u * NT) * 16));
+            x_rslot += x_bytes;
+            if (x_rslot == D * x_bytes) x_rslot = 0;
+            if (++j_in == G::SPS) {
+                j_in = 0;
+                w_rslot += G::SUP_BYTES;
+                if (w_rslot == DW * G::SUP_BYTES) w_rslot = 0;
+            }
+            fence_proxy_async_smem(); /* these generic-proxy stores are read by the tensor core (async proxy) */
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(full + s)) : "memory");
+            if (++s == NST) { s = 0; done_parity ^= 1u; }
+            sk_cp_wait(D - 2); /* this thread's share of slab it + 1 */
         }
-        /* activations: B[k / 8][batch row] */
-        for (int u = 0; u < x_mine; u++)
-            *reinterpret_cast<uint4*>(B + (tid + u * NT) * 16) = sk_x_unit<WK>(*reinterpret_cast<const uint4*>(xring + x_rslot + (tid + u * NT) * 16));
-        x_rslot += x_bytes;
-        if (x_rslot == D * x_bytes) x_rslot = 0;
-        if (++j_in == G::SPS) {
-            j_in = 0;
-            w_rslot += G::SUP_BYTES;
-            if (w_rslot == DW * G::SUP_BYTES) w_rslot = 0;
-        }
-        sk_cp_wait(D - 2);        /* this thread's share of slab it + 1; the barrier makes everyone's visible */
-        fence_proxy_async_smem(); /* these generic-proxy stores are read by the tensor core (async proxy) */
-        __syncthreads();
-        if (tid == 0) {
+        asm volatile("cp.async.wait_all;" ::: "memory"); /* nothing of this thread's is in flight past here */
+    } else {
+        /* ---- the MMA warp (its lane 0 issues) */
+        /* instruction descriptor: D f32, A and B f16, both K-major, N = NB, M = 128 */
+        const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(SK_BM >> 4) << 24);
+        const uint64_t desc_a0 = sk_smem_desc(smem_u32(smem), SK_BM * 16, 128);
+        const uint64_t desc_b0 = sk_smem_desc(smem_u32(stage_b0), (uint32_t)NB * 16, 128);
+        int s = 0;
+        unsigned full_parity = 0;
+        for (int it = 0; it < nk; it++) {
+            ok = mbar_wait_bounded(full + s, full_parity, status);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            /* the start-address field counts 16-byte units: stage s and K step kk are plain additions */
-            const uint64_t da0 = desc_a0 + (uint64_t)((s * G::A_BYTES) >> 4);
-            const uint64_t db0 = desc_b0 + (uint64_t)((s * b_bytes) >> 4);
+            if (lane == 0) {
+                /* the start-address field counts 16-byte units: stage s and K step kk are plain additions */
+                const uint64_t da0 = desc_a0 + (uint64_t)((s * G::A_BYTES) >> 4);
+                const uint64_t db0 = desc_b0 + (uint64_t)((s * b_bytes) >> 4);
 #pragma unroll
-            for (int kk = 0; kk < KC / 16; kk++) {
-                const uint64_t da = da0 + (uint64_t)(kk * 2 * SK_BM);
-                const uint64_t db = db0 + (uint64_t)(kk * 2 * NB);
-                const uint32_t accumulate = (it > 0 || kk > 0) ? 1u : 0u;
-                asm volatile(
-                    "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                    "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                    ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+                for (int kk = 0; kk < KC / 16; kk++) {
+                    const uint64_t da = da0 + (uint64_t)(kk * 2 * SK_BM);
+                    const uint64_t db = db0 + (uint64_t)(kk * 2 * NB);
+                    const uint32_t accumulate = (it > 0 || kk > 0) ? 1u : 0u;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+                }
+                /* arrives on the barrier once every MMA issued so far has completed */
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(done + s)) : "memory");
             }
-            /* arrives on the barrier once every MMA issued so far has completed */
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(done + s)) : "memory");
+            __syncwarp();
+            if (++s == NST) { s = 0; full_parity ^= 1u; }
         }
     }
-    asm volatile("cp.async.wait_all;" ::: "memory"); /* nothing of this CTA's is in flight past here */
     /* the last commit covers every MMA before it */
-    if (ok) ok = mbar_wait_bounded(done + ((nk - 1) & 1), (unsigned)((nk - 1) >> 1) & 1u, status);
+    if (ok) ok = mbar_wait_bounded(done + ((nk - 1) % NST), (unsigned)((nk - 1) / NST) & 1u, status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) { /* warp w reads TMEM lanes 32 (w % 4) .. + 31 = weight rows; the warps of a lane quarter share the columns */
+    if (ok && !mma_warp) { /* warp w reads TMEM lanes 32 (w % 4) .. + 31 = weight rows; the warps of a lane quarter share the columns */
         const int grow = n0 + (warp & 3) * 32 + lane;
         float rs = 1.f;
         if (WK == WK_INT8_CH && grow < N) rs = static_cast<const float*>(scales)[grow];
@@ -368,7 +387,7 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
         __syncthreads();
         if (tid == 0) s_last = ok && (atomicAdd(arrivals + stile, 1u) == (unsigned)(KS - 1));
         __syncthreads();
-        if (s_last) {
+        if (s_last && !mma_warp) {
             __threadfence();
             /* four outputs per thread and round, the loads of all splits in flight together; the adds keep split order */
             for (int e0 = tid; e0 < SK_BM * M; e0 += NT * 4) {
@@ -404,7 +423,6 @@ __global__ void __launch_bounds__(NT, 512 / NT) k_skinny_tc(const void* __restri
 }
 
 constexpr size_t SK_SMEM_ONE = 226 * 1024; /* one CTA per SM */
-constexpr size_t SK_SMEM_TWO = 111 * 1024; /* two, each with its static kilobyte and the system's */
 constexpr int SK_MAX_DEPTH = 8;
 
 /* scratch for split-K launches: f32 partials [split tile][piece][batch row][128] and one arrival counter per split tile */
@@ -433,9 +451,9 @@ extern "C" cudaError_t skinny_setup(int max_rows) {
     return cudaSuccess;
 }
 
-/* shared memory of a launch: two converted stages, D slabs of raw activations, DW copy rounds of raw weights, barriers */
+/* shared memory of a launch: the converted stages, D slabs of raw activations, DW copy rounds of raw weights, barriers */
 template <int WK, int NT, int KCP> static size_t sk_fixed_bytes(int NB) {
-    return 2 * ((size_t)SkGeom<WK, NT, KCP>::A_BYTES + (size_t)NB * SkGeom<WK, NT, KCP>::KC * 2) + 64;
+    return SK_STAGES * ((size_t)SkGeom<WK, NT, KCP>::A_BYTES + (size_t)NB * SkGeom<WK, NT, KCP>::KC * 2) + 64;
 }
 /* ring depths that fit `budget` bytes; false if not even the shallowest does */
 template <int WK, int NT, int KCP> static bool sk_depths(int NB, size_t budget, int min_d, int* D, int* DW) {
@@ -465,11 +483,9 @@ static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, int lgN
     }
     const int NB = 1 << lgNB;
     int D = 0, DW = 0;
-    /* two CTAs of 256 threads per SM if rings of useful depth fit in half the shared memory, else one */
-    if (!(NT == 256 && sk_depths<WK, NT, KCP>(NB, SK_SMEM_TWO, 3, &D, &DW)) && !sk_depths<WK, NT, KCP>(NB, SK_SMEM_ONE, 2, &D, &DW))
-        return cudaErrorInvalidValue;
+    if (!sk_depths<WK, NT, KCP>(NB, SK_SMEM_ONE, 2, &D, &DW)) return cudaErrorInvalidValue; /* one CTA per SM */
     const size_t smem = sk_fixed_bytes<WK, NT, KCP>(NB) + (size_t)D * NB * G::KC * 2 + (size_t)DW * G::SUP_BYTES;
-    k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)(tiles - S + S * KS)), NT, smem, st>>>(
+    k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)(tiles - S + S * KS)), NT + 32, smem, st>>>(
         lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, lgNB, D, DW, S, KS, (__nv_bfloat16*)y,
         (const __nv_bfloat16*)resid, partial, arrivals);
     return cudaGetLastError();
