@@ -3,19 +3,23 @@
  * kernels stop at 16 rows, src/sched/int8_gemv.cu:964-986, so there is no bit-exact contract
  * beyond that: results agree with the exact path to f32-accumulation-order tolerance).
  *
- * One CTA owns 128 weight rows (the MMA's M; the batch is its N, padded to a multiple of 16):
- *   - all 256 threads dequantise a [128 rows x 128 k] slab of packed INT4 / INT8 codes into f16
- *     in shared memory (INT4: code x f16 group scale, one rounding of a 15-bit product; INT8
- *     per-channel: the exact code, the row scale is applied to the accumulator), in the
- *     K-major, unswizzled core-matrix layout the instruction reads: 16-byte units
- *     [k / 8][row], i.e. 8 rows x 16 B core matrices, 128 B apart along rows (SBO) and
- *     one [k/8] plane apart along K (LBO);
+ * One CTA owns 128 weight rows (the MMA's M; the batch is its N, padded to a power of two from 16
+ * to 128; a larger batch takes two launches), or a piece of their K range:
+ *   - converting threads (256 or 512) each own one (row, 16-byte unit of packed codes) of every K
+ *     slab: they bring the codes and the unit's scales into shared memory with asynchronous copies
+ *     that run several slabs ahead (weights in rounds of 256 k, activations slab by slab), convert
+ *     them to f16 (INT4: code x f16 group scale, one rounding of a 15-bit product; INT8
+ *     per-channel: the exact code, the row scale is applied to the accumulator) and store them in
+ *     the K-major, unswizzled core-matrix layout the instruction reads: 16-byte units
+ *     [k / 8][row], i.e. 8 rows x 16 B core matrices, 128 B apart along rows (SBO) and one
+ *     [k / 8] plane apart along K (LBO);
  *   - the activations (bf16 -> f16, exact in the normal range) go beside them as [k / 8][batch row];
- *   - one thread issues eight tcgen05.mma (M 128, N = padded batch, K 16, f16 x f16 -> f32 in
- *     TMEM) per slab and commits them to an mbarrier; two slabs are in flight, so the
- *     dequantisation of slab i+1 overlaps the MMAs of slab i;
+ *   - a separate warp issues the tcgen05.mma of a slab (M 128, N = padded batch, K 16,
+ *     f16 x f16 -> f32 in TMEM) when the converting warps have handed the stage over, and commits
+ *     them to the mbarrier that gives the stage back; three stages are in flight;
  *   - epilogue: tcgen05.ld of the accumulator (lane = weight row, column = batch row), row
- *     scale, bf16, stores coalesced over weight rows.
+ *     scale, optional residual, bf16, stores coalesced over weight rows; pieces of a split tile
+ *     leave f32 partials that the last piece to arrive adds in a fixed order.
  * Every mbarrier wait is bounded; on a time-out the kernel records a status code, skips the
  * epilogue, frees its TMEM and returns.
  */
