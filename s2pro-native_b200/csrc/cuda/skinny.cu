@@ -475,28 +475,18 @@ template <int WK, int NT, int KCP> static bool sk_depths(int NB, size_t budget, 
     return false;
 }
 
-template <int WK, int NT, int KCP>
-static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, int lgNB, int tiles, int S, int KS, void* y, const void* resid,
-                                float* partial, unsigned* arrivals, cudaStream_t st) {
-    typedef SkGeom<WK, NT, KCP> G;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
-    const int NB = 1 << lgNB;
-    int D = 0, DW = 0;
-    if (!sk_depths<WK, NT, KCP>(NB, SK_SMEM_ONE, 2, &D, &DW)) return cudaErrorInvalidValue; /* one CTA per SM */
-    const size_t smem = sk_fixed_bytes<WK, NT, KCP>(NB) + (size_t)D * NB * G::KC * 2 + (size_t)DW * G::SUP_BYTES;
-    k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)(tiles - S + S * KS)), NT + 32, smem, st>>>(
-        lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, lgNB, D, DW, S, KS, (__nv_bfloat16*)y,
-        (const __nv_bfloat16*)resid, partial, arrivals);
-    return cudaGetLastError();
-}
+/* What a launch looks like, decided on the host from the shapes alone (no CUDA call: the CPU tests check it) */
+struct SkPlan {
+    int lgNB;        /* batch padded to 1 << lgNB */
+    int tiles;       /* row tiles of 128 */
+    int S, KS;       /* S of them split into KS pieces each (the pieces come first in the grid) */
+    int nt, kc;      /* converting threads, K extent of a slab */
+    int D, DW;       /* ring depths: activation slabs, weight copy rounds */
+    int grid, smem;  /* CTAs, dynamic shared memory */
+};
 
-/* launch policy (skinny_tune): CTAs the split aims at, and the kernel shape: 0 = 256 threads, 64-k slabs (two
- * CTAs per SM fit); 1 = 512 threads, 128-k slabs; 2 = 256 threads, 128-k slabs (fewest instructions per weight) */
+/* launch policy (skinny_tune): CTAs the split aims at, and the kernel shape: 0 = 256 threads, 64-k slabs;
+ * 1 = 512 threads, 128-k slabs (the default, fastest measured); 2 = 256 threads, 128-k slabs */
 static int g_sk_target_ctas = 148;
 static int g_sk_shape = 1;
 extern "C" void skinny_tune(int target_ctas, int shape) {
@@ -504,43 +494,89 @@ extern "C" void skinny_tune(int target_ctas, int shape) {
     g_sk_shape = shape;
 }
 
-template <int WK>
-static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
-    int lgNB = 4; /* the batch is padded to a power of two: the MMA's N */
-    while ((1 << lgNB) < M) lgNB++;
-    const int tiles = (lin->N + SK_BM - 1) / SK_BM;
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
+template <int WK, int NT, int KCP> static bool sk_plan_shape(SkPlan* p) {
+    typedef SkGeom<WK, NT, KCP> G;
+    const int NB = 1 << p->lgNB;
+    if (!sk_depths<WK, NT, KCP>(NB, SK_SMEM_ONE, NT == 256 && KCP == 64 ? 2 : 3, &p->D, &p->DW)) return false;
+    p->nt = NT; p->kc = KCP;
+    p->smem = (int)(sk_fixed_bytes<WK, NT, KCP>(NB) + (size_t)p->D * NB * G::KC * 2 + (size_t)p->DW * G::SUP_BYTES);
+    return true;
+}
+
+/* scratch_rows: batch rows the split-K scratch of the device was set up for (0: none) */
+template <int WK> static bool sk_plan(int N, int K, int M, int scratch_rows, SkPlan* p) {
+    p->lgNB = 4; /* the batch is padded to a power of two: the MMA's N */
+    while ((1 << p->lgNB) < M) p->lgNB++;
+    p->tiles = (N + SK_BM - 1) / SK_BM;
     /* S of the row tiles have their K range split into KS pieces:
      *  - few tiles: all of them, until the grid fills the GPU;
      *  - a few more tiles than SMs: the surplus ones, so that no SM is left with two whole tiles while the
      *    others idle (the pieces run first, the whole tiles fill in behind them). */
-    int S = 0, KS = 1;
-    if (dev >= 0 && dev < 64 && g_partial_rows[dev] >= M) {
-        int max_ks = lin->K / SK_SUPER_K;
+    p->S = 0; p->KS = 1;
+    if (scratch_rows >= M) {
+        int max_ks = K / SK_SUPER_K;
         if (max_ks > SK_MAX_SPLIT) max_ks = SK_MAX_SPLIT;
-        if (tiles * 2 <= g_sk_target_ctas) {
-            S = tiles;
-            KS = g_sk_target_ctas / tiles < max_ks ? g_sk_target_ctas / tiles : max_ks;
-        } else if (tiles > 148 && tiles < 2 * 148) {
-            S = tiles - 148;
-            KS = max_ks;
+        if (p->tiles * 2 <= g_sk_target_ctas) {
+            p->S = p->tiles;
+            p->KS = g_sk_target_ctas / p->tiles < max_ks ? g_sk_target_ctas / p->tiles : max_ks;
+        } else if (p->tiles > 148 && p->tiles < 2 * 148) {
+            p->S = p->tiles - 148;
+            p->KS = max_ks;
         }
-        const size_t cap = (size_t)SK_SCRATCH_FLOATS_PER_ROW * g_partial_rows[dev];
-        while (KS > 1 && (size_t)S * KS * M * SK_BM > cap) KS--;
-        if (KS <= 1 || S > SK_MAX_SPLIT_TILES) { S = 0; KS = 1; }
+        const size_t cap = (size_t)SK_SCRATCH_FLOATS_PER_ROW * scratch_rows;
+        while (p->KS > 1 && (size_t)p->S * p->KS * M * SK_BM > cap) p->KS--;
+        if (p->KS <= 1 || p->S > SK_MAX_SPLIT_TILES) { p->S = 0; p->KS = 1; }
     }
-    float* partial = S ? g_partial[dev] : nullptr;
-    unsigned* arrivals = S ? g_arrivals[dev] : nullptr;
-    int d = 0, dw = 0;
-    if (lin->K % 128 == 0) {
-        if (g_sk_shape == 1 && sk_depths<WK, 512, 128>(1 << lgNB, SK_SMEM_ONE, 3, &d, &dw))
-            return sk_launch_nt<WK, 512, 128>(lin, x, M, lgNB, tiles, S, KS, y, resid, partial, arrivals, st);
-        if (g_sk_shape == 2 && sk_depths<WK, 256, 128>(1 << lgNB, SK_SMEM_ONE, 3, &d, &dw))
-            return sk_launch_nt<WK, 256, 128>(lin, x, M, lgNB, tiles, S, KS, y, resid, partial, arrivals, st);
+    p->grid = p->tiles - p->S + p->S * p->KS;
+    if (K % 128 == 0) {
+        if (g_sk_shape == 1 && sk_plan_shape<WK, 512, 128>(p)) return true;
+        if (g_sk_shape == 2 && sk_plan_shape<WK, 256, 128>(p)) return true;
     }
-    return sk_launch_nt<WK, 256, 64>(lin, x, M, lgNB, tiles, S, KS, y, resid, partial, arrivals, st);
+    return sk_plan_shape<WK, 256, 64>(p);
+}
+
+template <int WK, int NT, int KCP>
+static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, const SkPlan& p, void* y, const void* resid, float* partial,
+                                unsigned* arrivals, cudaStream_t st) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)p.grid), NT + 32, (size_t)p.smem, st>>>(
+        lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, p.lgNB, p.D, p.DW, p.S, p.KS, (__nv_bfloat16*)y,
+        (const __nv_bfloat16*)resid, partial, arrivals);
+    return cudaGetLastError();
+}
+
+template <int WK>
+static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const bool have = dev >= 0 && dev < 64;
+    SkPlan p;
+    if (!sk_plan<WK>(lin->N, lin->K, M, have ? g_partial_rows[dev] : 0, &p)) return cudaErrorInvalidValue;
+    float* partial = p.S ? g_partial[dev] : nullptr;
+    unsigned* arrivals = p.S ? g_arrivals[dev] : nullptr;
+    if (p.nt == 512) return sk_launch_nt<WK, 512, 128>(lin, x, M, p, y, resid, partial, arrivals, st);
+    if (p.kc == 128) return sk_launch_nt<WK, 256, 128>(lin, x, M, p, y, resid, partial, arrivals, st);
+    return sk_launch_nt<WK, 256, 64>(lin, x, M, p, y, resid, partial, arrivals, st);
+}
+
+/* the plan for a shape as 10 ints (SkPlan's fields in order); 0 when the shape cannot be served (tests) */
+extern "C" int skinny_plan_probe(int kind, int N, int K, int M, int scratch_rows, int out[10]) {
+    SkPlan p = {};
+    bool ok = false;
+    switch (kind) {
+    case WK_INT8_CH: ok = sk_plan<WK_INT8_CH>(N, K, M, scratch_rows, &p); break;
+    case WK_INT8_GRP: ok = sk_plan<WK_INT8_GRP>(N, K, M, scratch_rows, &p); break;
+    case WK_INT4_PACK: ok = sk_plan<WK_INT4_PACK>(N, K, M, scratch_rows, &p); break;
+    }
+    const int v[10] = {p.lgNB, p.tiles, p.S, p.KS, p.nt, p.kc, p.D, p.DW, p.grid, p.smem};
+    for (int i = 0; i < 10; i++) out[i] = v[i];
+    return ok ? 1 : 0;
 }
 
 /* y[M, N] (bf16) = x[M, K] (bf16) · W^T for 1 <= M <= 256, plus `resid` [M, N] when given (it may be y
