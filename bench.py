@@ -402,7 +402,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return None
     ref_path = os.path.join(ROOT, "oracle", "_ref", "libs2pref.so" if args.layers == 36 else "libs2pref_l2.so")
-    base = {"impl": "reference", "metric": "decode ms/frame (B=1)", "unit": "ms/frame", "n_gpus": world, "steps": args.steps,
+    base = {"impl": "reference", "metric": f"decode ms/frame (B={args.batch})", "unit": "ms/frame", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": args.mode,
             "data": "synthetic (seeded random-init checkpoint, uniform random prompt)"}
     try:
