@@ -154,12 +154,12 @@ __global__ void __launch_bounds__(256) k_gemv_batch(__nv_bfloat16* __restrict__ 
             if (i + 1 < T)
                 nxt = *reinterpret_cast<const tile_t*>(wrow + (size_t)(i + 1) * 32 * sizeof(tile_t) +
                                                        (size_t)lane * sizeof(tile_t));
-            float w16[16];
-            widen16<WK>(cur, w16);
             const int k0 = i * 512 + lane * 16;
             float gs = 1.f;
             if (WK != WK_INT8_CH)
                 gs = __half2float(static_cast<const __half*>(scales)[(size_t)n * (K >> gshift) + (k0 >> gshift)]);
+            float w16[16];
+            widen16<WK>(cur, w16);
 #pragma unroll
             for (int m = 0; m < MM; m++) {
                 if (m < M) {
@@ -186,11 +186,123 @@ __global__ void __launch_bounds__(256) k_gemv_batch(__nv_bfloat16* __restrict__ 
     }
 }
 
+/* The same for packed INT4, R weight rows per warp: the 16 codes of each row's tile become bf16 once
+ * (exact), an activation row's 16 values are loaded once for the R rows, and every (row, activation row)
+ * pair runs its own chain of mixed-precision fmas (bf16 x bf16 exact, f32 accumulate: bit for bit
+ * fmaf((float)w, (float)x, s)).  Loading the activations once per R rows is what matters: a lockstep
+ * batch reads M x 32 bytes per lane and tile, which otherwise bounds the kernel by L1 bandwidth. */
+template <int MM, int R>
+__global__ void __launch_bounds__(256) k_gemv_batch_i4(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x,
+                                                       const unsigned char* __restrict__ w, const __half* __restrict__ scales,
+                                                       int M, int N, int K, int gshift) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const size_t row_bytes = (size_t)(K >> 1);
+    const int T = K >> 9, spr = K >> gshift;
+    for (int n0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * R; n0 < N; n0 += warps * R) {
+        const unsigned char* wrow[R];
+        const __half* srow[R];
+#pragma unroll
+        for (int r = 0; r < R; r++) { /* rows beyond N repeat row N - 1 and are not stored */
+            const int n = min(n0 + r, N - 1);
+            wrow[r] = w + (size_t)n * row_bytes + (size_t)lane * sizeof(uint2);
+            srow[r] = scales + (size_t)n * spr;
+        }
+        float acc[R][MM];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int m = 0; m < MM; m++) acc[r][m] = 0.f;
+        /* each row's next PD tiles are in registers: with few warps per SM the loads of one tile ahead
+         * would leave the weight stream bound by DRAM latency */
+        constexpr int PD = 4;
+        uint2 pf[R][PD];
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int d = 0; d < PD; d++)
+                pf[r][d] = d < T ? *reinterpret_cast<const uint2*>(wrow[r] + (size_t)d * 32 * sizeof(uint2)) : make_uint2(0, 0);
+        for (int i0 = 0; i0 < T; i0 += PD) {
+#pragma unroll
+          for (int d = 0; d < PD; d++) {
+            const int i = i0 + d;
+            if (i >= T) break;
+            const int k0 = i * 512 + lane * 16;
+            unsigned short wl[R][16];
+            float gs[R];
+#pragma unroll
+            for (int r = 0; r < R; r++) {
+                const uint2 cur = pf[r][d];
+                if (i + PD < T) pf[r][d] = *reinterpret_cast<const uint2*>(wrow[r] + (size_t)(i + PD) * 32 * sizeof(uint2));
+                gs[r] = __half2float(srow[r][k0 >> gshift]);
+                const uint32_t tw[2] = {cur.x, cur.y};
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t a = tw[h] ^ 0x88888888u; /* two's complement nibble -> code + 8 */
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        uint32_t mg = ((a >> (4 * k)) & 0x000F000Fu) | 0x43004300u; /* bf16x2 (128 + n_k, 128 + n_{k+4}) */
+                        __nv_bfloat162 hv = *reinterpret_cast<__nv_bfloat162*>(&mg);
+                        const uint32_t c136 = 0x43084308u;
+                        hv = __hsub2(hv, *reinterpret_cast<const __nv_bfloat162*>(&c136));
+                        const uint32_t pr = *reinterpret_cast<uint32_t*>(&hv);
+                        asm("mov.b32 {%0,%1}, %2;" : "=h"(wl[r][h * 8 + k]), "=h"(wl[r][h * 8 + 4 + k]) : "r"(pr));
+                    }
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < MM; m++) {
+                if (m < M) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)m * K + k0);
+                    const uint4 xa = xp[0], xb = xp[1];
+                    const uint32_t xu[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                    unsigned short xh[16];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) asm("mov.b32 {%0,%1}, %2;" : "=h"(xh[2 * j]), "=h"(xh[2 * j + 1]) : "r"(xu[j]));
+#pragma unroll
+                    for (int r = 0; r < R; r++) {
+                        float sm_ = 0.f;
+#pragma unroll
+                        for (int j = 0; j < 16; j++) sm_ = fma_bf16(wl[r][j], xh[j], sm_);
+                        acc[r][m] = __fmaf_rn(sm_, gs[r], acc[r][m]);
+                    }
+                }
+            }
+          }
+        }
+#pragma unroll
+        for (int r = 0; r < R; r++)
+#pragma unroll
+            for (int m = 0; m < MM; m++) {
+                const float a = warp_tree_sum(acc[r][m]);
+                if (lane == 0 && m < M && n0 + r < N) y[(size_t)m * N + n0 + r] = f2bf(a);
+            }
+    }
+}
+
 template <int WK>
 cudaError_t launch_gemv_batch(void* y, const void* x, const void* w, const void* scales, int M, int N, int K,
                               int gshift, cudaStream_t stream) {
-    int grid = (N + 7) / 8;
     const int cap = device_sm_count() * 8;
+    if (WK == WK_INT4_PACK) { /* two or four weight rows per warp, 8 warps per CTA */
+#define S2P_GB4(MM, R)                                                                                     \
+    do {                                                                                                   \
+        int g4 = (N + 8 * R - 1) / (8 * R);                                                                \
+        if (g4 > cap) g4 = cap;                                                                            \
+        k_gemv_batch_i4<MM, R><<<g4, 256, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,          \
+                                                       (const unsigned char*)w, (const __half*)scales, M, N, K, gshift); \
+    } while (0)
+        /* rows per warp: as many as leave about two CTAs per SM (a 2560-row matrix keeps one row per warp) */
+        const int sms = device_sm_count();
+        const int R = (N >= 8 * 4 * 2 * sms && M <= 8) ? 4 : (N >= 8 * 2 * 2 * sms ? 2 : 1);
+        if (M <= 2) { if (R == 4) S2P_GB4(2, 4); else if (R == 2) S2P_GB4(2, 2); else S2P_GB4(2, 1); }
+        else if (M <= 4) { if (R == 4) S2P_GB4(4, 4); else if (R == 2) S2P_GB4(4, 2); else S2P_GB4(4, 1); }
+        else if (M <= 8) { if (R == 4) S2P_GB4(8, 4); else if (R == 2) S2P_GB4(8, 2); else S2P_GB4(8, 1); }
+        else S2P_GB4(16, 2); /* 9..16 rows: the activation reloads weigh more than the smaller grid */
+#undef S2P_GB4
+        return cudaGetLastError();
+    }
+    int grid = (N + 7) / 8;
     if (grid > cap) grid = cap;
 #define S2P_GB(MM)                                                                                      \
     k_gemv_batch<WK, MM><<<grid, 256, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x, w, scales, \

@@ -301,6 +301,26 @@ def _ref_gemv(ref, kind, y, x, w, s, N, K):
 
 
 @pytest.mark.parametrize("kind", [0, 1, 2])
+@pytest.mark.parametrize("M", [2, 3, 5, 8, 11, 16])
+def test_batched_gemv_rows_match_reference(libs, kind, M):
+    """The lockstep GEMV for 2..16 rows (every row its own chain, tiles folded in order) against the
+    reference's batched kernels, bitwise, on a ragged N and the model's longest K."""
+    mine, _, ref = libs
+    N, K = 1031, 9728
+    w, s = _quantised(mine, N, K, kind, seed=21 + kind)
+    x = rnd(M, K, seed=9)
+    y1 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda"); y2 = torch.empty_like(y1)
+    for lib, y in ((mine, y1), (ref, y2)):
+        if kind == 0:
+            assert lib.s2p_int8_gemv(p(y), p(x), p(w), p(s), M, N, K, None) == 0
+        elif kind == 1:
+            assert lib.s2p_intq_gemv(p(y), p(x), p(w), p(s), M, N, K, 32, None) == 0
+        else:
+            assert lib.s2p_int4p_gemv(p(y), p(x), p(w), p(s), M, N, K, 32, None) == 0
+    assert_same(y1, y2, f"batched gemv kind={kind} M={M}")
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2])
 def test_fused_gemv_stages_equal_unfused_reference_ops(libs, kind):
     """norm->GEMV, GEMV->residual, norm->GEMV->SwiGLU and head->arg-max stages against the
     reference's separate kernels chained the way its run_layer chains them."""
