@@ -132,6 +132,11 @@ cudaError_t gemv_setup_all(void); /* once per device, before any stream capture 
 cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st);
 cudaError_t skinny_status(int* out);
 cudaError_t skinny_setup(int max_rows); /* once per device, outside stream capture: scratch for split-K launches */
+/* the launch plan for a shape as 10 ints (padding, tiles, split tiles, pieces, threads, slab, ring depths, grid,
+ * shared memory), 0 if the shape cannot be served; no CUDA call (CPU tests) */
+int skinny_plan_probe(int kind, int N, int K, int M, int scratch_rows, int out[10]);
+/* measurement aid: CTAs the split aims at, kernel shape (0: 256 threads / 64-k slabs, 1: 512 / 128, 2: 256 / 128) */
+void skinny_tune(int target_ctas, int shape);
 
 /* ---- persistent batch-1 decode tick (mega.cu) --------------------------------
  * The whole frame is one cooperative kernel that walks a list of stages; a grid
