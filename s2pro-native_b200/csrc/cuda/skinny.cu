@@ -266,10 +266,13 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         sk_cp_wait(D - 2); /* slab 0 */
 
         const int a_off0 = (cv_q0 * (G::WPU / 8) * SK_BM + cv_row) * 16;
-        int x_rslot = 0, w_rslot = 0, j_in = 0; /* read offsets into the rings; slab index inside the copy round */
+        int x_rslot = 0, w_rslot = 0; /* read offsets into the rings */
         int s = 0;                              /* stage of slab it, and whether it has been used before */
         unsigned done_parity = 1;               /* parity of the completion of done[s] that frees the stage: it / NST - 1 */
-        for (int it = 0; it < nk; it++) {
+        int it = 0;
+        for (int rnd = 0; rnd < nsup && ok; rnd++) {
+#pragma unroll
+          for (int j_in = 0; j_in < G::SPS; j_in++, it++) { /* the slab's place in its copy round is a constant */
             /* the places the next copies fill were read by this thread one round ago */
             if (x_issued < nk) issue_x();
             if (j_in == 0 && w_issued < nsup) issue_w();
@@ -304,16 +307,14 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
                 *reinterpret_cast<uint4*>(B + (tid + u * NT) * 16) = sk_x_unit<WK>(*reinterpret_cast<const uint4*>(xring + x_rslot + (tid + u * NT) * 16));
             x_rslot += x_bytes;
             if (x_rslot == D * x_bytes) x_rslot = 0;
-            if (++j_in == G::SPS) {
-                j_in = 0;
-                w_rslot += G::SUP_BYTES;
-                if (w_rslot == DW * G::SUP_BYTES) w_rslot = 0;
-            }
             fence_proxy_async_smem(); /* these generic-proxy stores are read by the tensor core (async proxy) */
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(full + s)) : "memory");
             if (++s == NST) { s = 0; done_parity ^= 1u; }
             sk_cp_wait(D - 2); /* this thread's share of slab it + 1 */
+          }
+          w_rslot += G::SUP_BYTES;
+          if (w_rslot == DW * G::SUP_BYTES) w_rslot = 0;
         }
         asm volatile("cp.async.wait_all;" ::: "memory"); /* nothing of this thread's is in flight past here */
     } else {
