@@ -1012,6 +1012,16 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
         m->mega_ok = 0; /* its barrier counters and tags are no longer in step */
         return S2P_ERR_INTERNAL;
     }
+    if (!mega && m->n_slow > 0 && m->mode == S2P_GEMM_INT8 && m->slow[0].wqkv.int8_ready &&
+        s2p_linear_rows_on_tc(&m->slow[0].wqkv, nact)) {
+        /* the batched linears ran on the tensor-core kernel: a bounded wait that gave up inside it left a code */
+        int sk = 0;
+        S2P_CUDA_TRY(skinny_status(&sk));
+        if (sk != 0) {
+            fprintf(stderr, "[s2pro] batched tensor-core linear gave up on a bounded wait (code %d); the frame is lost\n", sk);
+            return S2P_ERR_INTERNAL;
+        }
+    }
     m->last_rows = nact; m->last_fused = fused; m->last_graph = steady; m->last_kernels = m->tick_kernels;
     m->last_mega = mega;
     if (cudaEventElapsedTime(&m->last_device_ms, m->ev0, m->ev1) != cudaSuccess) m->last_device_ms = 0.f;
