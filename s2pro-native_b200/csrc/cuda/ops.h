@@ -130,6 +130,8 @@ cudaError_t gemv_setup_all(void); /* once per device, before any stream capture 
 
 /* batched decode linear on the tensor cores (skinny.cu): y[M, N] = x[M, K] · W^T, 1 <= M <= 256 */
 cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st);
+/* h[M, N / 2] = silu(x · Wg^T) * (x · Wu^T) for W = [Wg | Wu] stacked along N (gate/up linear + SwiGLU in one launch) */
+cudaError_t skinny_gemm_tc_swiglu(const LinRef* lin, const void* x, int M, void* h, cudaStream_t st);
 cudaError_t skinny_status(int* out);
 cudaError_t skinny_setup(int max_rows); /* once per device, outside stream capture: scratch for split-K launches */
 /* the launch plan for a shape as 10 ints (padding, tiles, split tiles, pieces, threads, slab, ring depths, grid,

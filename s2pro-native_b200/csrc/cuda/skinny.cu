@@ -145,13 +145,41 @@ template <int WK> __device__ __forceinline__ uint4 sk_x_unit(const uint4& v) {
                       *reinterpret_cast<uint32_t*>(&h[3]));
 }
 
+/* weight row behind row r of tile t: plain tiles are 128 consecutive rows; SwiGLU tiles (ffn > 0: the matrix is
+ * [gate rows | up rows], ffn of each) pair 64 gate rows with their 64 up rows.  Rows beyond the matrix repeat its
+ * last row: their outputs are never stored. */
+__device__ __forceinline__ int sk_row(int t, int r, int ffn) {
+    if (!ffn) return t * SK_BM + r;
+    const int gi = min(t * 64 + (r & 63), ffn - 1);
+    return r < 64 ? gi : ffn + gi;
+}
+/* silu(g) * u with the rounding steps of the unfused kernels (g, u: bf16 values held in f32) */
+__device__ __forceinline__ __nv_bfloat16 sk_swiglu(float g, float u) {
+    const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+    return f2bf(__fmul_rn(bf16_round(__fmul_rn(g, sig)), u));
+}
+/* 32 accumulator columns of this warp's 32 TMEM lanes */
+__device__ __forceinline__ void sk_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 template <int WK, int NT, int KCP>
 __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
                                                           int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
-                                                          int lgNB, int D, int DW, int n_split_tiles, int KS,
+                                                          int lgNB, int D, int DW, int n_split_tiles, int KS, int ffn,
                                                           __nv_bfloat16* y, const __nv_bfloat16* resid,
                                                           float* __restrict__ partial, unsigned* __restrict__ arrivals) {
     /* resid (may alias y): y = bf16(f32(resid) + f32(bf16(product))), the residual add of the decode layers */
+    /* ffn > 0: W is a [gate | up] pair of ffn rows each and y[M, ffn] = silu(x Wg^T) * (x Wu^T) (see sk_row) */
     /* The last n_split_tiles row tiles have their K range split over KS CTAs each; those CTAs come first
      * in the grid (short pieces first, whole tiles after them: the tail of the grid stays balanced).  Each
      * piece leaves its f32 partial in `partial`[split tile][piece][batch row][128] and the last piece of a
@@ -180,7 +208,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + NST);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool mma_warp = warp == NT / 32;
-    const int n_tiles = (N + SK_BM - 1) / SK_BM, n_pieces = n_split_tiles * KS;
+    const int n_tiles = ffn ? (ffn + 63) / 64 : (N + SK_BM - 1) / SK_BM, n_pieces = n_split_tiles * KS;
     const bool piece = (int)blockIdx.x < n_pieces;
     const int stile = piece ? (int)blockIdx.x / KS : 0;                     /* index among the split tiles */
     const int ks = piece ? (int)blockIdx.x % KS : 0, ksn = piece ? KS : 1;  /* this CTA's piece of how many */
@@ -216,7 +244,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         /* ---- this thread's row and units: unit q0 + i NT / 128 of every slab (i < NLD); rows beyond N (last
          * tile) repeat row N - 1: their outputs are never stored */
         const int cv_row = tid & (SK_BM - 1), cv_q0 = tid >> 7;
-        const int grow_c = min(n0 + cv_row, N - 1);
+        const int grow_c = min(sk_row(tile, cv_row, ffn), N - 1);
         const unsigned char* wsrc = static_cast<const unsigned char*>(w) + (size_t)grow_c * row_bytes + (size_t)sup_first * G::PITCHS;
         const int sc_round = SK_SUPER_K >> gshift; /* scales per row and round */
         const __half* sc_src = nullptr;
@@ -353,24 +381,18 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
     /* the last commit covers every MMA before it */
     if (ok) ok = mbar_wait_bounded(done + ((nk - 1) % NST), (unsigned)((nk - 1) / NST) & 1u, status);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok && !mma_warp) { /* warp w reads TMEM lanes 32 (w % 4) .. + 31 = weight rows; the warps of a lane quarter share the columns */
-        const int grow = n0 + (warp & 3) * 32 + lane;
-        float rs = 1.f;
-        if (WK == WK_INT8_CH && grow < N) rs = static_cast<const float*>(scales)[grow];
+    const bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0; /* one verdict for the CTA: the epilogue has barriers */
+    /* warp w reads TMEM lanes 32 (w % 4) .. + 31 = the tile's rows; the warps of a lane quarter share the columns */
+    const int lrow = (warp & 3) * 32 + lane;
+    const int grow = sk_row(tile, lrow, ffn);
+    const bool row_live = ffn ? (tile * 64 + (lrow & 63)) < ffn : grow < N;
+    float rs = 1.f;
+    if (WK == WK_INT8_CH && row_live) rs = static_cast<const float*>(scales)[grow];
+    if (all_ok && !mma_warp && (piece || !ffn)) {
         for (int col0 = (warp >> 2) * 32; col0 < NB; col0 += (NT / 128) * 32) {
             uint32_t v[32];
-            const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                  "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                  "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                  "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                : "r"(taddr)
-                : "memory");
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (grow < N) {
+            sk_tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0, v);
+            if (row_live) {
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     const int m = col0 + j;
@@ -380,7 +402,36 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
                             if (resid) o = f2bf(__fadd_rn(bf2f(resid[(size_t)m * N + grow]), bf2f(o)));
                             y[(size_t)m * N + grow] = o;
                         }
-                        else partial[(((size_t)stile * KS + ks) * M + m) * SK_BM + (grow - n0)] = __uint_as_float(v[j]);
+                        else partial[(((size_t)stile * KS + ks) * M + m) * SK_BM + lrow] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+    if (all_ok && ffn && !piece) {
+        /* SwiGLU: lanes 0..63 hold gate rows, lanes 64..127 the matching up rows; the up halves cross to the gate
+         * warps through shared memory (the stages are free: every MMA has completed).  Arithmetic of the unfused
+         * pair: both products rounded to bf16, sigmoid and silu in f32, silu rounded to bf16, times up, bf16. */
+        float* ex = reinterpret_cast<float*>(smem); /* [64 rows][NB + 1] */
+        if (!mma_warp && (warp & 3) >= 2) {
+            for (int col0 = (warp >> 2) * 32; col0 < NB; col0 += (NT / 128) * 32) {
+                uint32_t v[32];
+                sk_tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0, v);
+#pragma unroll
+                for (int j = 0; j < 32; j++) ex[(lrow - 64) * (NB + 1) + col0 + j] = bf16_round(__fmul_rn(__uint_as_float(v[j]), rs));
+            }
+        }
+        __syncthreads();
+        if (!mma_warp && (warp & 3) < 2) {
+            const int gi = tile * 64 + lrow;
+            for (int col0 = (warp >> 2) * 32; col0 < NB; col0 += (NT / 128) * 32) {
+                uint32_t v[32];
+                sk_tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0, v);
+                if (row_live) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int m = col0 + j;
+                        if (m < M) y[(size_t)m * ffn + gi] = sk_swiglu(bf16_round(__fmul_rn(__uint_as_float(v[j]), rs)), ex[lrow * (NB + 1) + m]);
                     }
                 }
             }
@@ -390,37 +441,60 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         __shared__ int s_last;
         __threadfence();
         __syncthreads();
-        if (tid == 0) s_last = ok && (atomicAdd(arrivals + stile, 1u) == (unsigned)(KS - 1));
+        if (tid == 0) s_last = all_ok && (atomicAdd(arrivals + stile, 1u) == (unsigned)(KS - 1));
         __syncthreads();
-        if (s_last && !mma_warp) {
+        if (s_last && !mma_warp && !ffn) {
             __threadfence();
             /* four outputs per thread and round, the loads of all splits in flight together; the adds keep split order */
             for (int e0 = tid; e0 < SK_BM * M; e0 += NT * 4) {
                 float v[4][SK_MAX_SPLIT];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    const int e = e0 + u * NT, m = e >> 7, grow = n0 + (e & (SK_BM - 1));
-                    const bool live = e < SK_BM * M && grow < N;
+                    const int e = e0 + u * NT, m = e >> 7, er = n0 + (e & (SK_BM - 1));
+                    const bool live = e < SK_BM * M && er < N;
 #pragma unroll
                     for (int q = 0; q < SK_MAX_SPLIT; q++)
                         v[u][q] = (live && q < KS) ? __ldcg(partial + (((size_t)stile * KS + q) * M + m) * SK_BM + (e & (SK_BM - 1))) : 0.f;
                 }
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    const int e = e0 + u * NT, m = e >> 7, grow = n0 + (e & (SK_BM - 1));
-                    if (e >= SK_BM * M || grow >= N) continue;
+                    const int e = e0 + u * NT, m = e >> 7, er = n0 + (e & (SK_BM - 1));
+                    if (e >= SK_BM * M || er >= N) continue;
                     float acc = 0.f;
 #pragma unroll
                     for (int q = 0; q < SK_MAX_SPLIT; q++)
                         if (q < KS) acc += v[u][q];
-                    if (WK == WK_INT8_CH) acc = __fmul_rn(acc, static_cast<const float*>(scales)[grow]);
+                    if (WK == WK_INT8_CH) acc = __fmul_rn(acc, static_cast<const float*>(scales)[er]);
                     __nv_bfloat16 o = f2bf(acc);
-                    if (resid) o = f2bf(__fadd_rn(bf2f(resid[(size_t)m * N + grow]), bf2f(o)));
-                    y[(size_t)m * N + grow] = o;
+                    if (resid) o = f2bf(__fadd_rn(bf2f(resid[(size_t)m * N + er]), bf2f(o)));
+                    y[(size_t)m * N + er] = o;
                 }
             }
-            if (tid == 0) arrivals[stile] = 0u;
         }
+        if (s_last && !mma_warp && ffn) {
+            __threadfence();
+            for (int e = tid; e < 64 * M; e += NT) { /* (batch row, gate row) pairs of the tile */
+                const int m = e >> 6, r = e & 63, gi = tile * 64 + r;
+                if (gi >= ffn) continue;
+                float vg[SK_MAX_SPLIT], vu[SK_MAX_SPLIT];
+#pragma unroll
+                for (int q = 0; q < SK_MAX_SPLIT; q++) {
+                    const float* pp = partial + (((size_t)stile * KS + (q < KS ? q : 0)) * M + m) * SK_BM;
+                    vg[q] = q < KS ? __ldcg(pp + r) : 0.f;
+                    vu[q] = q < KS ? __ldcg(pp + 64 + r) : 0.f;
+                }
+                float ag = 0.f, au = 0.f;
+#pragma unroll
+                for (int q = 0; q < SK_MAX_SPLIT; q++)
+                    if (q < KS) { ag += vg[q]; au += vu[q]; }
+                if (WK == WK_INT8_CH) {
+                    ag = __fmul_rn(ag, static_cast<const float*>(scales)[gi]);
+                    au = __fmul_rn(au, static_cast<const float*>(scales)[ffn + gi]);
+                }
+                y[(size_t)m * ffn + gi] = sk_swiglu(bf16_round(ag), bf16_round(au));
+            }
+        }
+        if (s_last && tid == 0) arrivals[stile] = 0u;
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -505,10 +579,10 @@ template <int WK, int NT, int KCP> static bool sk_plan_shape(SkPlan* p) {
 }
 
 /* scratch_rows: batch rows the split-K scratch of the device was set up for (0: none) */
-template <int WK> static bool sk_plan(int N, int K, int M, int scratch_rows, SkPlan* p) {
+template <int WK> static bool sk_plan(int N, int K, int M, int scratch_rows, int ffn, SkPlan* p) {
     p->lgNB = 4; /* the batch is padded to a power of two: the MMA's N */
     while ((1 << p->lgNB) < M) p->lgNB++;
-    p->tiles = (N + SK_BM - 1) / SK_BM;
+    p->tiles = ffn ? (ffn + 63) / 64 : (N + SK_BM - 1) / SK_BM; /* SwiGLU tiles: 64 gate rows + their 64 up rows */
     /* S of the row tiles have their K range split into KS pieces:
      *  - few tiles: all of them, until the grid fills the GPU;
      *  - a few more tiles than SMs: the surplus ones, so that no SM is left with two whole tiles while the
@@ -537,8 +611,8 @@ template <int WK> static bool sk_plan(int N, int K, int M, int scratch_rows, SkP
 }
 
 template <int WK, int NT, int KCP>
-static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, const SkPlan& p, void* y, const void* resid, float* partial,
-                                unsigned* arrivals, cudaStream_t st) {
+static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, const SkPlan& p, int ffn, void* y, const void* resid,
+                                float* partial, unsigned* arrivals, cudaStream_t st) {
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
@@ -546,24 +620,24 @@ static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, const S
         attr_set = true;
     }
     k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)p.grid), NT + 32, (size_t)p.smem, st>>>(
-        lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, p.lgNB, p.D, p.DW, p.S, p.KS, (__nv_bfloat16*)y,
+        lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, p.lgNB, p.D, p.DW, p.S, p.KS, ffn, (__nv_bfloat16*)y,
         (const __nv_bfloat16*)resid, partial, arrivals);
     return cudaGetLastError();
 }
 
 template <int WK>
-static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
+static cudaError_t sk_launch(const LinRef* lin, const void* x, int M, int ffn, void* y, const void* resid, cudaStream_t st) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     const bool have = dev >= 0 && dev < 64;
     SkPlan p;
-    if (!sk_plan<WK>(lin->N, lin->K, M, have ? g_partial_rows[dev] : 0, &p)) return cudaErrorInvalidValue;
+    if (!sk_plan<WK>(lin->N, lin->K, M, have ? g_partial_rows[dev] : 0, ffn, &p)) return cudaErrorInvalidValue;
     float* partial = p.S ? g_partial[dev] : nullptr;
     unsigned* arrivals = p.S ? g_arrivals[dev] : nullptr;
-    if (p.nt == 512) return sk_launch_nt<WK, 512, 128>(lin, x, M, p, y, resid, partial, arrivals, st);
-    if (p.kc == 128) return sk_launch_nt<WK, 256, 128>(lin, x, M, p, y, resid, partial, arrivals, st);
-    return sk_launch_nt<WK, 256, 64>(lin, x, M, p, y, resid, partial, arrivals, st);
+    if (p.nt == 512) return sk_launch_nt<WK, 512, 128>(lin, x, M, p, ffn, y, resid, partial, arrivals, st);
+    if (p.kc == 128) return sk_launch_nt<WK, 256, 128>(lin, x, M, p, ffn, y, resid, partial, arrivals, st);
+    return sk_launch_nt<WK, 256, 64>(lin, x, M, p, ffn, y, resid, partial, arrivals, st);
 }
 
 /* the plan for a shape as 10 ints (SkPlan's fields in order); 0 when the shape cannot be served (tests) */
@@ -571,9 +645,9 @@ extern "C" int skinny_plan_probe(int kind, int N, int K, int M, int scratch_rows
     SkPlan p = {};
     bool ok = false;
     switch (kind) {
-    case WK_INT8_CH: ok = sk_plan<WK_INT8_CH>(N, K, M, scratch_rows, &p); break;
-    case WK_INT8_GRP: ok = sk_plan<WK_INT8_GRP>(N, K, M, scratch_rows, &p); break;
-    case WK_INT4_PACK: ok = sk_plan<WK_INT4_PACK>(N, K, M, scratch_rows, &p); break;
+    case WK_INT8_CH: ok = sk_plan<WK_INT8_CH>(N, K, M, scratch_rows, 0, &p); break;
+    case WK_INT8_GRP: ok = sk_plan<WK_INT8_GRP>(N, K, M, scratch_rows, 0, &p); break;
+    case WK_INT4_PACK: ok = sk_plan<WK_INT4_PACK>(N, K, M, scratch_rows, 0, &p); break;
     }
     const int v[10] = {p.lgNB, p.tiles, p.S, p.KS, p.nt, p.kc, p.D, p.DW, p.grid, p.smem};
     for (int i = 0; i < 10; i++) out[i] = v[i];
@@ -583,27 +657,40 @@ extern "C" int skinny_plan_probe(int kind, int N, int K, int M, int scratch_rows
 /* y[M, N] (bf16) = x[M, K] (bf16) · W^T for 1 <= M <= 256, plus `resid` [M, N] when given (it may be y
  * itself).  K must be a multiple of 256, the group size of grouped kinds a power of two from 32 (INT4) / 16 (INT8
  * codes) to 128. */
-extern "C" cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
+static cudaError_t sk_entry(const LinRef* lin, const void* x, int M, int ffn, void* y, const void* resid, cudaStream_t st) {
     if (!lin || !x || !y || M < 1 || M > 256 || lin->K % SK_SUPER_K) return cudaErrorInvalidValue;
     if (((uintptr_t)x | (uintptr_t)lin->w) & 15) return cudaErrorInvalidValue;
-    if (lin->kind != WK_INT8_CH) /* a round's scales (256 / group of them) are copied as 4 to 32 aligned bytes */
+    if (lin->kind != WK_INT8_CH) /* a round's scales (256 / group of them) are copied in aligned 4-byte pairs */
         if (lin->gshift < 4 || lin->gshift > 7 || ((uintptr_t)lin->scales & 15)) return cudaErrorInvalidValue;
     if (lin->kind == WK_INT4_PACK && lin->gshift < 5) return cudaErrorInvalidValue;
+    if (ffn && (lin->N != 2 * ffn || resid)) return cudaErrorInvalidValue;
+    const int out_cols = ffn ? ffn : lin->N;
     /* the MMA's N is the batch padded to a power of two, at most 128: a larger batch takes two launches */
     for (int m0 = 0; m0 < M; m0 += 128) {
         const int mm = M - m0 < 128 ? M - m0 : 128;
         const void* xs = static_cast<const char*>(x) + (size_t)m0 * lin->K * 2;
-        void* ys = static_cast<char*>(y) + (size_t)m0 * lin->N * 2;
+        void* ys = static_cast<char*>(y) + (size_t)m0 * out_cols * 2;
         const void* rs = resid ? static_cast<const char*>(resid) + (size_t)m0 * lin->N * 2 : nullptr;
         cudaError_t e = cudaErrorInvalidValue;
         switch (lin->kind) {
-        case WK_INT8_CH: e = sk_launch<WK_INT8_CH>(lin, xs, mm, ys, rs, st); break;
-        case WK_INT8_GRP: e = sk_launch<WK_INT8_GRP>(lin, xs, mm, ys, rs, st); break;
-        case WK_INT4_PACK: e = sk_launch<WK_INT4_PACK>(lin, xs, mm, ys, rs, st); break;
+        case WK_INT8_CH: e = sk_launch<WK_INT8_CH>(lin, xs, mm, ffn, ys, rs, st); break;
+        case WK_INT8_GRP: e = sk_launch<WK_INT8_GRP>(lin, xs, mm, ffn, ys, rs, st); break;
+        case WK_INT4_PACK: e = sk_launch<WK_INT4_PACK>(lin, xs, mm, ffn, ys, rs, st); break;
         }
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
+}
+
+extern "C" cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st) {
+    return sk_entry(lin, x, M, 0, y, resid, st);
+}
+
+/* h[M, N / 2] (bf16) = silu(x · Wg^T) * (x · Wu^T) for W = [Wg | Wu] stacked along its N rows: the gate/up linear
+ * of a decode layer with the SwiGLU kernel's arithmetic in the epilogue */
+extern "C" cudaError_t skinny_gemm_tc_swiglu(const LinRef* lin, const void* x, int M, void* h, cudaStream_t st) {
+    if (!lin || (lin->N & 1)) return cudaErrorInvalidValue;
+    return sk_entry(lin, x, M, lin->N / 2, h, nullptr, st);
 }
 
 /* status word of the launches so far on the current device (0 = no wait ever gave up); synchronises */

@@ -251,6 +251,20 @@ s2p_status s2p_linear_tc_add(const s2p_linear* lin, const void* x_bf16, void* y_
     return S2P_OK;
 }
 
+/* h = silu(x · Wgᵀ) * (x · Wuᵀ) for a stacked [gate | up] linear in one launch; only where
+ * s2p_linear_rows_on_tc says so */
+s2p_status s2p_linear_tc_swiglu(const s2p_linear* lin, const void* x_bf16, void* h_bf16, int M, cudaStream_t stream) {
+    LinRef lr;
+    s2p_lin_ref(lin, &lr);
+    const cudaError_t ce = skinny_gemm_tc_swiglu(&lr, x_bf16, M, h_bf16, stream);
+    if (ce != cudaSuccess) {
+        fprintf(stderr, "[s2pro] batched tensor-core linear + SwiGLU (M=%d,N=%d,K=%d): %s\n", M, lin->out_features,
+                lin->in_features, cudaGetErrorString(ce));
+        return S2P_ERR_CUDA;
+    }
+    return S2P_OK;
+}
+
 s2p_status s2p_linear_gemv_rows(const s2p_linear* lin, const void* x_bf16, void* y_bf16, int M, cudaStream_t stream) {
     const int N = lin->out_features, K = lin->in_features;
     /* beyond the reference's 16-row GEMV the batch goes to the tensor cores in one launch

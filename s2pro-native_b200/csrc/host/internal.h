@@ -15,6 +15,7 @@ int s2p_env_is_one(const char* name);
 s2p_status s2p_linear_gemv_rows(const s2p_linear* lin, const void* x_bf16, void* y_bf16, int M, cudaStream_t stream);
 int s2p_linear_rows_on_tc(const s2p_linear* lin, int M);
 s2p_status s2p_linear_tc_add(const s2p_linear* lin, const void* x_bf16, void* y_inout_bf16, int M, cudaStream_t stream);
+s2p_status s2p_linear_tc_swiglu(const s2p_linear* lin, const void* x_bf16, void* h_bf16, int M, cudaStream_t stream);
 
 typedef struct {
     s2p_linear wqkv, wo, gate_up, w2;

@@ -199,8 +199,14 @@ static s2p_status layer_general(s2p_model* m, const s2p_layer* L, const layer_ct
     }
     S2P_TRY(lin_add(m, &L->wo, attn, x, proj, rows, c->decode));
     S2P_LAUNCH(m, rms_norm(x, L->ffn_norm.data, norm, rows, S2P_DIM, S2P_NORM_EPS, st));
-    S2P_TRY(lin_apply(m, &L->gate_up, norm, gu, rows, c->decode));
-    S2P_LAUNCH(m, silu_mul(gu, hff, rows, S2P_FFN_DIM, st));
+    if (c->decode && m->mode == S2P_GEMM_INT8 && L->gate_up.int8_ready && s2p_linear_rows_on_tc(&L->gate_up, rows) &&
+        L->gate_up.out_features == 2 * S2P_FFN_DIM) {
+        m->tick_kernels += 1; /* gate/up linear and SwiGLU in one launch */
+        S2P_TRY(s2p_linear_tc_swiglu(&L->gate_up, norm, hff, rows, st));
+    } else {
+        S2P_TRY(lin_apply(m, &L->gate_up, norm, gu, rows, c->decode));
+        S2P_LAUNCH(m, silu_mul(gu, hff, rows, S2P_FFN_DIM, st));
+    }
     S2P_TRY(lin_add(m, &L->w2, hff, x, proj, rows, c->decode));
     return S2P_OK;
 }

@@ -72,3 +72,49 @@ def test_tensor_core_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
         want = (r.float() + y_tc.float()).to(torch.bfloat16)
         assert torch.equal(y3.view(torch.int16), want.view(torch.int16))
         a0 = a
+
+
+@pytest.mark.parametrize("kind", [2, 0, 1])
+@pytest.mark.parametrize("M,ffn,K", [(32, 6400, 512), (17, 4810, 512), (200, 6400, 512), (32, 9728, 2560), (17, 200, 512)])
+def test_fused_swiglu_equals_linear_then_swiglu(mine, testlib, kind, M, ffn, K):
+    """The gate/up linear with SwiGLU in its epilogue against the same linear followed by the SwiGLU kernel.
+    76..148 row tiles (no tile is split over K in either launch, both accumulate every row in one pass): the same
+    bits, also with a ragged last tile and more than 128 rows.  Shapes whose tiles are split (the two launches
+    split different rows, so f32 partial sums are added in different orders): a rounding step of difference."""
+    dev()
+    N = 2 * ffn
+    testlib.skinny_gemm_tc.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    testlib.skinny_gemm_tc_swiglu.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    testlib.silu_mul.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    testlib.skinny_status.argtypes = [C.POINTER(C.c_int)]
+    testlib.skinny_setup.argtypes = [C.c_int]
+    assert testlib.skinny_setup(256) == 0
+    w, s = _quantised(mine, N, K, kind, seed=31 + kind)
+    x = rnd(M, K, seed=6)
+    lin = LinRef(kind, w.data_ptr(), s.data_ptr(), N, K, 0 if kind == 0 else 5)
+    gu = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    want = torch.empty(M, ffn, dtype=torch.bfloat16, device="cuda")
+    got = torch.full((M, ffn), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert testlib.skinny_gemm_tc(C.byref(lin), p(x), M, p(gu), None, None) == 0
+    assert testlib.silu_mul(p(gu), p(want), M, ffn, None) == 0
+    assert testlib.skinny_gemm_tc_swiglu(C.byref(lin), p(x), M, p(got), None) == 0
+    torch.cuda.synchronize()
+    st = C.c_int(-1)
+    assert testlib.skinny_status(C.byref(st)) == 0 and st.value == 0, "a bounded wait inside the kernel gave up"
+    assert torch.isfinite(got.float()).all()
+    tiles = (ffn + 63) // 64
+    if 75 <= tiles <= 148:
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    else:
+        a, b = got.float(), want.float()
+        diff = (a - b).abs()
+        scale = float(b.abs().max())
+        mag = torch.maximum(a.abs(), b.abs()).clamp_min(2.0 ** -20)
+        step = torch.exp2(torch.floor(torch.log2(mag)) - 7)  # one bf16 step at that magnitude
+        assert bool((diff <= 2 * step + 2e-3 * scale).all()), f"max diff {float(diff.max())} at scale {scale}"
+        assert float((diff == 0).float().mean()) >= 0.9
+        # the fused launch is reproducible run to run
+        got2 = torch.empty_like(got)
+        assert testlib.skinny_gemm_tc_swiglu(C.byref(lin), p(x), M, p(got2), None) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got2.view(torch.int16), got.view(torch.int16))
