@@ -62,6 +62,8 @@ def load():
     lib.s2po_next_frame.argtypes = [_P, _P, _P, _P]
     lib.s2po_fast_frame.argtypes = [_P, _P, _I, _P, _P]
     lib.s2po_layer_gemv_sample.argtypes = [_P, _P, _P, _P, _P, _I, _I]
+    lib.s2po_set_threads.restype = _I; lib.s2po_set_threads.argtypes = [_I]
+    lib.s2po_model_fill_synthetic.argtypes = [_P, C.c_uint64]
     return lib
 
 

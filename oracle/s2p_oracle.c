@@ -1272,6 +1272,92 @@ S2PO_API void s2po_fast_frame(const s2po_model* m, const uint16_t* hidden, int s
 
 /* ------------------------------------------------- CPU baseline sample ---- */
 
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+/* Threads the row loops use from now on (0: leave the OpenMP default); returns the count in
+ * force.  A launcher may have exported OMP_NUM_THREADS=1 for its children; a timing that
+ * reports "cores" sets the number itself. */
+S2PO_API int s2po_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
+static void fill_bytes(uint8_t* p, size_t n, uint64_t seed) {
+#pragma omp parallel for schedule(static)
+    for (int64_t blk = 0; blk < (int64_t)((n + 4095) / 4096); blk++) {
+        uint64_t z = seed + 0x9E3779B97F4A7C15ull * (uint64_t)(blk + 1);
+        const size_t lo = (size_t)blk * 4096, hi = lo + 4096 < n ? lo + 4096 : n;
+        for (size_t i = lo; i < hi; i++) {
+            z = z * 6364136223846793005ull + 1442695040888963407ull;
+            p[i] = (uint8_t)(z >> 56);
+        }
+    }
+}
+static void lin_synthetic(s2po_linear* l, int N, int K, int int4, uint64_t seed) {
+    memset(l, 0, sizeof(*l));
+    l->N = N; l->K = K;
+    if (int4) {
+        l->kind = 3; l->G = 32;
+        l->pack = (uint8_t*)malloc((size_t)N * K / 2);
+        fill_bytes(l->pack, (size_t)N * K / 2, seed);
+        l->scale_f16 = (uint16_t*)malloc((size_t)N * (K / 32) * 2);
+        for (size_t i = 0; i < (size_t)N * (K / 32); i++) l->scale_f16[i] = f2h(0.003f);
+    } else {
+        l->kind = 1;
+        l->q = (int8_t*)malloc((size_t)N * K);
+        fill_bytes((uint8_t*)l->q, (size_t)N * K, seed);
+        l->scale_f32 = (float*)malloc((size_t)N * sizeof(float));
+        for (int i = 0; i < N; i++) l->scale_f32[i] = 1.6e-4f;
+    }
+}
+static uint16_t* ones16(size_t n) {
+    uint16_t* p = (uint16_t*)malloc(n * 2);
+    for (size_t i = 0; i < n; i++) p[i] = 0x3F80; /* bf16 1.0 */
+    return p;
+}
+static uint16_t* small16(size_t n, uint64_t seed) { /* bf16 values of magnitude ~0.02, either sign */
+    uint16_t* p = (uint16_t*)malloc(n * 2);
+    fill_bytes((uint8_t*)p, n * 2, seed);
+    for (size_t i = 0; i < n; i++) p[i] = (uint16_t)((p[i] & 0x807F) | 0x3C80);
+    return p;
+}
+
+/* Timing aid: give a model quantised weights of the right shapes and storage forms without the
+ * load-time quantisers (seeded pseudo-random codes, constant scales, unit gains) - the frame
+ * functions then do exactly the work of a real checkpoint; the values carry no meaning.
+ * Requires quant != 0 and embed_i8_only. */
+S2PO_API void s2po_model_fill_synthetic(s2po_model* m, uint64_t seed) {
+    const int D = m->dim, QW = m->q_heads * HD, KVW = m->kv_heads * HD, F = m->ffn;
+    for (int f = 0; f < 2; f++) {
+        const int n = f ? m->n_fast : m->n_slow, i4 = f ? m->int4_fast : m->int4_backbone;
+        for (int l = 0; l < n; l++) {
+            s2po_layer* L = f ? &m->fast[l] : &m->slow[l];
+            const uint64_t s0 = seed + 1000u * (uint64_t)(f * 64 + l);
+            lin_synthetic(&L->wqkv, QW + 2 * KVW, D, i4, s0 + 1);
+            lin_synthetic(&L->wo, D, QW, i4, s0 + 2);
+            lin_synthetic(&L->gate_up, 2 * F, D, i4, s0 + 3);
+            lin_synthetic(&L->w2, D, F, i4, s0 + 4);
+            L->attn_norm = ones16((size_t)D); L->ffn_norm = ones16((size_t)D);
+            if (!f) { L->q_norm = ones16(HD); L->k_norm = ones16(HD); }
+        }
+    }
+    m->embed_i8 = (int8_t*)malloc((size_t)m->vocab * D);
+    fill_bytes((uint8_t*)m->embed_i8, (size_t)m->vocab * D, seed + 7);
+    m->embed_scale = (float*)malloc((size_t)m->vocab * sizeof(float));
+    for (int i = 0; i < m->vocab; i++) m->embed_scale[i] = 1.6e-4f;
+    m->final_norm = ones16((size_t)D); m->fast_norm = ones16((size_t)D);
+    lin_synthetic(&m->fast_out, m->cb_size, D, m->int4_fast, seed + 8);
+    m->cb_emb = small16((size_t)m->n_cb * m->cb_size * D, seed + 9);
+    m->fast_emb = small16((size_t)m->cb_size * D, seed + 10);
+}
+
+
 /* Weight-streaming work of `reps` backbone-shaped layers at batch 1 (the four
  * GEMVs of one layer: 6144x2560, 2560x4096, 19456x2560, 2560x9728) on packed
  * INT4 (int4 != 0) or per-channel INT8 weights.  Used only to time the CPU port

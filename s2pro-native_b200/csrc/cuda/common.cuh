@@ -71,19 +71,24 @@ __device__ __forceinline__ float block_tree(float v, float* red) {
  * pairs of the levels 128, 64 and 32 itself (lane t holds the values t + 32 j),
  * then the shuffle levels.  Same pairs as block_tree<256, false>, same result.
  * Thread t < 256 contributes v; `red` needs 256 floats and must not be written
- * again before the caller's next barrier.  All threads of the group must call it. */
-__device__ __forceinline__ float tree256_sum(float v, float* red) {
+ * again before the caller's next barrier.  All threads of the group must call it; `sync` is a
+ * barrier over that group (the whole CTA in the two-argument form). */
+template <class SyncFn>
+__device__ __forceinline__ float tree256_sum(float v, float* red, SyncFn sync) {
     const int t = threadIdx.x;
     if (t < 256) red[t] = v;
-    S2P_CTA_SYNC();
+    sync();
     if (t < 32) {
         const float a0 = red[t] + red[t + 128], a1 = red[t + 32] + red[t + 160];
         const float a2 = red[t + 64] + red[t + 192], a3 = red[t + 96] + red[t + 224];
         const float r = warp_tree_sum((a0 + a2) + (a1 + a3));
         if (t == 0) red[256] = r;
     }
-    S2P_CTA_SYNC();
+    sync();
     return red[256];
+}
+__device__ __forceinline__ float tree256_sum(float v, float* red) {
+    return tree256_sum(v, red, [] { S2P_CTA_SYNC(); });
 }
 
 /* Bytes of an int8x4 word (biased by 128) or nibbles of an int4x8 word (biased

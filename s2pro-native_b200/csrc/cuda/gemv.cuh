@@ -185,6 +185,15 @@ __device__ __forceinline__ void xs_store_vec8(unsigned char* xs, int v, const ui
         p[32] = make_float4(bf_lo(q.z), bf_hi(q.z), bf_lo(q.w), bf_hi(q.w));
     }
 }
+/* one element into the staged layout */
+template <int WK>
+__device__ __forceinline__ void xs_store(unsigned char* xs, int k, __nv_bfloat16 v) {
+    const int i = k >> 9, l = (k >> 4) & 31, j = k & 15;
+    if (WK == WK_INT4_PACK)
+        reinterpret_cast<__nv_bfloat16*>(xs)[(((i * 2 + (j >> 3)) * 32 + l) << 3) + (j & 7)] = v;
+    else
+        reinterpret_cast<float*>(xs)[(((i * 4 + (j >> 2)) * 32 + l) << 2) + (j & 3)] = bf2f(v);
+}
 template <int WK>
 __device__ __forceinline__ float xs_load(const unsigned char* xs, int k) {
     const int i = k >> 9, l = (k >> 4) & 31, j = k & 15;
@@ -209,24 +218,38 @@ __device__ __forceinline__ uint4 norm_vec8(const uint4& xq, const uint4& wq, flo
     return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
-/* `load(v)` returns the eight consecutive bf16 activations 8v .. 8v+7 as a uint4 */
-template <int WK, int PRO, class LoadVec>
+/* barrier over the threads that stage the activation: the whole CTA unless the caller passes its own */
+struct CtaSyncFn {
+    __device__ __forceinline__ void operator()() const { S2P_CTA_SYNC(); }
+};
+
+/* `load(v)` returns the eight consecutive bf16 activations 8v .. 8v+7 as a uint4; `sync` is a barrier
+ * over exactly the `nthreads` calling threads */
+template <int WK, int PRO, class LoadVec, class SyncFn = CtaSyncFn>
 __device__ __forceinline__ void stage_activation_from(const GemvStage& g, LoadVec load, unsigned char* xs, float* red,
-                                                      int nthreads) {
+                                                      int nthreads, SyncFn sync = SyncFn()) {
     const int K = g.K, NVEC = K >> 3;
     const uint4* wsrc = reinterpret_cast<const uint4*>(g.norm_w);
-    /* the first vector of a thread stays in registers for the normalisation (the model's
-     * normed widths need no more than one per thread) */
-    const int v0 = threadIdx.x;
-    uint4 x0 = make_uint4(0, 0, 0, 0), w0 = x0;
+    /* the first two vectors of a thread stay in registers for the normalisation (the model's
+     * normed widths need no more with 256 threads), and their gains are fetched before the
+     * activations, which may have to be waited for */
+    const int v0 = threadIdx.x, v1 = threadIdx.x + nthreads;
+    uint4 x0 = make_uint4(0, 0, 0, 0), w0 = x0, x1 = x0, w1 = x0;
+    if (PRO == PRO_NORM) {
+        if (v0 < NVEC) w0 = wsrc[v0];
+        if (v1 < NVEC) w1 = wsrc[v1];
+    }
     if (v0 < NVEC) {
-        if (PRO == PRO_NORM) w0 = wsrc[v0];
         x0 = load(v0);
         xs_store_vec8<WK>(xs, v0, x0);
     }
-    for (int v = v0 + nthreads; v < NVEC; v += nthreads) xs_store_vec8<WK>(xs, v, load(v));
+    if (v1 < NVEC) {
+        x1 = load(v1);
+        xs_store_vec8<WK>(xs, v1, x1);
+    }
+    for (int v = v1 + nthreads; v < NVEC; v += nthreads) xs_store_vec8<WK>(xs, v, load(v));
     if (PRO == PRO_VEC) return;
-    S2P_CTA_SYNC();
+    sync();
     /* 256 strided partial sums of squares, halving tree, rsqrtf(mean + eps):
      * src/slowar/kernels.cu:46-68 */
     float ss = 0.f;
@@ -235,7 +258,7 @@ __device__ __forceinline__ void stage_activation_from(const GemvStage& g, LoadVe
             const float v = xs_load<WK>(xs, i);
             ss = __fmaf_rn(v, v, ss);
         }
-    const float tot = tree256_sum(ss, red); /* its first barrier also orders the reads above before the rewrite below */
+    const float tot = tree256_sum(ss, red, sync); /* its first barrier also orders the reads above before the rewrite below */
     const float inv = rsqrtf(__fdiv_rn(tot, (float)K) + g.eps);
     const bool emit = g.normed_out != nullptr && blockIdx.x == 0;
     if (v0 < NVEC) {
@@ -243,7 +266,12 @@ __device__ __forceinline__ void stage_activation_from(const GemvStage& g, LoadVe
         xs_store_vec8<WK>(xs, v0, q);
         if (emit) reinterpret_cast<uint4*>(g.normed_out)[v0] = q;
     }
-    for (int v = v0 + nthreads; v < NVEC; v += nthreads) {
+    if (v1 < NVEC) {
+        const uint4 q = norm_vec8(x1, w1, inv);
+        xs_store_vec8<WK>(xs, v1, q);
+        if (emit) reinterpret_cast<uint4*>(g.normed_out)[v1] = q;
+    }
+    for (int v = v1 + nthreads; v < NVEC; v += nthreads) {
         const uint4 q = norm_vec8(load(v), wsrc[v], inv);
         xs_store_vec8<WK>(xs, v, q);
         if (emit) reinterpret_cast<uint4*>(g.normed_out)[v] = q;

@@ -37,8 +37,9 @@ constexpr int MEGA_ISSUER = MEGA_WORKERS - 32;  /* lane 0 of the last warp issue
 constexpr int MEGA_SLOTS = MEGA_RING_SLOTS;
 constexpr int MEGA_PARTS = MEGA_PARTIAL_BUFFERS;
 constexpr int MEGA_RED_BYTES = 3072;            /* 260 floats tree | 256 residuals | 252 row scales */
-constexpr int MEGA_TAIL_BYTES = 1024;           /* mbarriers, the staged copy command, two stage descriptors */
-static_assert(sizeof(MegaStage) % 16 == 0 && 2 * sizeof(MegaStage) + 256 <= MEGA_TAIL_BYTES, "descriptor staging");
+constexpr int MEGA_TAIL_BYTES = 1536;           /* mbarriers, the staged copy command, two stage descriptors, the stage kinds */
+constexpr int MEGA_MAX_STAGES = 512;
+static_assert(sizeof(MegaStage) % 16 == 0 && 2 * sizeof(MegaStage) + 256 + MEGA_MAX_STAGES <= MEGA_TAIL_BYTES, "descriptor staging");
 constexpr int MEGA_SMEM_MAX = 225 * 1024; /* 227 KB per CTA less the kernel's static shared memory */
 constexpr int MEGA_PART_BYTES_DEFAULT = 19456;  /* 152 (row, tile) units: 30 rows of 5 tiles, 19 of 8, 8 of 19 */
 /* shared memory: ring slots | work area (x | partial buffers | red) | tail.  Attention and the
@@ -79,28 +80,39 @@ __device__ __forceinline__ void store_all(T* p, T v) {
     for (int i = 0; i < g_tp.n; i++) *reinterpret_cast<T*>(reinterpret_cast<unsigned char*>(p) + g_tp.delta[i]) = v;
 }
 
+/* What every thread needs to know about the ring and the partial buffers.  One copy in shared
+ * memory, written once at kernel start: the per-stage functions below are compiled out of line
+ * (their registers are their own), and what they share travels through here rather than through
+ * by-reference arguments, which would live in local memory. */
 struct Ring {
-    unsigned char* slots;
-    uint64_t* full;    /* [MEGA_SLOTS] a chunk has landed */
-    uint64_t* pfull;   /* [MEGA_PARTS] all warps have written their partials of a chunk */
-    uint64_t* pdone;   /* [MEGA_PARTS] all warps have folded their rows of it (its slot and buffer are free) */
     int* status;
     int cta, n_cta;
     int slot_bytes, part_floats, x_bytes;
+    int tail_off;      /* the mbarriers' offset in dynamic shared memory */
     unsigned seq_base; /* stage instances of earlier ticks */
-    unsigned tag;      /* the tag this stage writes into its flagged outputs */
-    unsigned consumed; /* chunks consumed so far (every thread keeps its own copy) */
     /* issuer thread only: this CTA's command list (built by the host with mega_stage_geom,
-     * the function the consumers use), how many were issued, and the next one, loaded early */
+     * the function the consumers use), how many were issued */
     const MegaCopyCmd* cmds;
     unsigned n_cmds, issued;
-    MegaCopyCmd* next; /* shared memory, filled by an asynchronous copy */
 };
+__shared__ Ring g_ring;
+/* the kernel's parameters, for the functions compiled out of line (a kernel parameter has no address
+ * they could take without a copy in local memory) */
+__shared__ MegaParams g_P;
+extern __shared__ __align__(1024) unsigned char g_smem[];
 
-__device__ __forceinline__ void ring_load_next(Ring& r) {
-    if (r.issued < r.n_cmds) {
-        const char* src = reinterpret_cast<const char*>(r.cmds + r.issued);
-        const uint32_t dst = smem_u32(r.next);
+__device__ __forceinline__ unsigned char* ring_slot(unsigned slot) { return g_smem + (size_t)slot * g_ring.slot_bytes; }
+__device__ __forceinline__ unsigned char* ring_work() { return g_smem + (size_t)MEGA_SLOTS * g_ring.slot_bytes; }
+__device__ __forceinline__ uint64_t* ring_bars() { return reinterpret_cast<uint64_t*>(g_smem + g_ring.tail_off); }
+__device__ __forceinline__ uint64_t* ring_full(unsigned slot) { return ring_bars() + slot; }                      /* a chunk has landed */
+__device__ __forceinline__ uint64_t* ring_pfull(unsigned b) { return ring_bars() + MEGA_SLOTS + b; }              /* the streaming warps have written a buffer */
+__device__ __forceinline__ uint64_t* ring_pdone(unsigned b) { return ring_bars() + MEGA_SLOTS + MEGA_PARTS + b; } /* the folding warps have finished it */
+__device__ __forceinline__ MegaCopyCmd* ring_next_cmd() { return reinterpret_cast<MegaCopyCmd*>(g_smem + g_ring.tail_off + 128); }
+
+__device__ __forceinline__ void ring_load_next() {
+    if (g_ring.issued < g_ring.n_cmds) {
+        const char* src = reinterpret_cast<const char*>(g_ring.cmds + g_ring.issued);
+        const uint32_t dst = smem_u32(ring_next_cmd());
 #pragma unroll
         for (int i = 0; i < 4; i++)
             asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 16 * i) : "memory");
@@ -112,124 +124,186 @@ __device__ __forceinline__ void ring_load_next(Ring& r) {
  * started.  The caller guarantees their slots are free: chunk q reuses the slot of chunk
  * q - MEGA_SLOTS, so limit = q + 1 + MEGA_SLOTS once chunk q is known to be completely
  * consumed (and MEGA_SLOTS at kernel start). */
-__device__ __forceinline__ void ring_issue_upto(Ring& r, unsigned limit) {
-    while (r.issued < limit && r.issued < r.n_cmds) {
-        const unsigned slot = r.issued % MEGA_SLOTS;
-        unsigned char* dst = r.slots + (size_t)slot * r.slot_bytes;
+__device__ __forceinline__ void ring_issue_upto(unsigned limit) {
+    while (g_ring.issued < limit && g_ring.issued < g_ring.n_cmds) {
+        const unsigned slot = g_ring.issued % MEGA_SLOTS;
+        unsigned char* dst = ring_slot(slot);
         asm volatile("cp.async.wait_all;" ::: "memory");
-        const MegaCopyCmd c = *r.next;
+        const MegaCopyCmd c = *ring_next_cmd();
         fence_proxy_async_smem(); /* the slot's previous chunk was read through the generic proxy */
-        mbar_expect_tx(r.full + slot, c.bytes[0] + c.bytes[1] + c.bytes[2] + c.bytes[3]);
+        mbar_expect_tx(ring_full(slot), c.bytes[0] + c.bytes[1] + c.bytes[2] + c.bytes[3]);
 #pragma unroll
         for (int k = 0; k < 4; k++)
             if (c.bytes[k])
-                tma_load_1d(dst + c.dst_off[k], reinterpret_cast<const void*>(c.src[k]), c.bytes[k], r.full + slot);
-        r.issued++;
-        ring_load_next(r);
+                tma_load_1d(dst + c.dst_off[k], reinterpret_cast<const void*>(c.src[k]), c.bytes[k], ring_full(slot));
+        g_ring.issued++;
+        ring_load_next();
     }
 }
 
-/* One GEMV stage of this CTA, chunk by chunk out of the ring.  Returns false
- * (uniformly over the working warps) if a bounded wait gave up. */
-template <int WK, int TT> /* TT: K / 512 known at compile time (loops unroll), or 0 */
-__device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* trace) {
-    typedef typename LaneTile<WK>::type tile_t;
-    const MegaGeom ge = mega_stage_geom(s.lin.N, s.epi == EPI_SWIGLU, s.rows_per_chunk, r.cta, r.n_cta);
-    if (ge.cnt <= 0) { /* uniform over the CTA; leave as a GEMV stage always does: copies landed, warps together */
-        asm volatile("cp.async.wait_all;" ::: "memory");
-        S2P_CTA_SYNC();
-        return true;
+/* ---- a GEMV stage: two groups of eight warps -------------------------------------------
+ * The streaming warps (0..7) stage the activation vector and turn every chunk of weights
+ * into per-(row, K-tile) lane partials in one of the partial buffers; the folding warps
+ * (8..15) turn a finished buffer into outputs: tiles folded in ascending order with the
+ * group scales, the 16/8/4/2/1 lane tree, the epilogue, the store.  The groups meet only at
+ * mbarriers (`pfull`: a buffer is written, `pdone`: it is folded), so the streaming warps,
+ * which are bound by instruction issue, never sit in the latency-bound fold, and at a stage
+ * boundary they already wait for and stage the next stage's input while the last chunk is
+ * folded and published.  Eight warps keep the integer pipe as busy as sixteen did.
+ * Named barriers 1 and 2 synchronise the two groups separately. */
+constexpr int MEGA_STREAM_WARPS = 8;
+constexpr int MEGA_FOLD_WARPS = 8;
+constexpr int MEGA_GROUP_THREADS = 256;
+constexpr int MEGA_FOLD_CHAINS = 4; /* rows of one chunk a folding warp takes (two pairs with the SwiGLU epilogue) */
+constexpr int MEGA_NORM_ELEMS = 10; /* elements a streaming thread normalises itself: inputs up to 2560 wide */
+static_assert(MEGA_STREAM_WARPS + MEGA_FOLD_WARPS == GEMV_WARPS && MEGA_ISSUER >= 32 * MEGA_STREAM_WARPS,
+              "the copy issuer belongs to the folding group");
+
+struct StreamSync {
+    __device__ __forceinline__ void operator()() const { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+};
+__device__ __forceinline__ bool stream_sync_and(bool p) {
+    uint32_t r;
+    asm volatile("{ .reg .pred a, b; setp.ne.u32 a, %1, 0; bar.red.and.pred b, 1, 256, a; selp.u32 %0, 1, 0, b; }"
+                 : "=r"(r) : "r"((uint32_t)p) : "memory");
+    return r != 0;
+}
+
+/* Stage the input vector of a GEMV stage (streaming group only): wait for it, normalise it if the
+ * stage asks for that, lay it out in shared memory for the unit loop.  Returns false, uniformly over
+ * the group, if a bounded wait gave up. */
+template <int WK>
+__device__ __noinline__ bool gemv_stage_input(const MegaStage* sp) {
+    const MegaStage& s = *sp;
+    const int K = s.lin.K;
+    bool ok = true;
+    unsigned char* xs = ring_work();
+    float* red = reinterpret_cast<float*>(xs + g_ring.x_bytes) + MEGA_PARTS * g_ring.part_floats;
+    if (mega_stage_geom(s.lin.N, s.epi == EPI_SWIGLU, s.rows_per_chunk, g_ring.cta, g_ring.n_cta).cnt <= 0) return true; /* no rows here */
+    GemvStage g = {};
+    g.K = K; g.x = s.x.base; g.x_index = s.x.index; g.x_key = s.x.key;
+    g.norm_w = s.norm_w; g.eps = S2P_NORM_EPS; g.normed_out = s.normed_out;
+    /* the input arrives as flagged words from the CTAs (of all ranks) of stage x_from - wait
+     * for each word's tag instead of a grid barrier - or is a plain bf16 row that an earlier
+     * grid barrier has published (x_from < 0) */
+    const bool ll = s.x_from >= 0;
+    const uint4* xsrc;
+    {
+        const __nv_bfloat16* x = s.x.base;
+        if (s.x.index) x += (size_t)__ldcg(s.x.index) * K;
+        else if (s.x.key) x += (size_t)key_index(__ldcg(s.x.key)) * K;
+        xsrc = reinterpret_cast<const uint4*>(x);
     }
-    const int K = s.lin.K, T = TT ? TT : (K >> 9), gshift = s.lin.gshift;
+    const unsigned tag = (g_ring.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
+    int* status = g_ring.status;
+    /* eight elements = two 16-byte groups of flagged words, fetched together, again and again until
+     * both carry the tag (one L2 round trip once they are there, not two) */
+    auto load = [xsrc, ll, tag, status, &ok](int v) -> uint4 {
+        if (!ll) return __ldcg(xsrc + v);
+        uint4 a, b;
+        for (unsigned spin = 0;; spin++) {
+            a = flag_ld4(xsrc + 2 * v);
+            b = flag_ld4(xsrc + 2 * v + 1);
+            if (flag_tags4(a, tag) & flag_tags4(b, tag)) break;
+            if (spin > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); ok = false; }
+            if ((spin & 63u) == 63u && status_peek(status) != PIPE_OK) ok = false;
+            if (!ok) return make_uint4(0, 0, 0, 0);
+        }
+        return make_uint4((a.x & 0xFFFFu) | (a.y << 16), (a.z & 0xFFFFu) | (a.w << 16), (b.x & 0xFFFFu) | (b.y << 16),
+                          (b.z & 0xFFFFu) | (b.w << 16));
+    };
+    if (s.pro == PRO_NORM && ll && (K & 255) == 0 && K <= 256 * MEGA_NORM_ELEMS) {
+        /* Normalised flagged input: thread t takes the elements t, t + 256, ... - the ones whose
+         * squares it sums in the reference's order (src/slowar/kernels.cu:46-68) - as single words,
+         * all in flight together, so the sum needs neither shared memory nor a barrier; the 256 sums
+         * meet in the halving tree, and the thread normalises its own elements
+         * (y = bf16(x * inv * w)) straight into the staged layout.  Gains are fetched before the wait. */
+        const int tid = threadIdx.x;
+        const uint32_t* wsrc32 = reinterpret_cast<const uint32_t*>(xsrc);
+        const unsigned short* gain = reinterpret_cast<const unsigned short*>(s.norm_w);
+        const int ne = K >> 8;
+        unsigned short gw[MEGA_NORM_ELEMS];
+        uint32_t xw[MEGA_NORM_ELEMS];
+#pragma unroll
+        for (int m = 0; m < MEGA_NORM_ELEMS; m++) gw[m] = m < ne ? __ldg(gain + tid + 256 * m) : (unsigned short)0;
+        for (unsigned spin = 0;; spin++) {
+            bool here = true;
+#pragma unroll
+            for (int m = 0; m < MEGA_NORM_ELEMS; m++) xw[m] = m < ne ? flag_ld1(wsrc32 + tid + 256 * m) : (tag << 16);
+#pragma unroll
+            for (int m = 0; m < MEGA_NORM_ELEMS; m++) here &= (xw[m] >> 16) == tag;
+            if (here) break;
+            if (spin > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); ok = false; }
+            if ((spin & 63u) == 63u && status_peek(status) != PIPE_OK) ok = false;
+            if (!ok) break;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int m = 0; m < MEGA_NORM_ELEMS; m++)
+            if (m < ne) {
+                const float v = flag_payload(xw[m]);
+                ss = __fmaf_rn(v, v, ss);
+            }
+        const float tot = tree256_sum(ss, red, StreamSync());
+        const float inv = rsqrtf(__fdiv_rn(tot, (float)K) + S2P_NORM_EPS);
+        const bool emit = s.normed_out != nullptr && blockIdx.x == 0;
+#pragma unroll
+        for (int m = 0; m < MEGA_NORM_ELEMS; m++)
+            if (m < ne) {
+                const int k = tid + 256 * m;
+                const __nv_bfloat16 y = f2bf(__fmul_rn(__fmul_rn(flag_payload(xw[m]), inv), bf_bits_to_f32(gw[m])));
+                xs_store<WK>(xs, k, y);
+                if (emit) s.normed_out[k] = y;
+            }
+    } else if (s.pro == PRO_NORM) {
+        stage_activation_from<WK, PRO_NORM>(g, load, xs, red, MEGA_GROUP_THREADS, StreamSync());
+    } else {
+        stage_activation_from<WK, PRO_VEC>(g, load, xs, red, MEGA_GROUP_THREADS, StreamSync());
+    }
+    return stream_sync_and(ok); /* uniform over the group; the staged vector is complete */
+}
+
+/* The streaming group's part of a GEMV stage after its input is staged; `q0`: chunks this CTA consumed before the stage.
+ * Returns the stage's chunk count times two, plus one if no bounded wait gave up (uniform over
+ * the group up to the end of the staging, per warp after it). */
+template <int WK>
+__device__ __noinline__ int gemv_stream(const MegaStage* sp, unsigned q0, unsigned long long* trace) {
+    typedef typename LaneTile<WK>::type tile_t;
+    const MegaStage& s = *sp;
+    const int cta = g_ring.cta, n_cta = g_ring.n_cta;
+    const MegaGeom ge = mega_stage_geom(s.lin.N, s.epi == EPI_SWIGLU, s.rows_per_chunk, cta, n_cta);
+    if (ge.cnt <= 0) return 1; /* uniform over the CTA */
+    unsigned char* work = ring_work();
+    int* const status = g_ring.status;
+    const int part_floats = g_ring.part_floats;
+    const int K = s.lin.K, T = K >> 9;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int SW = (s.epi == EPI_SWIGLU) ? 2 : 1;
-    const int F = s.lin.N >> 1;
     const unsigned rb = (WK == WK_INT4_PACK) ? (unsigned)(K >> 1) : (unsigned)K;
-    const unsigned sb = (WK == WK_INT8_CH) ? 0u : (unsigned)(K >> gshift) * 2u;
 
-    bool ok = true;
     unsigned char* xs = work;
-    float* part0 = reinterpret_cast<float*>(work + r.x_bytes);
-    float* red = part0 + MEGA_PARTS * r.part_floats;
-    float* resid_s = red + 260;  /* residual values of this CTA's rows */
-    float* rscale_s = red + 516; /* per-channel row scales of this CTA's rows (gate rows, then up rows) */
-    {
-        /* what the epilogue needs from global memory, fetched while the activation is staged */
-        if (s.epi == EPI_RESID && threadIdx.x < ge.cnt) {
-            const __nv_bfloat16* resid = s.resid.base;
-            if (s.resid.index) resid += (size_t)__ldcg(s.resid.index) * s.lin.N;
-            else if (s.resid.key) resid += (size_t)key_index(__ldcg(s.resid.key)) * s.lin.N;
-            /* a flagged residual needs no wait: this CTA has already read the whole vector as an input */
-            resid_s[threadIdx.x] = (s.io_flags & MEGA_RESID_LL)
-                                       ? flag_payload(__ldcg(reinterpret_cast<const uint32_t*>(resid) + ge.row0 + threadIdx.x))
-                                       : ldcg_bf16(resid + ge.row0 + threadIdx.x);
-        }
-        if (WK == WK_INT8_CH && threadIdx.x < ge.cnt * SW) {
-            const int l = threadIdx.x;
-            const int grow = l < ge.cnt ? ge.row0 + l : F + ge.row0 + (l - ge.cnt);
-            rscale_s[l] = static_cast<const float*>(s.lin.scales)[grow];
-        }
-        GemvStage g = {};
-        g.K = K; g.x = s.x.base; g.x_index = s.x.index; g.x_key = s.x.key;
-        g.norm_w = s.norm_w; g.eps = S2P_NORM_EPS; g.normed_out = s.normed_out;
-        /* the input arrives as flagged words from the CTAs (of all ranks) of stage x_from - wait
-         * for each word's tag instead of a grid barrier - or is a plain bf16 row that an earlier
-         * grid barrier has published (x_from < 0) */
-        const bool ll = s.x_from >= 0;
-        const uint4* xsrc;
-        {
-            const __nv_bfloat16* x = s.x.base;
-            if (s.x.index) x += (size_t)__ldcg(s.x.index) * K;
-            else if (s.x.key) x += (size_t)key_index(__ldcg(s.x.key)) * K;
-            xsrc = reinterpret_cast<const uint4*>(x);
-        }
-        const unsigned tag = (r.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
-        int* status = r.status;
-        auto load = [xsrc, ll, tag, status, &ok](int v) -> uint4 {
-            if (!ll) return __ldcg(xsrc + v);
-            uint4 a, b;
-            if (!flag_wait4(xsrc + 2 * v, tag, status, a) || !flag_wait4(xsrc + 2 * v + 1, tag, status, b)) {
-                ok = false;
-                return make_uint4(0, 0, 0, 0);
-            }
-            return make_uint4((a.x & 0xFFFFu) | (a.y << 16), (a.z & 0xFFFFu) | (a.w << 16), (b.x & 0xFFFFu) | (b.y << 16),
-                              (b.z & 0xFFFFu) | (b.w << 16));
-        };
-        if (s.pro == PRO_NORM) stage_activation_from<WK, PRO_NORM>(g, load, xs, red, MEGA_WORKERS);
-        else stage_activation_from<WK, PRO_VEC>(g, load, xs, red, MEGA_WORKERS);
-    }
-    if (!cta_sync_and(ok)) return false;
-    if (trace && threadIdx.x == 0) trace[1] = clock64();
-    unsigned long long best = 0ull;
-    const unsigned q0 = r.consumed;
-    long long tacc[6] = {0, 0, 0, 0, 0, 0}; /* trace: cycles of thread 0 in stream wait, stream, fold wait, fold, fold chain, fold tree */
+    float* part0 = reinterpret_cast<float*>(work + g_ring.x_bytes);
+    long long tacc[2] = {0, 0}; /* trace: cycles of thread 0 waiting for a chunk / a buffer, and streaming */
     const int pstride = T * 32;
 
-    /* Every warp streams its share of each chunk's (row, tile) units into a partial buffer
-     * and, one chunk later, folds one row (or one gate/up pair) of it.  Three buffers and
-     * mbarriers instead of CTA barriers let the warps drift apart by a chunk; odd warps
-     * fold before they stream and even warps after, so that at any time some warps run
-     * the issue-bound unit loop while others sit in the latency-bound fold. */
-    auto stream_chunk = [&](int j) -> bool {
+#pragma unroll 1
+    for (int j = 0; j < ge.n_chunks; j++) {
         const unsigned q = q0 + (unsigned)j, slot = q % MEGA_SLOTS, b = q % MEGA_PARTS;
         const int cnt = min(ge.rc, ge.cnt - j * ge.rc);
         const int local_rows = cnt * SW;
-        const unsigned char* wsl = r.slots + (size_t)slot * r.slot_bytes;
-        float* part = part0 + b * r.part_floats;
+        const unsigned char* wsl = ring_slot(slot);
+        float* part = part0 + b * part_floats;
         const long long c0 = trace ? clock64() : 0;
-        if (!mbar_wait_bounded(r.full + slot, (q / MEGA_SLOTS) & 1u, r.status)) return false;
-        /* the buffer's previous chunk (q - 3) must be folded by everyone; that also frees its slot */
-        if (q >= MEGA_PARTS) {
-            if (!mbar_wait_bounded(r.pdone + b, ((q / MEGA_PARTS) - 1u) & 1u, r.status)) return false;
-            if (threadIdx.x == MEGA_ISSUER) ring_issue_upto(r, q - MEGA_PARTS + 1 + MEGA_SLOTS);
-        }
+        if (!mbar_wait_bounded(ring_full(slot), (q / MEGA_SLOTS) & 1u, status)) return 0;
+        /* the buffer's previous chunk (q - MEGA_PARTS) must be folded */
+        if (q >= MEGA_PARTS && !mbar_wait_bounded(ring_pdone(b), ((q / MEGA_PARTS) - 1u) & 1u, status)) return 0;
         const long long c1 = trace ? clock64() : 0;
         /* tile-major units; this warp's contiguous range, walked one tile segment at a time:
          * the activations of the tile stay in registers while up to four rows, whose chains
          * are independent, run side by side */
         const int U = local_rows * T;
-        int u = (int)((long long)U * warp / GEMV_WARPS);
-        const int u_end = (int)((long long)U * (warp + 1) / GEMV_WARPS);
+        int u = (int)((long long)U * warp / MEGA_STREAM_WARPS);
+        const int u_end = (int)((long long)U * (warp + 1) / MEGA_STREAM_WARPS);
 #pragma unroll 1
         while (u < u_end) {
             const int tile = u / local_rows, lr0 = u - tile * local_rows;
@@ -265,142 +339,211 @@ __device__ bool gemv_chunks(const MegaStage& s, Ring& r, unsigned char* work, un
             u += n;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(r.pfull + b); /* release: the partials are visible to whoever waits */
+        if (lane == 0) mbar_arrive(ring_pfull(b)); /* release: the partials are visible to whoever waits */
         if (trace && threadIdx.x == 0) {
             const long long c2 = clock64();
             tacc[0] += c1 - c0; tacc[1] += c2 - c1;
         }
-        return true;
-    };
+    }
+    if (trace && threadIdx.x == 0) { trace[4] = (unsigned long long)tacc[0]; trace[5] = (unsigned long long)tacc[1]; }
+    if (trace && lane == 0) trace[8 + warp] = clock64(); /* when each streaming warp was through */
+    return 2 * ge.n_chunks + 1;
+}
 
-    /* output n of the stage: a bf16 cell, or a flagged word consumers wait on */
-    const bool y_ll = (s.io_flags & MEGA_Y_LL) != 0;
-    const unsigned my_tag = r.tag;
-    auto put_y = [&](int n, __nv_bfloat16 v) {
-        if (y_ll) store_all(reinterpret_cast<uint32_t*>(s.y) + n, flag_word(v, my_tag));
-        else store_all(s.y + n, v);
-    };
+/* What the folding group needs of a stage descriptor, read from global memory (the staged
+ * copy in shared memory belongs to the streaming group, which may be a stage ahead). */
+struct FoldDesc {
+    int N, K, gshift, epi, rows_per_chunk, io_flags;
+    const void* scales;
+    __nv_bfloat16* y;
+    VecRef resid;
+    unsigned long long* key;
+};
+__device__ __forceinline__ FoldDesc fold_desc_load(const MegaStage* g) {
+    FoldDesc d;
+    d.N = __ldg(&g->lin.N); d.K = __ldg(&g->lin.K); d.gshift = __ldg(&g->lin.gshift);
+    d.epi = __ldg(&g->epi); d.rows_per_chunk = __ldg(&g->rows_per_chunk); d.io_flags = __ldg(&g->io_flags);
+    d.scales = reinterpret_cast<const void*>(__ldg(reinterpret_cast<const unsigned long long*>(&g->lin.scales)));
+    d.y = reinterpret_cast<__nv_bfloat16*>(__ldg(reinterpret_cast<const unsigned long long*>(&g->y)));
+    d.resid.base = reinterpret_cast<const __nv_bfloat16*>(__ldg(reinterpret_cast<const unsigned long long*>(&g->resid.base)));
+    d.resid.index = reinterpret_cast<const int32_t*>(__ldg(reinterpret_cast<const unsigned long long*>(&g->resid.index)));
+    d.resid.key = reinterpret_cast<const unsigned long long*>(__ldg(reinterpret_cast<const unsigned long long*>(&g->resid.key)));
+    d.key = reinterpret_cast<unsigned long long*>(__ldg(reinterpret_cast<const unsigned long long*>(&g->key)));
+    return d;
+}
 
-    /* fold the tiles of row `warp` (rows `warp` and `warp + cnt` of a SwiGLU pair, chains
-     * interleaved) in ascending order, merge lanes, run the epilogue */
-    auto fold_chunk = [&](int j) -> bool {
+/* Fold up to four rows of a chunk (chains c < nch; row c's partials at pp[c], its group scales
+ * at ss[c]): per lane the tiles in ascending order, acc = fma(partial, group scale, acc) (INT4,
+ * grouped INT8) or acc += partial (per-channel INT8), then the 16/8/4/2/1 lane tree.  TT > 0:
+ * the tile count at compile time, so that all loads of the chains are in flight together. */
+template <int WK, int TT, int C0, int C1>
+__device__ __forceinline__ void fold_chain_pass(int T, int nch, const float* const* pp, const __half* const* ss, int sstep, float* acc) {
+    if (TT) {
+#pragma unroll
+        for (int i = 0; i < (TT ? TT : 1); i++) {
+#pragma unroll
+            for (int c = C0; c < C1; c++)
+                if (c < nch) {
+                    if (WK == WK_INT8_CH) acc[c] += pp[c][i * 32];
+                    else acc[c] = __fmaf_rn(pp[c][i * 32], __half2float(ss[c][i * sstep]), acc[c]);
+                }
+        }
+    } else {
+#pragma unroll 2
+        for (int i = 0; i < T; i++) {
+#pragma unroll
+            for (int c = C0; c < C1; c++)
+                if (c < nch) {
+                    if (WK == WK_INT8_CH) acc[c] += pp[c][i * 32];
+                    else acc[c] = __fmaf_rn(pp[c][i * 32], __half2float(ss[c][i * sstep]), acc[c]);
+                }
+        }
+    }
+}
+/* PASS2: the chains run as two passes of two (fewer loads in flight: wide rows), else all four together */
+template <int WK, int TT, bool PASS2>
+__device__ __forceinline__ void fold_chains(int T, int nch, const float* const* pp, const __half* const* ss, int sstep, float* acc) {
+#pragma unroll
+    for (int c = 0; c < MEGA_FOLD_CHAINS; c++) acc[c] = 0.f;
+    if (PASS2) {
+        fold_chain_pass<WK, TT, 0, 2>(T, nch, pp, ss, sstep, acc);
+        if (nch > 2) fold_chain_pass<WK, TT, 2, 4>(T, nch, pp, ss, sstep, acc);
+    } else {
+        fold_chain_pass<WK, TT, 0, 4>(T, nch, pp, ss, sstep, acc);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int c = 0; c < MEGA_FOLD_CHAINS; c++) acc[c] += __shfl_xor_sync(S2P_FULL_MASK, acc[c], off);
+    }
+}
+
+/* The folding group's part of a GEMV stage (`gs`: the descriptor in global memory, `my_tag`: the tag
+ * of the stage's flagged outputs).  Returns like gemv_stream, per warp. */
+template <int WK>
+__device__ __noinline__ int gemv_fold(const MegaStage* gs, unsigned q0, unsigned my_tag, unsigned long long* trace) {
+    const FoldDesc d = fold_desc_load(gs);
+    const bool two = d.epi == EPI_SWIGLU;
+    const MegaGeom ge = mega_stage_geom(d.N, two, d.rows_per_chunk, g_ring.cta, g_ring.n_cta);
+    if (ge.cnt <= 0) return 1;
+    unsigned char* work = ring_work();
+    int* const status = g_ring.status;
+    const int part_floats = g_ring.part_floats;
+    const int K = d.K, T = K >> 9, gshift = d.gshift;
+    const int lane = threadIdx.x & 31, fw = (threadIdx.x >> 5) - MEGA_STREAM_WARPS;
+    const int SW = two ? 2 : 1;
+    const int F = d.N >> 1;
+    const unsigned rb = (WK == WK_INT4_PACK) ? (unsigned)(K >> 1) : (unsigned)K;
+    const unsigned sb = (WK == WK_INT8_CH) ? 0u : (unsigned)(K >> gshift) * 2u;
+    const float* part0 = reinterpret_cast<const float*>(work + g_ring.x_bytes);
+    const int pstride = T * 32;
+    const int sl = (lane * 16) >> gshift, sstep = 512 >> gshift;
+    const bool y_ll = (d.io_flags & MEGA_Y_LL) != 0;
+    unsigned long long best = 0ull;
+    bool ok = true;
+    long long tacc[2] = {0, 0};
+    /* the residual row (EPI_RESID): the vector itself, or a row of a table picked on the device */
+    const __nv_bfloat16* resid = d.resid.base;
+    if (d.epi == EPI_RESID) {
+        if (d.resid.index) resid += (size_t)__ldcg(d.resid.index) * d.N;
+        else if (d.resid.key) resid += (size_t)key_index(__ldcg(d.resid.key)) * d.N;
+    }
+
+#pragma unroll 1
+    for (int j = 0; j < ge.n_chunks; j++) {
         const unsigned q = q0 + (unsigned)j, slot = q % MEGA_SLOTS, b = q % MEGA_PARTS;
         const int cnt = min(ge.rc, ge.cnt - j * ge.rc);
         const int l0 = j * ge.rc, r0 = ge.row0 + l0;
         const int local_rows = cnt * SW;
-        const unsigned char* ssl = r.slots + (size_t)slot * r.slot_bytes + (size_t)local_rows * rb;
-        const float* part = part0 + b * r.part_floats;
+        const unsigned char* ssl = ring_slot(slot) + (size_t)local_rows * rb;
+        const float* part = part0 + b * part_floats;
+        /* chains of this warp: plain rows fw, fw+8, fw+16, fw+24 of the chunk; with SwiGLU the
+         * gate rows of pairs fw, fw+8 (chains 0, 1) and their up rows (chains 2, 3) */
+        int lr[MEGA_FOLD_CHAINS], nch;
+        if (two) {
+            lr[0] = fw; lr[1] = fw + MEGA_FOLD_WARPS; lr[2] = fw + cnt; lr[3] = fw + MEGA_FOLD_WARPS + cnt;
+            nch = fw + MEGA_FOLD_WARPS < cnt ? 4 : (fw < cnt ? 3 : 0); /* a lone pair uses chains 0 and 2 */
+        } else {
+#pragma unroll
+            for (int c = 0; c < MEGA_FOLD_CHAINS; c++) lr[c] = fw + c * MEGA_FOLD_WARPS;
+            nch = fw >= cnt ? 0 : min(MEGA_FOLD_CHAINS, (cnt - fw + MEGA_FOLD_WARPS - 1) / MEGA_FOLD_WARPS);
+        }
+        const float* pp[MEGA_FOLD_CHAINS];
+        const __half* ss[MEGA_FOLD_CHAINS];
+#pragma unroll
+        for (int c = 0; c < MEGA_FOLD_CHAINS; c++) {
+            const int l = lr[c] < local_rows ? lr[c] : 0; /* unused chains point at valid memory */
+            pp[c] = part + (size_t)l * pstride + lane;
+            ss[c] = reinterpret_cast<const __half*>(ssl + (size_t)l * sb) + sl;
+        }
+        /* what the epilogue of lane c needs from global memory, fetched before the wait: the
+         * residual value and the per-channel row scale(s) of row r0 + fw + 8 c */
+        const int my_l = fw + lane * MEGA_FOLD_WARPS;             /* row (pair) of the chunk this lane finishes */
+        const bool mine = lane < (two ? 2 : MEGA_FOLD_CHAINS) && my_l < cnt;
+        const int my_n = r0 + my_l;
+        float res_v = 0.f, rs_a = 1.f, rs_b = 1.f;
+        if (mine) {
+            if (d.epi == EPI_RESID)
+                res_v = (d.io_flags & MEGA_RESID_LL) ? flag_payload(__ldcg(reinterpret_cast<const uint32_t*>(resid) + my_n))
+                                                     : ldcg_bf16(resid + my_n);
+            if (WK == WK_INT8_CH) {
+                rs_a = __ldg(static_cast<const float*>(d.scales) + my_n);
+                if (two) rs_b = __ldg(static_cast<const float*>(d.scales) + F + my_n);
+            }
+        }
         const long long c0 = trace ? clock64() : 0;
-        if (!mbar_wait_bounded(r.pfull + b, (q / MEGA_PARTS) & 1u, r.status)) return false;
+        if (!mbar_wait_bounded(ring_pfull(b), (q / MEGA_PARTS) & 1u, status)) return 0;
         const long long c1 = trace ? clock64() : 0;
-        if (warp < cnt) {
-            /* second chain: the up row of the pair, or (plain rows) row warp + 16 of the chunk */
-            const bool two = (SW == 2);
-            const bool second = !two && warp + GEMV_WARPS < cnt;
-            const int la = warp, lb = two ? warp + cnt : (second ? warp + GEMV_WARPS : warp);
-            float accA = 0.f, accB = 0.f;
-            const float* pa = part + (size_t)la * pstride + lane;
-            const float* pb = part + (size_t)lb * pstride + lane;
-            if (WK == WK_INT8_CH) {
-#pragma unroll
-                for (int i = 0; i < T; i++) { accA += pa[i * 32]; accB += pb[i * 32]; }
-            } else {
-                const __half* sa = reinterpret_cast<const __half*>(ssl + (size_t)la * sb);
-                const __half* sbp = reinterpret_cast<const __half*>(ssl + (size_t)lb * sb);
-                const int sl = (lane * 16) >> gshift, sstep = 512 >> gshift;
-#pragma unroll
-                for (int i = 0; i < T; i++) {
-                    accA = __fmaf_rn(pa[i * 32], __half2float(sa[sl + i * sstep]), accA);
-                    accB = __fmaf_rn(pb[i * 32], __half2float(sbp[sl + i * sstep]), accB);
-                }
+        if (nch > 0) {
+            float acc[MEGA_FOLD_CHAINS];
+            switch (T) {
+            /* the model's widths with the tile count at compile time */
+            case 5: fold_chains<WK, 5, false>(T, nch, pp, ss, sstep, acc); break;
+            case 8: fold_chains<WK, 8, true>(T, nch, pp, ss, sstep, acc); break;
+            case 19: fold_chains<WK, 19, true>(T, nch, pp, ss, sstep, acc); break;
+            default: fold_chains<WK, 0, false>(T, nch, pp, ss, sstep, acc); break;
             }
-            const long long f1 = trace ? clock64() : 0;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                accA += __shfl_xor_sync(S2P_FULL_MASK, accA, off);
-                accB += __shfl_xor_sync(S2P_FULL_MASK, accB, off);
-            }
-            const long long f2 = trace ? clock64() : 0;
-            if (trace && threadIdx.x == 0) { tacc[4] += f1 - c1; tacc[5] += f2 - f1; }
-            if (WK == WK_INT8_CH) {
-                accA = __fmul_rn(accA, rscale_s[l0 + la]);
-                accB = __fmul_rn(accB, rscale_s[two ? ge.cnt + l0 + la : l0 + lb]);
-            }
-            if (lane == 0) {
-                const int n = r0 + la;
+            if (mine) {
                 if (two) {
-                    const float gate = bf16_round(accA), up = bf16_round(accB);
+                    float gate = lane == 0 ? acc[0] : acc[1], up = lane == 0 ? acc[2] : acc[3];
+                    if (WK == WK_INT8_CH) { gate = __fmul_rn(gate, rs_a); up = __fmul_rn(up, rs_b); }
+                    gate = bf16_round(gate); up = bf16_round(up);
                     const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-gate)));
                     const float sil = bf16_round(__fmul_rn(gate, sig));
-                    put_y(n, f2bf(__fmul_rn(sil, up)));
+                    const __nv_bfloat16 v = f2bf(__fmul_rn(sil, up));
+                    if (y_ll) store_all(reinterpret_cast<uint32_t*>(d.y) + my_n, flag_word(v, my_tag));
+                    else store_all(d.y + my_n, v);
                 } else {
-                    const __nv_bfloat16 yb = f2bf(accA);
-                    put_y(n, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + la], bf2f(yb))) : yb);
-                    if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(yb, n));
-                    if (second) {
-                        const int n2 = n + GEMV_WARPS;
-                        const __nv_bfloat16 y2 = f2bf(accB);
-                        put_y(n2, s.epi == EPI_RESID ? f2bf(__fadd_rn(resid_s[l0 + lb], bf2f(y2))) : y2);
-                        if (s.epi == EPI_ARGMAX) best = max(best, argmax_key(y2, n2));
-                    }
+                    float a = lane == 0 ? acc[0] : (lane == 1 ? acc[1] : (lane == 2 ? acc[2] : acc[3]));
+                    if (WK == WK_INT8_CH) a = __fmul_rn(a, rs_a);
+                    const __nv_bfloat16 yb = f2bf(a);
+                    const __nv_bfloat16 v = d.epi == EPI_RESID ? f2bf(__fadd_rn(res_v, bf2f(yb))) : yb;
+                    if (y_ll) store_all(reinterpret_cast<uint32_t*>(d.y) + my_n, flag_word(v, my_tag));
+                    else store_all(d.y + my_n, v);
+                    if (d.epi == EPI_ARGMAX) best = max(best, argmax_key(yb, my_n));
                 }
             }
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(r.pdone + b); /* this warp is done with the chunk's scales and partials */
-        if (trace && threadIdx.x == 0) {
-            const long long c2 = clock64();
-            tacc[2] += c1 - c0; tacc[3] += c2 - c1;
+        if (lane == 0) mbar_arrive(ring_pdone(b)); /* this warp is done with the chunk's scales and partials */
+        if (threadIdx.x == MEGA_ISSUER) {
+            /* once every folding warp has left the chunk its slot takes the chunk MEGA_SLOTS further on */
+            if (mbar_wait_bounded(ring_pdone(b), (q / MEGA_PARTS) & 1u, status)) ring_issue_upto(q + 1 + MEGA_SLOTS);
+            else ok = false;
         }
-        return true;
-    };
-
-    /* Odd warps alternate strictly (stream 0, fold 0, stream 1, fold 1, ...); even warps run one
-     * chunk ahead with the streaming (stream 0, stream 1, fold 0, stream 2, fold 1, ..., fold n-1).
-     * One loop over 2 n actions so that each body exists once in the kernel's code. */
-    const bool fold_first = (warp & 1) != 0;
-    const int n = ge.n_chunks;
-#pragma unroll 1
-    for (int t = 0; t < 2 * n && ok; t++) {
-        bool do_stream;
-        int idx;
-        if (fold_first) { do_stream = !(t & 1); idx = t >> 1; }
-        else if (t == 0) { do_stream = true; idx = 0; }
-        else if (t & 1) { idx = (t + 1) >> 1; do_stream = idx < n; if (!do_stream) idx = n - 1; }
-        else { do_stream = false; idx = (t >> 1) - 1; }
-        ok = do_stream ? stream_chunk(idx) : fold_chunk(idx);
+        __syncwarp();
+        if (trace && fw == 0 && lane == 0) {
+            const long long c2 = clock64();
+            tacc[0] += c1 - c0; tacc[1] += c2 - c1;
+        }
     }
-    if (trace && threadIdx.x == 0) {
-#pragma unroll
-        for (int i = 0; i < 6; i++) trace[4 + i] = (unsigned long long)tacc[i]; /* plain stores: no round trip on the traced path */
-    }
-    if (s.epi == EPI_ARGMAX && lane == 0 && best) {
-        atomicMax(s.key, best);
+    if (trace && fw == 0 && lane == 0) { trace[6] = (unsigned long long)tacc[0]; trace[7] = (unsigned long long)tacc[1]; }
+    if (d.epi == EPI_ARGMAX && best) {
+        atomicMax(d.key, best);
         for (int i = 0; i < g_tp.n; i++)
-            atomicMax_system(reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(s.key) + g_tp.delta[i]), best);
+            atomicMax_system(reinterpret_cast<unsigned long long*>(reinterpret_cast<unsigned char*>(d.key) + g_tp.delta[i]), best);
     }
-    r.consumed = q0 + (unsigned)ge.n_chunks;
-    /* a warp that gave up skipped its remaining chunks: everyone leaves with the same verdict.  The
-     * barrier also publishes the next stage's descriptor (staged by asynchronous copies). */
-    asm volatile("cp.async.wait_all;" ::: "memory");
-    if (!cta_sync_and(ok)) return false;
-    /* every chunk so far is folded by every warp: all their slots are free */
-    if (threadIdx.x == MEGA_ISSUER) ring_issue_upto(r, r.consumed + MEGA_SLOTS);
-    return true;
-}
-
-template <int WK>
-__device__ __forceinline__ bool gemv_dispatch_t(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
-    /* one body per weight kind (tile count at run time): the kernel's code has to stay within
-     * reach of the instruction caches, every stage switches between these bodies */
-    return gemv_chunks<WK, 0>(s, r, work, tr);
-}
-__device__ bool gemv_dispatch(const MegaStage& s, Ring& r, unsigned char* work, unsigned long long* tr) {
-    switch (s.lin.kind) {
-    case WK_INT8_CH: return gemv_dispatch_t<WK_INT8_CH>(s, r, work, tr);
-    case WK_INT8_GRP: return gemv_dispatch_t<WK_INT8_GRP>(s, r, work, tr);
-    default: return gemv_dispatch_t<WK_INT4_PACK>(s, r, work, tr);
-    }
+    return 2 * ge.n_chunks + (ok ? 1 : 0);
 }
 
 /* ---- fast-AR attention stage: head RoPE, cache append and single-tile causal
@@ -505,18 +648,85 @@ __device__ void tick_begin_cta(const TickBeginArgs& a, unsigned tag) {
     if (a.keys && threadIdx.x < 9) a.keys[threadIdx.x] = 0ull;
 }
 
+/* The stages that take the whole CTA: frame start, attention of both stacks, sampler, frame end.
+ * Each out of line with registers of its own, so that the stage loop of the kernel stays small and
+ * holds few registers across its calls. */
+__device__ __noinline__ void cta_stage_attn_slow(const MegaStage* sp, unsigned my_tag) {
+    const MegaStage& s = *sp;
+    const int n_local = gridDim.x;
+    const int cta = g_P.tp_rank * n_local + blockIdx.x, n_cta = g_P.tp_world * n_local;
+    const unsigned in_tag = (g_P.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
+    /* the workers of one kv head are consecutive CTAs of one rank (8 divides by tp_world);
+     * its cache planes are only kept current on that rank */
+    const int workers = n_cta / S2P_SLOW_KV_HEADS;
+    if (cta >= workers * S2P_SLOW_KV_HEADS) return;
+    AttnArgs a = {};
+    a.out = s.out;
+    a.q_heads = S2P_SLOW_Q_HEADS; a.kv_heads = S2P_SLOW_KV_HEADS; a.max_seq = g_P.ctx_len; a.kv8 = g_P.kv8;
+    a.pos_arr = g_P.pos_arr; a.kv = s.kv; a.part = g_P.part; a.counters = g_P.counters;
+    a.n_split_slots = g_P.n_split_slots; a.workers = workers; a.head_dim = g_P.head_dim;
+    a.n_out_peers = g_tp.n; a.out_peer_delta = g_tp.delta;
+    a.out_ll = 1; a.out_ll_tag = my_tag;
+    const AttnPrep pz = {s.qkv, s.q_norm, s.k_norm, g_P.eps, g_P.rope_base,
+                         reinterpret_cast<const uint32_t*>(s.qkv), in_tag, g_P.status};
+    if (g_P.kv8)
+        attn_decode_cta<true, true, 1>(a, pz, 0, cta / workers, cta % workers, workers, *reinterpret_cast<AttnSmem<true>*>(ring_work()));
+    else
+        attn_decode_cta<false, true, 1>(a, pz, 0, cta / workers, cta % workers, workers, *reinterpret_cast<AttnSmem<false>*>(ring_work()));
+}
+
+__device__ __noinline__ void cta_stage_other(const MegaStage* sp, int stage_type, unsigned my_tag) {
+    const MegaStage& s = *sp;
+    const int tid = threadIdx.x;
+    const bool cta0 = blockIdx.x == 0;
+    unsigned char* work = ring_work();
+    const unsigned in_tag = (g_P.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
+    switch (stage_type) {
+    case MEGA_BEGIN:
+        if (cta0) tick_begin_cta(g_P.begin, my_tag);
+        break;
+    case MEGA_ATTN_FAST:
+        /* kv head h of the fast-AR lives on rank h / (8 / tp_world), always in the same CTA */
+        if ((int)blockIdx.x < S2P_SLOW_KV_HEADS / g_P.tp_world)
+            fast_attn_cta(s, g_P.tp_rank * (S2P_SLOW_KV_HEADS / g_P.tp_world) + blockIdx.x, g_P.rope_base, g_P.head_dim, in_tag,
+                          my_tag, g_P.status, *reinterpret_cast<FastAttnSmem*>(work));
+        break;
+    case MEGA_SAMPLE:
+        if (cta0) { /* every rank samples for itself: same logits, same state, same draw */
+            /* the head stages wrote flagged words: wait for them and unflag into the scratch row */
+            const uint32_t* lc = reinterpret_cast<const uint32_t*>(g_P.sem_logits);
+            const unsigned tc = (g_P.seq_base + (unsigned)g_P.logc_from + 1u) & 0xFFFFu;
+            const unsigned te = (g_P.seq_base + (unsigned)g_P.loge_from + 1u) & 0xFFFFu;
+            for (int i = tid; i < 4097; i += MEGA_WORKERS) {
+                uint32_t w = 0;
+                if (i < 4096) flag_wait1(lc + i, tc, g_P.status, w);
+                else flag_wait1(reinterpret_cast<const uint32_t*>(g_P.eos_logit), te, g_P.status, w);
+                reinterpret_cast<unsigned short*>(g_P.logits_plain)[i] = (unsigned short)(w & 0xFFFFu);
+            }
+            __threadfence_block();
+            S2P_CTA_SYNC();
+            sampler_cta<MEGA_WORKERS>(g_P.logits_plain, g_P.logits_plain + 4096, g_P.states[0], g_P.out_tok, g_P.out_sem,
+                                      g_P.out_codes, g_P.out_eos, *reinterpret_cast<SamplerSmem<MEGA_WORKERS>*>(work));
+        }
+        break;
+    case MEGA_FINISH:
+        if (cta0 && tid < 9) g_P.out_codes[tid + 1] = (int32_t)key_index(__ldcg(g_P.keys + tid));
+        break;
+    default: break;
+    }
+}
+
 __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
-    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* const smem = g_smem;
     unsigned char* work = smem + (size_t)MEGA_SLOTS * P.lay.slot_bytes;
     unsigned char* tail = work + P.lay.x_bytes + MEGA_PARTS * P.lay.part_bytes + MEGA_RED_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail);
-    MegaCopyCmd* next_cmd = reinterpret_cast<MegaCopyCmd*>(tail + 128);
-    static_assert(MEGA_SLOTS + 2 * MEGA_PARTS <= 16, "the barrier words precede the staged command");
+    static_assert(MEGA_SLOTS + 2 * MEGA_PARTS + 1 <= 16, "the barrier words precede the staged command");
     /* cta / n_cta: position in the grid of all ranks (they equal blockIdx.x / gridDim.x on one GPU) */
     const int n_local = gridDim.x, tid = threadIdx.x;
     const int cta = P.tp_rank * n_local + blockIdx.x, n_cta = P.tp_world * n_local;
-    const bool cta0 = blockIdx.x == 0; /* the CTA of each rank that runs the frame start, the sampler and the frame end */
 
+    if (tid == 32) g_P = P;
     if (tid == 0) { /* constant indices only: see TpPeers */
         int n = 0;
 #pragma unroll
@@ -530,139 +740,155 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
             }
         g_tp.n = n;
     }
-    Ring ring;
-    ring.slots = smem; ring.full = bars; ring.pfull = bars + MEGA_SLOTS; ring.pdone = bars + MEGA_SLOTS + MEGA_PARTS;
-    ring.status = P.status;
-    ring.seq_base = P.seq_base; ring.tag = 0;
-    ring.slot_bytes = P.lay.slot_bytes; ring.part_floats = P.lay.part_bytes / 4; ring.x_bytes = P.lay.x_bytes;
-    ring.cta = cta; ring.n_cta = n_cta; ring.consumed = 0;
-    ring.cmds = P.cmds + P.cmd_start[blockIdx.x];
-    ring.n_cmds = (unsigned)(P.cmd_start[blockIdx.x + 1] - P.cmd_start[blockIdx.x]);
-    ring.issued = 0; ring.next = next_cmd;
+    uint64_t* join = bars + MEGA_SLOTS + 2 * MEGA_PARTS; /* where the two groups meet before a stage that needs the whole CTA */
     if (tid == MEGA_ISSUER) {
-        for (int i = 0; i < MEGA_SLOTS; i++) mbar_init(ring.full + i, 1);
+        g_ring.status = P.status;
+        g_ring.seq_base = P.seq_base;
+        g_ring.slot_bytes = P.lay.slot_bytes; g_ring.part_floats = P.lay.part_bytes / 4; g_ring.x_bytes = P.lay.x_bytes;
+        g_ring.tail_off = (int)(tail - smem);
+        g_ring.cta = cta; g_ring.n_cta = n_cta;
+        g_ring.cmds = P.cmds + P.cmd_start[blockIdx.x];
+        g_ring.n_cmds = (unsigned)(P.cmd_start[blockIdx.x + 1] - P.cmd_start[blockIdx.x]);
+        g_ring.issued = 0;
+        for (int i = 0; i < MEGA_SLOTS; i++) mbar_init(ring_full(i), 1);
         for (int i = 0; i < MEGA_PARTS; i++) {
-            mbar_init(ring.pfull + i, GEMV_WARPS);
-            mbar_init(ring.pdone + i, GEMV_WARPS);
+            mbar_init(ring_pfull(i), MEGA_STREAM_WARPS);
+            mbar_init(ring_pdone(i), MEGA_FOLD_WARPS);
         }
+        mbar_init(join, GEMV_WARPS);
         mbar_init_fence();
-        ring_load_next(ring);
-        ring_issue_upto(ring, MEGA_SLOTS);
+        ring_load_next();
+        ring_issue_upto(MEGA_SLOTS);
     }
-    __syncthreads(); /* the barriers are initialised before anyone waits on them */
+    /* kind and flags of every stage, for both groups: one byte each (kind | flags << 4) */
+    unsigned char* kinds = tail + 256 + 2 * sizeof(MegaStage);
+#define MEGA_KINDS() (g_smem + g_ring.tail_off + 256 + 2 * sizeof(MegaStage))
+#define MEGA_STBUF() reinterpret_cast<MegaStage*>(g_smem + g_ring.tail_off + 256)
+#define MEGA_JOIN() (reinterpret_cast<uint64_t*>(g_smem + g_ring.tail_off) + MEGA_SLOTS + 2 * MEGA_PARTS)
+#define MEGA_TR() ((P.trace && blockIdx.x == 0) ? P.trace + (size_t)si * 16 : nullptr)
+    for (int i = tid; i < P.n_stages; i += MEGA_THREADS)
+        kinds[i] = (unsigned char)(__ldg(&P.stages[i].type) | (__ldg(&P.stages[i].flags) << 4));
 
-    /* Stage descriptors are staged one stage ahead in shared memory: read from global
-     * memory at the start of a stage they would cost two dependent cache misses. */
-    MegaStage* st_buf = reinterpret_cast<MegaStage*>(tail + 256);
+    /* Stage descriptors are staged one stage ahead in shared memory by the streaming group: read
+     * from global memory at the start of a stage they would cost two dependent cache misses. */
     constexpr int ST_VECS = (int)(sizeof(MegaStage) / 16);
+    static_assert(ST_VECS <= MEGA_GROUP_THREADS, "one thread per 16 bytes of a descriptor");
     auto stage_prefetch = [&](int si) {
-        if (si < P.n_stages && tid < ST_VECS)
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(st_buf + (si & 1)) + 16u * tid),
-                         "l"(reinterpret_cast<const char*>(P.stages + si) + 16 * tid) : "memory");
+        if (si < P.n_stages && threadIdx.x < ST_VECS)
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(MEGA_STBUF() + (si & 1)) + 16u * threadIdx.x),
+                         "l"(reinterpret_cast<const char*>(P.stages + si) + 16 * threadIdx.x) : "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     stage_prefetch(0);
     asm volatile("cp.async.wait_all;" ::: "memory");
-    __syncthreads();
+    __syncthreads(); /* barriers initialised, first descriptor and the kinds table in place */
 
-    unsigned n_bar = 0;
+    /* `ok` turns false when a bounded wait of this thread gave up (the status word is set then, and
+     * every other wait gives up soon after).  A thread that sees it leaves the stage loop; nobody
+     * may be left behind at a barrier, so the verdict is made uniform where a barrier follows: over
+     * the streaming group at its barrier on entering a GEMV stage, over the CTA at the join
+     * (an mbarrier with a bounded wait). */
+    unsigned n_bar = 0, n_join = 0, consumed = 0; /* consumed: chunks of the ring this CTA is through (every thread counts) */
     bool ok = true;
-    for (int si = 0; si < P.n_stages && ok; si++) {
-        const MegaStage& s = st_buf[si & 1];
-        /* what is needed after the stage's last barrier is read now: past that barrier a faster
-         * thread may already be staging stage si + 2 over this descriptor */
-        const int no_barrier = s.flags & MEGA_NO_BARRIER, stage_type = s.type;
-        stage_prefetch(si + 1); /* the other buffer held stage si - 1, which every thread has left */
-        unsigned long long* tr = (P.trace && cta0) ? P.trace + (size_t)si * 16 : nullptr;
-        if (tr && tid == 0) { tr[0] = clock64(); }
+    for (int si = 0; si < P.n_stages; si++) {
+        const int stage_type = MEGA_KINDS()[si] & 15, no_barrier = (MEGA_KINDS()[si] >> 4) & MEGA_NO_BARRIER;
         const unsigned my_tag = (P.seq_base + (unsigned)si + 1u) & 0xFFFFu;
-        const unsigned in_tag = (P.seq_base + (unsigned)s.x_from + 1u) & 0xFFFFu;
-        ring.tag = my_tag;
-        switch (s.type) {
-        case MEGA_BEGIN:
-            if (cta0) tick_begin_cta(P.begin, my_tag);
-            break;
-        case MEGA_GEMV:
-            ok = gemv_dispatch(s, ring, work, tr);
-            break;
-        case MEGA_ATTN_SLOW: {
-            /* the workers of one kv head are consecutive CTAs of one rank (8 divides by tp_world);
-             * its cache planes are only kept current on that rank */
-            const int workers = n_cta / S2P_SLOW_KV_HEADS;
-            if (cta < workers * S2P_SLOW_KV_HEADS) {
-                AttnArgs a = {};
-                a.out = s.out;
-                a.q_heads = S2P_SLOW_Q_HEADS; a.kv_heads = S2P_SLOW_KV_HEADS; a.max_seq = P.ctx_len; a.kv8 = P.kv8;
-                a.pos_arr = P.pos_arr; a.kv = s.kv; a.part = P.part; a.counters = P.counters;
-                a.n_split_slots = P.n_split_slots; a.workers = workers; a.head_dim = P.head_dim;
-                a.n_out_peers = g_tp.n; a.out_peer_delta = g_tp.delta;
-                a.out_ll = 1; a.out_ll_tag = my_tag;
-                const AttnPrep pz = {s.qkv, s.q_norm, s.k_norm, P.eps, P.rope_base,
-                                     reinterpret_cast<const uint32_t*>(s.qkv), in_tag, P.status};
-                if (P.kv8)
-                    attn_decode_cta<true, true, 1>(a, pz, 0, cta / workers, cta % workers, workers,
-                                                *reinterpret_cast<AttnSmem<true>*>(work));
-                else
-                    attn_decode_cta<false, true, 1>(a, pz, 0, cta / workers, cta % workers, workers,
-                                                 *reinterpret_cast<AttnSmem<false>*>(work));
-            }
-            break;
-        }
-        case MEGA_ATTN_FAST:
-            /* kv head h of the fast-AR lives on rank h / (8 / tp_world), always in the same CTA */
-            if ((int)blockIdx.x < S2P_SLOW_KV_HEADS / P.tp_world)
-                fast_attn_cta(s, P.tp_rank * (S2P_SLOW_KV_HEADS / P.tp_world) + blockIdx.x, P.rope_base, P.head_dim, in_tag,
-                              my_tag, P.status, *reinterpret_cast<FastAttnSmem*>(work));
-            break;
-        case MEGA_SAMPLE:
-            if (cta0) { /* every rank samples for itself: same logits, same state, same draw */
-                /* the head stages wrote flagged words: wait for them and unflag into the scratch row */
-                const uint32_t* lc = reinterpret_cast<const uint32_t*>(P.sem_logits);
-                const unsigned tc = (P.seq_base + (unsigned)P.logc_from + 1u) & 0xFFFFu;
-                const unsigned te = (P.seq_base + (unsigned)P.loge_from + 1u) & 0xFFFFu;
-                for (int i = tid; i < 4097; i += MEGA_WORKERS) {
-                    uint32_t w = 0;
-                    if (i < 4096) flag_wait1(lc + i, tc, P.status, w);
-                    else flag_wait1(reinterpret_cast<const uint32_t*>(P.eos_logit), te, P.status, w);
-                    reinterpret_cast<unsigned short*>(P.logits_plain)[i] = (unsigned short)(w & 0xFFFFu);
+        if (stage_type == MEGA_GEMV) {
+            if (threadIdx.x < MEGA_GROUP_THREADS) {
+                /* the descriptor was staged while the previous stage ran; the group barrier inside
+                 * gemv_stream (or the join below) publishes it to the group */
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                if (!stream_sync_and(ok)) { ok = false; break; }
+                const MegaStage& s = MEGA_STBUF()[si & 1];
+                stage_prefetch(si + 1); /* the other buffer held stage si - 1, which the group has left */
+                if (MEGA_TR() && threadIdx.x == 0) MEGA_TR()[0] = clock64();
+                /* (the group barrier above: every streaming warp has left the previous stage's activation) */
+                int rc = 0;
+                bool staged;
+                switch (s.lin.kind) {
+                case WK_INT8_CH: staged = gemv_stage_input<WK_INT8_CH>(&s); break;
+                case WK_INT8_GRP: staged = gemv_stage_input<WK_INT8_GRP>(&s); break;
+                default: staged = gemv_stage_input<WK_INT4_PACK>(&s); break;
                 }
-                __threadfence_block();
-                S2P_CTA_SYNC();
-                sampler_cta<MEGA_WORKERS>(P.logits_plain, P.logits_plain + 4096, P.states[0], P.out_tok, P.out_sem,
-                                          P.out_codes, P.out_eos, *reinterpret_cast<SamplerSmem<MEGA_WORKERS>*>(work));
+                if (MEGA_TR() && threadIdx.x == 0) MEGA_TR()[1] = clock64();
+                if (P.trace && threadIdx.x == 0) { /* every CTA: when its input was staged, on the GPU-wide timer */
+                    unsigned long long gt;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+                    P.trace[(size_t)P.n_stages * (16 + (int)gridDim.x) + (size_t)si * (int)gridDim.x + blockIdx.x] = gt;
+                }
+                if (staged) switch (s.lin.kind) {
+                case WK_INT8_CH: rc = gemv_stream<WK_INT8_CH>(&s, consumed, MEGA_TR()); break;
+                case WK_INT8_GRP: rc = gemv_stream<WK_INT8_GRP>(&s, consumed, MEGA_TR()); break;
+                default: rc = gemv_stream<WK_INT4_PACK>(&s, consumed, MEGA_TR()); break;
+                }
+                ok = rc & 1; consumed += (unsigned)(rc >> 1);
+                if (MEGA_TR() && threadIdx.x == 0) MEGA_TR()[2] = clock64();
+            } else {
+                if (!ok) break; /* the folding warps share no barrier: each leaves on its own */
+                const MegaStage* gs = P.stages + si;
+                int rc;
+                switch (__ldg(&gs->lin.kind)) {
+                case WK_INT8_CH: rc = gemv_fold<WK_INT8_CH>(gs, consumed, my_tag, MEGA_TR()); break;
+                case WK_INT8_GRP: rc = gemv_fold<WK_INT8_GRP>(gs, consumed, my_tag, MEGA_TR()); break;
+                default: rc = gemv_fold<WK_INT4_PACK>(gs, consumed, my_tag, MEGA_TR()); break;
+                }
+                ok = rc & 1; consumed += (unsigned)(rc >> 1);
+                if (MEGA_TR() && threadIdx.x == MEGA_GROUP_THREADS) MEGA_TR()[3] = clock64();
+                if (P.trace && threadIdx.x == MEGA_GROUP_THREADS) { /* every CTA: when its outputs of the stage were out, on the GPU-wide timer */
+                    unsigned long long gt;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+                    P.trace[(size_t)P.n_stages * 16 + (size_t)si * (int)gridDim.x + blockIdx.x] = gt;
+                }
             }
-            break;
-        case MEGA_FINISH:
-            if (cta0 && tid < 9) P.out_codes[tid + 1] = (int32_t)key_index(__ldcg(P.keys + tid));
-            break;
-        default: break;
+            if (no_barrier) continue; /* the groups go on separately; the next stage's waits order them */
         }
-        if (tr && tid == 0) tr[2] = clock64();
-        if (P.trace && tid == 0) { /* every CTA: when its own work of the stage was done, on the GPU-wide timer */
-            unsigned long long gt;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
-            P.trace[(size_t)P.n_stages * 16 + (size_t)si * n_local + blockIdx.x] = gt;
+        /* A stage of the whole CTA (or a grid barrier) follows: the groups meet.  One arrival per
+         * warp; the wait is bounded like every other, so a group that gave up cannot strand the other. */
+        if (!ok) break; /* without arriving: the others' wait at the join runs out */
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive(MEGA_JOIN());
+        if (!mbar_wait_bounded(MEGA_JOIN(), n_join & 1u, P.status)) { ok = false; break; }
+        n_join++;
+        /* all sixteen warps arrived, so all of them are fine and take the CTA barriers below */
+        if (stage_type != MEGA_GEMV) {
+            if (threadIdx.x < MEGA_GROUP_THREADS) asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncthreads();
+            if (MEGA_TR() && threadIdx.x == 0) MEGA_TR()[0] = clock64();
+            if (stage_type == MEGA_ATTN_SLOW) cta_stage_attn_slow(MEGA_STBUF() + (si & 1), my_tag);
+            else cta_stage_other(MEGA_STBUF() + (si & 1), stage_type, my_tag);
+            if (MEGA_TR() && threadIdx.x == 0) MEGA_TR()[2] = clock64();
+            if (P.trace && threadIdx.x == 0) {
+                unsigned long long gt;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+                P.trace[(size_t)P.n_stages * 16 + (size_t)si * (int)gridDim.x + blockIdx.x] = gt;
+            }
+            __syncthreads(); /* the work area and the descriptor buffer are free again */
+            if (threadIdx.x < MEGA_GROUP_THREADS) stage_prefetch(si + 1);
         }
-        asm volatile("cp.async.wait_all;" ::: "memory"); /* the next descriptor; the barrier below publishes it */
-        /* without a grid barrier the next stage still reuses the work area: wait for this
-         * CTA's slowest warp */
-        if (no_barrier && stage_type != MEGA_GEMV) S2P_CTA_SYNC(); /* a GEMV stage ends with its own barrier */
-        if (ok && !no_barrier) {
+        if (!no_barrier) {
             n_bar++;
-            ok = grid_barrier_tp(P.barrier, g_tp.delta, g_tp.n, (P.bar_base + n_bar) * (unsigned)n_cta, P.status);
+            if (!grid_barrier_tp(P.barrier, g_tp.delta, g_tp.n, (P.bar_base + n_bar) * (unsigned)n_cta, P.status)) {
+                ok = false; /* uniform over the CTA */
+                break;
+            }
         }
-        if (tr && tid == 0) tr[3] = clock64();
+        if (MEGA_TR() && threadIdx.x == 0 && stage_type != MEGA_GEMV) MEGA_TR()[3] = clock64();
     }
     /* A wait gave up: the copies this CTA already started still land in its shared memory,
      * so it stays until they have (bounded), then leaves. */
-    if (!ok && tid == MEGA_ISSUER) {
-        for (unsigned q = ring.consumed; q < ring.issued; q++) {
-            uint64_t* bar = bars + (q % MEGA_SLOTS);
+    if (!ok && threadIdx.x == MEGA_ISSUER) {
+        for (unsigned q = consumed; q < g_ring.issued; q++) {
+            uint64_t* bar = ring_full(q % MEGA_SLOTS);
             const unsigned parity = (q / MEGA_SLOTS) & 1u;
             for (unsigned i = 0; i < PIPE_MBAR_TRIES && !mbar_try_wait(bar, parity); i++) {}
         }
     }
 }
+
+#undef MEGA_KINDS
+#undef MEGA_STBUF
+#undef MEGA_JOIN
+#undef MEGA_TR
 
 extern "C" void mega_layout(int x_bytes, MegaLayout* out) {
     out->x_bytes = (x_bytes + 255) & ~255;

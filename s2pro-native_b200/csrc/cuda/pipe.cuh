@@ -99,6 +99,9 @@ __device__ __forceinline__ bool flag_wait4(const uint4* p, unsigned tag, int* st
         if ((i & 63u) == 63u && status_peek(status) != PIPE_OK) return false;
     }
 }
+__device__ __forceinline__ bool flag_tags4(const uint4& q, unsigned tag) {
+    return ((q.x >> 16) == tag) & ((q.y >> 16) == tag) & ((q.z >> 16) == tag) & ((q.w >> 16) == tag);
+}
 /* the payload of a flagged word as f32 */
 __device__ __forceinline__ float flag_payload(uint32_t w) { return __uint_as_float(w << 16); }
 

@@ -853,7 +853,7 @@ static s2p_status mega_build(s2p_model* m) {
         e = cudaMemcpyAsync(m->d_mega_cmd_start, cmd_start, ((size_t)n_cta + 1) * sizeof(int), cudaMemcpyHostToDevice,
                             m->stream);
     if (e == cudaSuccess && s2p_env_is_one("S2P_TICK_TRACE")) {
-        const size_t tb = (size_t)n * (16 + (size_t)n_cta) * sizeof(unsigned long long);
+        const size_t tb = (size_t)n * (16 + 2 * (size_t)n_cta) * sizeof(unsigned long long);
         e = cudaMalloc((void**)&m->d_mega_trace, tb);
         if (e == cudaSuccess) e = cudaMemsetAsync(m->d_mega_trace, 0, tb, m->stream);
     }
@@ -1091,7 +1091,7 @@ s2p_status s2p_b200_model_tick_trace(s2p_model* m, uint64_t* out, int32_t* types
     S2P_CUDA_TRY(cudaMemcpy(out, m->d_mega_trace, (size_t)n * 16 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     if (getenv("S2P_TICK_TRACE_ALL") && max_stages >= m->mega_n_stages) /* probe: per-CTA finish stamps follow */
         S2P_CUDA_TRY(cudaMemcpy(out + (size_t)m->mega_n_stages * 16, m->d_mega_trace + (size_t)m->mega_n_stages * 16,
-                                (size_t)m->mega_n_stages * m->mega_ctas * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+                                (size_t)m->mega_n_stages * 2 * m->mega_ctas * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     if (types && m->mega_types) memcpy(types, m->mega_types, (size_t)n * sizeof(int32_t));
     return S2P_OK;
 }
