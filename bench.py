@@ -12,9 +12,13 @@ of the same tick (CUDA events on the model's stream around the graph launch).
 With N GPUs every rank runs an independent replica on its own sessions (the path
 shards by session, there is no data-path collective): weak scaling.
 
-The workload is BASELINE.json's batch-1 all-INT4 configuration: 36 + 4 layers,
+The headline workload is the batch-1 all-INT4 configuration: 36 + 4 layers,
 seeded random-init checkpoint (the real one is gated), 512-token uniform random
-prompt, temperature 0.8 / top-p 0.8 with a fixed seed.
+prompt, temperature 0.8 / top-p 0.8 with a fixed seed.  The same JSON line also
+carries the two other parts of the metric: `lockstep_b32` (32 sessions per GPU
+with 8192-token contexts, frames/s summed over the GPUs) and, with N >= 2 ranks,
+`tp` (one batch-1 session sharded over the N GPUs, with a frame-by-frame check
+against the single-GPU run of the same seed).
 """
 import argparse
 import ctypes as C
@@ -46,9 +50,11 @@ def algorithmic_bytes_per_frame(mode, n_slow=36):
     return n_slow * layer + 10 * 4 * layer + 9 * fast_head + 4097 * (2560 + 4)
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one k_tick_mega launch, from the ncu capture summarised in
-# profiles/k_tick_mega_int4_b1.md (36+4 layers, all-INT4, batch 1, ~540 cached positions)
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_tick_mega launch (36+4 layers, all-INT4, batch 1,
+# ~540 cached positions) from an ncu capture; the capture is named beside the figure because the figure
+# does not follow later kernel changes by itself
 NCU_TRAFFIC_TICK_MEGA_INT4 = 4426394112
+NCU_TRAFFIC_SOURCE = "ncu capture of k_tick_mega (dram__bytes_read.sum + dram__bytes_write.sum, one launch), kernel as of the capture's commit; see the k_tick_mega profile summary"
 
 
 def ncu_traffic_per_launch(mode, layers, batch, stats):
@@ -119,6 +125,7 @@ class Engine:
         self.m = C.c_void_p()
         capi.check(lib.s2p_model_load(ckpt.encode(), C.byref(opts), C.byref(self.m)), "s2p_model_load")
         self.sessions = []
+        self.record = None  # a list: tick() appends the first session's ten codes of every frame
 
     def save_prefix(self, ids):
         """Prefill `ids` in a scratch session and return its KV blob (device memory) for kv_load."""
@@ -156,6 +163,8 @@ class Engine:
     def tick(self):
         self.capi.check(self.L.s2p_model_batch_next_frame(self.m, self.arr, len(self.sessions), self.codes, self.eos),
                         "s2p_model_batch_next_frame")
+        if self.record is not None:
+            self.record.append(tuple(self.codes[:10]))
         return any(self.eos)
 
     def close(self):
@@ -196,31 +205,42 @@ def stage_trace_summary(lib, model, sm_mhz):
     return out
 
 
-def cpu_baseline(mode, seconds=12.0):
-    """CPU port of the hot loop (oracle/, exact reference order) on a bounded sample:
-    the four GEMVs of one backbone-shaped layer at batch 1, scaled to one frame."""
+def host_threads():
+    return len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+
+
+def cpu_baseline(mode, frames=5, layers=36):
+    """CPU port of the path (oracle/, exact reference order): whole frames of the full model - backbone
+    step, tied head, sampler, ten fast-AR passes - through the oracle's frame function, on all host
+    threads (set here, not inherited: a launcher may export OMP_NUM_THREADS=1).  The weights are synthetic
+    codes of the right shapes and storage forms (the load-time quantisers are not part of the path)."""
     import numpy as np
     from oracle import oracle_api
     lib = oracle_api.load()
-    rng = np.random.default_rng(0)
-    int4 = mode == "int4"
-    wbytes = 19456 * 2560 // (2 if int4 else 1)
-    w = rng.integers(0, 256, size=wbytes, dtype=np.uint8)
-    sc16 = np.full(19456 * (9728 // 32), 0x2C00, dtype=np.uint16)
-    sc32 = np.full(19456, 1e-3, dtype=np.float32)
-    x = oracle_api.f32_to_bf16(rng.standard_normal(9728).astype(np.float32))
-    y = np.zeros(19456, dtype=np.uint16)
-    lib.s2po_layer_gemv_sample(oracle_api.ptr(w), oracle_api.ptr(sc16), oracle_api.ptr(sc32), oracle_api.ptr(x), oracle_api.ptr(y), int(int4), 1)
-    reps, t0 = 0, time.time()
-    while time.time() - t0 < seconds:
-        lib.s2po_layer_gemv_sample(oracle_api.ptr(w), oracle_api.ptr(sc16), oracle_api.ptr(sc32), oracle_api.ptr(x), oracle_api.ptr(y), int(int4), 1)
-        reps += 1
-    per_layer_ms = (time.time() - t0) / reps * 1e3
-    layers_per_frame = 36 + 40 + (9 * 4096 * 2560 + 4097 * 2560) / WEIGHTS_PER_LAYER
-    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    return {"value": per_layer_ms * layers_per_frame, "unit": "ms/frame", "cores": cores, "kind": "port",
-            "sample": f"{reps} x the 4 GEMVs of one backbone-shaped layer ({'INT4 g32' if int4 else 'INT8'}, batch 1), "
-                      f"OpenMP over rows, scaled by {layers_per_frame:.2f} layer-equivalents per frame; attention, norms and sampler (<1% of the work) left out"}
+    threads = lib.s2po_set_threads(host_threads())
+    int4 = int(mode == "int4")
+    m = lib.s2po_model_new(2560, 32, 8, 9728, 155776, layers, 4, 4096, 10, 151678, 151645, 1, int4, int4, 1, 1, 256)
+    lib.s2po_model_fill_synthetic(m, 12345)
+    times, tries = [], 0
+    while len(times) < frames and tries < 4:
+        tries += 1
+        s = lib.s2po_session_new(m, 0.8, 0.8, 1.1, 16, 42 + tries)
+        ids = np.array([151700, 151701], dtype=np.int64)
+        lib.s2po_prefill(s, oracle_api.ptr(ids), len(ids), None)
+        codes = np.zeros(16, dtype=np.int32)
+        lib.s2po_next_frame(s, oracle_api.ptr(codes), None, None)  # first frame: no backbone step, not timed
+        while len(times) < frames:
+            t0 = time.perf_counter()
+            eos = lib.s2po_next_frame(s, oracle_api.ptr(codes), None, None)
+            if eos:
+                break
+            times.append((time.perf_counter() - t0) * 1e3)
+        lib.s2po_session_free(s)
+    lib.s2po_model_free(m)
+    return {"value": round(statistics.median(times), 2), "unit": "ms/frame", "cores": int(threads), "kind": "port",
+            "sample": f"{len(times)} whole frames (median) of the {layers}+4-layer model through the CPU port's frame function "
+                      f"({'all-INT4 g32' if int4 else 'INT8'} weights + INT8 KV, batch 1, 2-token context, OpenMP over output rows, "
+                      f"{threads} threads set explicitly); synthetic codes of the real shapes stand in for quantised weights"}
 
 
 def isolated_gemv_roofline(lib, torch, mode, peak_gbs):
@@ -268,6 +288,143 @@ def isolated_gemv_roofline(lib, torch, mode, peak_gbs):
     return out
 
 
+def workload_text(args, seed_used):
+    """The one description of the headline workload both arms print."""
+    return (f"dual-AR decode, all-{args.mode.upper()} weights + INT8 KV, {args.layers}+4 layers, batch {args.batch} per GPU, " +
+            (f"{args.prompt}-token prompt" if args.batch == 1 else f"prompts 256-2048 tokens after a shared {args.shared_prefix}-token KV prefix") +
+            f", T=0.8 top-p=0.8 seed {seed_used}")
+
+
+def config_block(args, seed_used, replicas, tp, ctx_len, eos_in_timed, arm):
+    return {"workload": workload_text(args, seed_used), "replicas": replicas, "tensor_parallel": tp, "ctx_len": ctx_len,
+            "l2": "weights per frame (4.4-7.8 GB) exceed the 126 MB L2: every frame streams from HBM",
+            "eos_in_timed_region": bool(eos_in_timed), "arm": arm}
+
+
+def tp_attach(lib, capi, eng, rank, world):
+    """Exchange the arena handles of all ranks and attach (before any session exists)."""
+    import torch
+    import torch.distributed as dist
+    handle = (C.c_ubyte * 64)()
+    capi.check(lib.s2p_b200_model_tp_export(eng.m, handle), "s2p_b200_model_tp_export")
+    mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
+    allh = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(allh, mine)
+    blob = (C.c_ubyte * (64 * world))(*[int(v) for t in allh for v in t.cpu().tolist()])
+    capi.check(lib.s2p_b200_model_tp_attach(eng.m, rank, world, blob), "s2p_b200_model_tp_attach")
+    dist.barrier()
+
+
+def max_over_ranks(values, world, device="cuda"):
+    """Element-wise maximum of a few floats over the ranks (a multi-GPU time is the slowest rank's)."""
+    if world <= 1:
+        return [float(v) for v in values]
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([float(v) for v in values], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def job_frames_per_s(world, sessions_per_gpu, ms_per_tick):
+    """Whole-job throughput of `world` GPUs that each advance `sessions_per_gpu` sessions one frame per tick."""
+    return world * sessions_per_gpu * 1e3 / ms_per_tick
+
+
+def timed_ticks(eng, lib, capi, steps, world, device="cuda"):
+    """`steps` ticks bracketed by a barrier and a device synchronisation on both sides: (wall ms per tick,
+    device ms per tick (mean), per-tick device ms of this rank, EOS seen); wall and device are maxima over the ranks."""
+    import torch
+    on_gpu = device == "cuda"
+    stats = capi.Stats()
+    dev_ms = []
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    if on_gpu:
+        torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    eos = False
+    for _ in range(steps):
+        eos = eng.tick() or eos
+        lib.s2p_b200_model_stats(eng.m, C.byref(stats))
+        dev_ms.append(stats.last_tick_device_ms)
+    if on_gpu:
+        torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) * 1e3 / steps
+    dev = sum(dev_ms) / len(dev_ms)
+    wall, dev = max_over_ranks([wall, dev], world, device)
+    return wall, dev, dev_ms, eos
+
+
+def lockstep_block(args, lib, capi, synth, ckpt, rank, world, peak):
+    """32 lockstep sessions per GPU with 8192-token contexts (data parallel over the ranks, no collective in the
+    data path).  One 8192-token context is prefilled in 2048-row slices, saved, and loaded into every session, which
+    then prefills a 16-token prompt of its own; every session attends over its own copy of the cache."""
+    import numpy as np
+    n, ctx_tokens, own = args.lockstep_sessions, args.lockstep_context, 16
+    steps = max(3, min(args.steps, args.lockstep_steps))
+    ctx_len = ((ctx_tokens + 1 + 3 + steps + 64 + 63) // 64) * 64
+    eng = Engine(lib, capi, ckpt, ctx_len, n + 1)
+    shared = ctx_tokens - own
+    blob = eng.save_prefix(synth.random_prompt(shared, 4242 + rank))
+    seed = args.seed + 7919 * rank
+    for attempt in range(4):
+        eng.open_sessions([synth.random_prompt(own, 1000 * rank + 50 * attempt + i) for i in range(n)], 0.8, 0.8, seed + 100 * attempt,
+                          (blob, shared))
+        hit = eng.tick()  # first frame: sampled from the prefill state, not captured
+        for _ in range(3):
+            hit = hit or eng.tick()
+        if not hit:
+            break
+        for sess in eng.sessions:
+            lib.s2p_session_destroy(sess)
+        eng.sessions = []
+    wall, dev, dev_ms, eos = timed_ticks(eng, lib, capi, steps, world)
+    stats = capi.Stats()
+    lib.s2p_b200_model_stats(eng.m, C.byref(stats))
+    kv_tokens = n * (ctx_tokens + 4 + steps // 2)
+    byts = algorithmic_bytes_per_frame(args.mode, args.layers) + stats.kv_bytes_per_token * kv_tokens
+    out = {"sessions_per_gpu": n, "n_gpus": world, "context_tokens": ctx_tokens, "ctx_len": ctx_len, "steps": steps, "warmup": 3,
+           "ms_per_tick": round(dev, 3), "ms_per_tick_e2e": round(wall, 3),
+           "frames_per_s": round(job_frames_per_s(world, n, wall), 1), "frames_per_s_device": round(job_frames_per_s(world, n, dev), 1),
+           "scaling": "weak", "eos_in_timed_region": bool(eos),
+           "tick": {"kernels": int(stats.last_tick_kernels), "graph": int(stats.last_tick_graph)},
+           "roofline": {"bound": "hbm", "bytes_per_tick": int(byts), "achieved": round(byts / (dev * 1e-3) / 1e9, 1), "peak": peak,
+                        "unit": "GB/s", "frac": round(byts / (dev * 1e-3) / 1e9 / peak, 4),
+                        "note": "weights once per tick + every session's INT8 KV at its context length, / device time of the tick"}}
+    del blob
+    eng.close()
+    return out
+
+
+def tp_block(args, lib, capi, synth, ckpt, rank, world, seed_used, ref_frames, n1_value):
+    """ONE batch-1 session sharded over the `world` GPUs (tensor parallel, strong scaling): same checkpoint,
+    prompt, seed and call sequence as rank 0's single-GPU engine of the headline measurement, whose frames
+    (`ref_frames`, rank 0 only) the sharded run must reproduce code for code."""
+    import torch.distributed as dist
+    ctx_len = max(4096, ((args.prompt + args.steps + args.warmup + 64 + 63) // 64) * 64)
+    eng = Engine(lib, capi, ckpt, ctx_len, 1)
+    tp_attach(lib, capi, eng, rank, world)
+    eng.record = []
+    eng.open_sessions([synth.random_prompt(args.prompt, 0)], 0.8, 0.8, seed_used)
+    eng.tick()
+    for _ in range(args.warmup):
+        eng.tick()
+    wall, dev, dev_ms, eos = timed_ticks(eng, lib, capi, args.steps, world)
+    stats = capi.Stats()
+    lib.s2p_b200_model_stats(eng.m, C.byref(stats))
+    same = None
+    if rank == 0 and ref_frames is not None:
+        k = min(len(ref_frames), len(eng.record))
+        same = f"{sum(1 for i in range(k) if ref_frames[i] == eng.record[i])}/{k}"
+    dist.barrier()  # no rank frees its arena while a peer's kernel may still store into it
+    eng.close()
+    return {"world": world, "ms_per_frame": round(dev, 4), "ms_per_frame_e2e": round(wall, 4), "steps": args.steps,
+            "speedup_vs_one_gpu": round(n1_value / dev, 3) if n1_value else None, "frames_identical": same,
+            "persistent": int(stats.last_tick_persistent), "scaling": "strong", "eos_in_timed_region": bool(eos)}
+
+
 def run_ours(args, rank, world):
     import numpy as np
     import torch
@@ -295,15 +452,9 @@ def run_ours(args, rank, world):
     who = 0 if tp else rank  # tensor-parallel ranks must issue identical calls: same prompt, same seed
     for attempt in range(8):  # a sampled EOS would end a session early: move to the next seed
         eng = Engine(lib, capi, ckpt, ctx_len, max(args.batch, 1))
-        if tp:  # exchange the arena handles and attach before any session exists
-            handle = (C.c_ubyte * 64)()
-            capi.check(lib.s2p_b200_model_tp_export(eng.m, handle), "s2p_b200_model_tp_export")
-            mine = torch.tensor(list(handle), dtype=torch.uint8, device="cuda")
-            allh = [torch.empty_like(mine) for _ in range(world)]
-            dist.all_gather(allh, mine)
-            blob = (C.c_ubyte * (64 * world))(*[int(v) for t in allh for v in t.cpu().tolist()])
-            capi.check(lib.s2p_b200_model_tp_attach(eng.m, rank, world, blob), "s2p_b200_model_tp_attach")
-            dist.barrier()
+        if tp:
+            tp_attach(lib, capi, eng, rank, world)
+        eng.record = []
         rng = np.random.default_rng(1000 * who + attempt)
         lens = [args.prompt] * args.batch if args.batch == 1 else list(rng.integers(256, 2049, size=args.batch))
         prompts = [synth.random_prompt(int(n), 100 * who + i) for i, n in enumerate(lens)]
@@ -323,75 +474,70 @@ def run_ours(args, rank, world):
     stats = capi.Stats()
     sampler = ClockSampler(local)
     sampler.start()
-    dev_ms = []
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
     if args.profile_region:
         torch.cuda.profiler.start()
-    t0 = time.perf_counter()
-    eos_in_timed = False
-    for _ in range(args.steps):
-        eos_in_timed = eng.tick() or eos_in_timed
-        lib.s2p_b200_model_stats(eng.m, C.byref(stats))
-        dev_ms.append(stats.last_tick_device_ms)
-    torch.cuda.synchronize()
-    wall_ms = (time.perf_counter() - t0) * 1e3
+    step_wall, step_dev, dev_ms, eos_in_timed = timed_ticks(eng, lib, capi, args.steps, world)
     if args.profile_region:
         torch.cuda.profiler.stop()
     sampler.stop_flag = True
     sampler.join(timeout=2)
     lib.s2p_b200_model_stats(eng.m, C.byref(stats))
-    step_wall = wall_ms / args.steps
-    step_dev = sum(dev_ms) / len(dev_ms)
-    if world > 1:
-        t = torch.tensor([step_wall, step_dev], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        step_wall, step_dev = float(t[0]), float(t[1])
     if tp:
         dist.barrier()
-    if rank != 0:
-        eng.close()
-        return None
+    frames_rank0 = list(eng.record)
     peaks, peak_kind = measured_peaks()
     peak = float(peaks["hbm_gbs"])
-    kv_tokens = sum(int(n) for n in lens) + args.batch * (1 + args.warmup + args.steps // 2)
-    if args.batch > 1:
-        kv_tokens += args.batch * args.shared_prefix
-    algo = algorithmic_bytes_per_frame(args.mode, args.layers)
-    traffic_model = algo + stats.kv_bytes_per_token * kv_tokens
-    achieved = algo / (step_dev * 1e-3) / 1e9
-    line = {
-        "metric": "decode ms/frame (B=%d)" % args.batch + (" TP=%d" % world if tp else ""), "value": round(step_dev, 4), "unit": "ms/frame",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_wall, 4),
-        "higher_is_better": False, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": args.mode,
-        "data": "synthetic (seeded random-init checkpoint, uniform random prompt)",
-        "config": {"workload": f"dual-AR decode, all-{args.mode.upper()} weights + INT8 KV, {args.layers}+4 layers, batch {args.batch} per GPU, " +
-                               (f"{args.prompt}-token prompt" if args.batch == 1 else f"prompts 256-2048 tokens after a shared {args.shared_prefix}-token KV prefix") + f", T=0.8 top-p=0.8 seed {seed_used}",
-                   "replicas": 1 if tp else world, "tensor_parallel": world if tp else 1, "ctx_len": ctx_len, "l2": "weights per frame (4.4-7.8 GB) exceed the 126 MB L2: every frame streams from HBM",
-                   "eos_in_timed_region": bool(eos_in_timed)},
-        "frames_per_s": round((1 if tp else world) * args.batch * 1e3 / step_wall, 1),
-        "e2e": {"value": round(step_wall, 4), "unit": "ms/frame", "h2d_bytes_per_step": int(stats.upload_bytes),
-                "d2h_bytes_per_step": int(stats.download_bytes)},
-        "gpu_launches": int(stats.last_tick_kernels) * args.steps,
-        "tick": {"kernels": int(stats.last_tick_kernels), "persistent": int(stats.last_tick_persistent),
-                 "fused": int(stats.last_tick_fused), "graph": int(stats.last_tick_graph),
-                 "device_ms_p50": round(statistics.median(dev_ms), 4), "device_ms_p95": round(sorted(dev_ms)[int(0.95 * (len(dev_ms) - 1))], 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "traffic": ncu_traffic_per_launch(args.mode, args.layers, args.batch, stats), "peak_source": peak_kind,
-                     "kernel": "k_tick_mega (one launch = one frame)" if stats.last_tick_persistent else "whole tick (per-stage launches)",
-                     "note": "algorithmic weight bytes per frame / device time of the tick, CUDA events on the model stream; "
-                             "roofline_kernels lists the stand-alone GEMV stage kernels of the non-persistent path",
-                     "algorithmic_bytes_per_frame": int(algo), "modelled_bytes_with_kv": int(traffic_model)},
-        "clocks": sampler.summary(),
-    }
-    if args.stage_trace:
-        line["stage_trace"] = stage_trace_summary(lib, eng.m, float(line["clocks"].get("sm_mhz") or 1965.0))
+    line = None
+    if rank == 0:
+        kv_tokens = sum(int(n) for n in lens) + args.batch * (1 + args.warmup + args.steps // 2)
+        if args.batch > 1:
+            kv_tokens += args.batch * args.shared_prefix
+        algo = algorithmic_bytes_per_frame(args.mode, args.layers)
+        traffic_model = algo + stats.kv_bytes_per_token * kv_tokens
+        achieved = algo / (step_dev * 1e-3) / 1e9
+        traffic = ncu_traffic_per_launch(args.mode, args.layers, args.batch, stats)
+        line = {
+            "metric": "decode ms/frame (B=%d)" % args.batch + (" TP=%d" % world if tp else ""), "value": round(step_dev, 4), "unit": "ms/frame",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(step_wall, 4),
+            "higher_is_better": False, "scaling": "strong" if tp else "weak", "vs_baseline": None, "dtype": args.mode,
+            "data": "synthetic (seeded random-init checkpoint, uniform random prompt)",
+            "config": config_block(args, seed_used, 1 if tp else world, world if tp else 1, ctx_len, eos_in_timed,
+                                   "this library (libs2pro_b200.so) through the C ABI"),
+            "frames_per_s": round((1 if tp else world) * args.batch * 1e3 / step_wall, 1),
+            "e2e": {"value": round(step_wall, 4), "unit": "ms/frame", "h2d_bytes_per_step": int(stats.upload_bytes),
+                    "d2h_bytes_per_step": int(stats.download_bytes)},
+            "gpu_launches": int(stats.last_tick_kernels) * args.steps,
+            "tick": {"kernels": int(stats.last_tick_kernels), "persistent": int(stats.last_tick_persistent),
+                     "fused": int(stats.last_tick_fused), "graph": int(stats.last_tick_graph),
+                     "device_ms_p50": round(statistics.median(dev_ms), 4), "device_ms_p95": round(sorted(dev_ms)[int(0.95 * (len(dev_ms) - 1))], 4)},
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "traffic": traffic, "traffic_source": NCU_TRAFFIC_SOURCE if traffic else None, "peak_source": peak_kind,
+                         "kernel": "k_tick_mega (one launch = one frame)" if stats.last_tick_persistent else "whole tick (per-stage launches)",
+                         "note": "algorithmic weight bytes per frame / device time of the tick, CUDA events on the model stream; "
+                                 "roofline_kernels lists the stand-alone GEMV stage kernels of the non-persistent path",
+                         "algorithmic_bytes_per_frame": int(algo), "modelled_bytes_with_kv": int(traffic_model)},
+            "clocks": sampler.summary(),
+        }
+        if args.stage_trace:
+            line["stage_trace"] = stage_trace_summary(lib, eng.m, float(line["clocks"].get("sm_mhz") or 1965.0))
     eng.close()
-    if not args.no_kernel_roofline:
-        line["roofline_kernels"] = isolated_gemv_roofline(lib, torch, args.mode, peak)
-    if not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(args.mode)
+    # the other two parts of the metric, measured in the same run and carried by the same line
+    if args.batch == 1 and not tp and not args.no_lockstep:
+        blk = lockstep_block(args, lib, capi, synth, ckpt, rank, world, peak)
+        if rank == 0:
+            line["lockstep_b32"] = blk
+    if args.batch == 1 and not tp and world > 1 and not args.no_tp_block:
+        blk = tp_block(args, lib, capi, synth, ckpt, rank, world, seed_used, frames_rank0 if rank == 0 else None,
+                       line["value"] if rank == 0 else None)
+        if rank == 0:
+            line["tp"] = blk
+    if rank != 0:
+        return None
+    if world == 1:  # bounded host-side legs only where no other GPU waits for them
+        if not args.no_kernel_roofline:
+            line["roofline_kernels"] = isolated_gemv_roofline(lib, torch, args.mode, peak)
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args.mode, layers=args.layers)
     return line
 
 
@@ -440,16 +586,17 @@ def run_reference(args, rank, world):
         step = (time.perf_counter() - t0) * 1e3 / args.steps
         eng.close()
         base.update({"value": round(step, 4), "ms_per_step": round(step, 4),
-                     "config": {"workload": f"dual-AR decode, all-{args.mode.upper()} weights + INT8 KV, {args.layers}+4 layers, batch {args.batch}, "
-                                            + (f"{args.prompt}-token prompt" if args.batch == 1 else f"prompts 256-2048 tokens after a shared {args.shared_prefix}-token KV prefix") + f", T=0.8 top-p=0.8 seed {seed_used}",
-                                "arm": "reference CUDA path rebuilt unchanged for sm_100a (oracle/_ref), same GPU, same API calls"},
+                     "config": config_block(args, seed_used, world, 1, 4096, False,
+                                            "reference CUDA path rebuilt unchanged for sm_100a (oracle/_ref), same GPU, same API calls"),
                      "cpu_baseline": {"value": round(step, 4), "unit": "ms/frame", "cores": 1, "kind": "reference",
                                       "sample": "the reference has no CPU decode path; this is its CUDA path on the GPU, one host thread issuing"},
-                     "e2e": {"value": round(step, 4), "unit": "ms/frame", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+                     "e2e": {"value": round(step, 4), "unit": "ms/frame", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                             "note": "the reference's tick uploads its own staging block and downloads its result block inside the "
+                                     "timed call; their sizes are private to that library, so none is declared here"}})
         return base
-    cb = cpu_baseline(args.mode)
+    cb = cpu_baseline(args.mode, layers=args.layers)
     base.update({"value": round(cb["value"], 2), "ms_per_step": round(cb["value"], 2),
-                 "config": {"workload": f"dual-AR decode, all-{args.mode.upper()}, batch 1", "arm": "CPU port of the hot loop (oracle/): the reference library is not built here"},
+                 "config": config_block(args, args.seed, world, 1, 4096, False, "CPU port of the path (oracle/): the reference library is not built here"),
                  "cpu_baseline": cb,
                  "e2e": {"value": round(cb["value"], 2), "unit": "ms/frame", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
     return base
@@ -474,6 +621,11 @@ def main():
     ap.add_argument("--no-kernel-roofline", action="store_true")
     ap.add_argument("--stage-trace", action="store_true",
                     help="batch 1: add the persistent kernel's per-stage clock stamps (CTA 0) of the last frame, summed per stage kind")
+    ap.add_argument("--no-lockstep", action="store_true", help="skip the lockstep_b32 block")
+    ap.add_argument("--no-tp-block", action="store_true", help="N > 1: skip the tp block")
+    ap.add_argument("--lockstep-sessions", type=int, default=32)
+    ap.add_argument("--lockstep-context", type=int, default=8192)
+    ap.add_argument("--lockstep-steps", type=int, default=20)
     ap.add_argument("--tp", action="store_true",
                     help="with N > 1 ranks: one batch-1 session sharded over the N GPUs (tensor parallel) instead of N replicas")
     args = ap.parse_args()
