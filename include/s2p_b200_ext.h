@@ -54,8 +54,14 @@ cudaStream_t s2p_b200_model_stream(s2p_model* m);
  * between them, store each stage's outputs into every rank's arena over NVLink and meet at a
  * barrier that spans the ranks.  Every row is still computed by one thread block with the
  * single-GPU arithmetic, so the frames are bit-identical to a single-GPU run.  Each kv head's
- * cache is kept current only on the rank that attends over it: KV blobs saved from a
- * tensor-parallel session are not portable.  Prefill is replicated on every rank. */
+ * cache is kept current only on the rank that attends over it.  Consequences, enforced with
+ * S2P_ERR_UNSUPPORTED and a message rather than left to produce wrong frames:
+ *  - s2p_session_kv_save is refused for a tensor-parallel session (the blob would be incomplete);
+ *  - a tick with decoding rows that cannot run as the persistent kernel is refused: more than one
+ *    session, or any tick after the persistent kernel was disabled because one of its bounded waits
+ *    gave up (that tick returned S2P_ERR_INTERNAL).  The single-GPU fallbacks of an unsharded model
+ *    do not exist here.
+ * Prefill is replicated on every rank. */
 #define S2P_B200_TP_HANDLE_BYTES 64
 s2p_status s2p_b200_model_tp_export(s2p_model* m, void* handle_out);
 s2p_status s2p_b200_model_tp_attach(s2p_model* m, int rank, int world, const void* handles);

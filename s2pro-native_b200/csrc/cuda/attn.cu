@@ -84,7 +84,8 @@ extern "C" s2p_status s2p_b200_attention_decode_noalloc(const s2p_bf16* q, const
     }
     /* The array's name is only a host-side handle; the kernel needs its device address.
      * It is looked up once per device, with that device current. */
-    static void* dev_addr[64] = {0};
+    static void* dev_addr[64] = {0}; /* filled without a lock: two host threads making their first call at once both look
+                                      * the same address up, which is harmless; they must not overlap their launches anyway */
     int dev = -1;
     S2P_CUDA_TRY(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return S2P_ERR_UNSUPPORTED;
@@ -102,9 +103,12 @@ extern "C" s2p_status s2p_b200_attention_decode_noalloc(const s2p_bf16* q, const
     a.out = reinterpret_cast<__nv_bfloat16*>(out);
     a.q_heads = q_heads; a.kv_heads = kv_heads; a.max_seq = max_seq; a.kv8 = 0; a.head_dim = head_dim;
     a.pos0 = pos; a.pos_row_step = 0;
-    a.kv.base0 = (void*)k_cache;
-    a.kv.k_off = 0;
-    a.kv.v_off = (size_t)((const char*)v_cache - (const char*)k_cache);
+    /* K and V may be separate allocations in either order: offsets from the lower of the two
+     * addresses, computed on integers, so that neither is negative */
+    const uintptr_t ka = (uintptr_t)k_cache, va = (uintptr_t)v_cache, lo = ka < va ? ka : va;
+    a.kv.base0 = (void*)lo;
+    a.kv.k_off = (size_t)(ka - lo);
+    a.kv.v_off = (size_t)(va - lo);
     a.part = reinterpret_cast<float*>(base);
     a.counters = counters;
     a.n_split_slots = NOALLOC_SLOTS;

@@ -201,13 +201,12 @@ __device__ __noinline__ bool gemv_stage_input(const MegaStage* sp) {
     auto load = [xsrc, ll, tag, status, &ok](int v) -> uint4 {
         if (!ll) return __ldcg(xsrc + v);
         uint4 a, b;
+        PipeDeadline dl;
         for (unsigned spin = 0;; spin++) {
             a = flag_ld4(xsrc + 2 * v);
             b = flag_ld4(xsrc + 2 * v + 1);
             if (flag_tags4(a, tag) & flag_tags4(b, tag)) break;
-            if (spin > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); ok = false; }
-            if ((spin & 63u) == 63u && status_peek(status) != PIPE_OK) ok = false;
-            if (!ok) return make_uint4(0, 0, 0, 0);
+            if (flag_wait_over(spin, dl, status)) { ok = false; return make_uint4(0, 0, 0, 0); }
         }
         return make_uint4((a.x & 0xFFFFu) | (a.y << 16), (a.z & 0xFFFFu) | (a.w << 16), (b.x & 0xFFFFu) | (b.y << 16),
                           (b.z & 0xFFFFu) | (b.w << 16));
@@ -226,6 +225,7 @@ __device__ __noinline__ bool gemv_stage_input(const MegaStage* sp) {
         uint32_t xw[MEGA_NORM_ELEMS];
 #pragma unroll
         for (int m = 0; m < MEGA_NORM_ELEMS; m++) gw[m] = m < ne ? __ldg(gain + tid + 256 * m) : (unsigned short)0;
+        PipeDeadline dl;
         for (unsigned spin = 0;; spin++) {
             bool here = true;
 #pragma unroll
@@ -233,9 +233,7 @@ __device__ __noinline__ bool gemv_stage_input(const MegaStage* sp) {
 #pragma unroll
             for (int m = 0; m < MEGA_NORM_ELEMS; m++) here &= (xw[m] >> 16) == tag;
             if (here) break;
-            if (spin > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); ok = false; }
-            if ((spin & 63u) == 63u && status_peek(status) != PIPE_OK) ok = false;
-            if (!ok) break;
+            if (flag_wait_over(spin, dl, status)) { ok = false; break; }
         }
         float ss = 0.f;
 #pragma unroll
@@ -880,7 +878,10 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) k_tick_mega(MegaParams P) {
         for (unsigned q = consumed; q < g_ring.issued; q++) {
             uint64_t* bar = ring_full(q % MEGA_SLOTS);
             const unsigned parity = (q / MEGA_SLOTS) & 1u;
-            for (unsigned i = 0; i < PIPE_MBAR_TRIES && !mbar_try_wait(bar, parity); i++) {}
+            PipeDeadline dl; /* these copies do land (nothing but memory is waited for): a fixed, generous limit, whatever
+                              * deadline the other waits were given */
+            for (unsigned i = 0; i < PIPE_MBAR_TRIES && !mbar_try_wait(bar, parity); i++)
+                if ((i & 63u) == 63u && dl.expired(2000000000ull)) break;
         }
     }
 }
@@ -900,6 +901,46 @@ extern "C" void mega_layout(int x_bytes, MegaLayout* out) {
 extern "C" int mega_max_local_rows(const MegaLayout* lay, int K) {
     const int fit = lay->part_bytes / ((K >> 9) * 128);
     return fit < 2 * GEMV_WARPS ? fit : 2 * GEMV_WARPS; /* the fold takes two rows per warp */
+}
+
+/* Test hooks for the bounded waits.  mega_set_wait_ns: the deadline of every wait of the persistent
+ * tick on the current device (default two seconds).  pipe_wait_probe: one small CTA waits on an mbarrier
+ * (which = 0) or a flagged word (which = 1) that nobody will ever signal, with a deadline of limit_ns;
+ * the wait gives up, the kernel ends normally, and the status code and the time the wait took come back.
+ * Nothing hangs or faults: this is how the give-up path is exercised. */
+extern "C" cudaError_t mega_set_wait_ns(unsigned long long ns) {
+    return cudaMemcpyToSymbol(c_pipe_wait_ns, &ns, sizeof(ns));
+}
+__global__ void k_wait_probe(int which, uint32_t* word, int* status, unsigned long long* elapsed) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_init_fence(); }
+    __syncthreads();
+    const unsigned long long t0 = pipe_now();
+    bool got;
+    if (which == 0) got = mbar_wait_bounded(&bar, 0u, status);
+    else { uint32_t w; got = flag_wait1(word, 0x1234u, status, w); }
+    if (threadIdx.x == 0) { elapsed[0] = pipe_now() - t0; elapsed[1] = got ? 1ull : 0ull; }
+}
+extern "C" cudaError_t pipe_wait_probe(int which, unsigned long long limit_ns, int* status_out, unsigned long long* elapsed_ns_out,
+                                       int* got_out) {
+    unsigned long long saved = 0, h[2] = {0, 0};
+    unsigned char* d = nullptr;
+    cudaError_t e = cudaMemcpyFromSymbol(&saved, c_pipe_wait_ns, sizeof(saved));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&d, 64);
+    if (e == cudaSuccess) e = cudaMemset(d, 0, 64);
+    if (e == cudaSuccess) e = mega_set_wait_ns(limit_ns);
+    if (e == cudaSuccess) {
+        k_wait_probe<<<1, 32>>>(which, reinterpret_cast<uint32_t*>(d), reinterpret_cast<int*>(d + 16),
+                                reinterpret_cast<unsigned long long*>(d + 32));
+        e = cudaDeviceSynchronize();
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(status_out, d + 16, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess) e = cudaMemcpy(h, d + 32, sizeof(h), cudaMemcpyDeviceToHost);
+    *elapsed_ns_out = h[0];
+    *got_out = (int)h[1];
+    const cudaError_t r = mega_set_wait_ns(saved ? saved : 2000000000ull);
+    if (d) cudaFree(d);
+    return e != cudaSuccess ? e : r;
 }
 
 /* host-side probe of the row partition (tests) */

@@ -133,6 +133,8 @@ cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, con
 /* h[M, N / 2] = silu(x · Wg^T) * (x · Wu^T) for W = [Wg | Wu] stacked along N (gate/up linear + SwiGLU in one launch) */
 cudaError_t skinny_gemm_tc_swiglu(const LinRef* lin, const void* x, int M, void* h, cudaStream_t st);
 cudaError_t skinny_status(int* out);
+cudaError_t skinny_reset(cudaStream_t st);            /* clears the status code and the arrival counters */
+cudaError_t skinny_set_wait_ns(unsigned long long ns); /* test hook: deadline of the kernel's bounded waits */
 cudaError_t skinny_setup(int max_rows); /* once per device, outside stream capture: scratch for split-K launches */
 /* the launch plan for a shape as 10 ints (padding, tiles, split tiles, pieces, threads, slab, ring depths, grid,
  * shared memory), 0 if the shape cannot be served; no CUDA call (CPU tests) */
@@ -255,6 +257,10 @@ void mega_layout(int x_bytes, MegaLayout* out);
 int mega_max_local_rows(const MegaLayout* lay, int K); /* rows of one chunk the fold and the partial buffer can take */
 void mega_geom_probe(int N, int swiglu, int rows_per_chunk, int cta, int n_cta, int out[4]);
 cudaError_t mega_setup(int* n_cta_out);   /* once per device: attribute + occupancy check; grid size */
+/* test hooks: the deadline of the persistent tick's bounded waits on the current device, and a one-CTA kernel
+ * that lets a wait nobody will satisfy run out (which: 0 mbarrier, 1 flagged word) */
+cudaError_t mega_set_wait_ns(unsigned long long ns);
+cudaError_t pipe_wait_probe(int which, unsigned long long limit_ns, int* status_out, unsigned long long* elapsed_ns_out, int* got_out);
 cudaError_t mega_launch(const MegaParams* p, int n_cta, cudaStream_t st);
 
 cudaError_t qkv_post(const QkvPostArgs* a, int rows, cudaStream_t st);

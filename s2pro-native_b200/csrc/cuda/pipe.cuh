@@ -1,8 +1,9 @@
 /* Primitives of the persistent decode-tick kernel: mbarrier + TMA bulk copies
- * into a shared-memory ring, and a grid-wide barrier.  Every wait is bounded:
- * after its iteration limit a wait records an error code in a global status
- * word and returns false; all other waits see the word and give up too, so the
- * kernel always runs to its normal exit and the host reads the status.
+ * into a shared-memory ring, and a grid-wide barrier.  Every wait is bounded by
+ * a deadline on the GPU-wide timer: past it a wait records an error code in a
+ * global status word and returns false; all other waits see the word and give
+ * up too, so the kernel always runs to its normal exit and the host reads the
+ * status.
  */
 #pragma once
 #include <stdint.h>
@@ -12,8 +13,29 @@ namespace s2p {
 
 enum PipeError { PIPE_OK = 0, PIPE_ERR_TMA_WAIT = 1, PIPE_ERR_GRID_BARRIER = 2, PIPE_ERR_FLAG_WAIT = 3 };
 
-constexpr unsigned PIPE_MBAR_TRIES = 1u << 20;   /* each try_wait already blocks for a hardware time slice */
-constexpr unsigned PIPE_GRID_SPINS = 1u << 23;   /* a few seconds of polling an L2 word */
+/* How long a wait may last before it gives up, in nanoseconds of the GPU-wide timer (read every 64
+ * polls).  Two seconds: far beyond anything a healthy run shows, short enough that a lost peer costs
+ * the GPU's other users nothing.  One copy per translation unit; a test lowers it to make a wait run
+ * out on purpose (nothing hangs or faults: the wait returns false and the kernel ends normally). */
+static __constant__ unsigned long long c_pipe_wait_ns = 2000000000ull;
+constexpr unsigned PIPE_MBAR_TRIES = 1u << 26;   /* backstops in polls, should the timer ever stand still */
+constexpr unsigned PIPE_GRID_SPINS = 1u << 26;
+
+__device__ __forceinline__ unsigned long long pipe_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+/* started at its first check, so that a wait that succeeds at once never reads the timer */
+struct PipeDeadline {
+    unsigned long long t0 = 0;
+    __device__ __forceinline__ bool expired(unsigned long long limit_ns) {
+        const unsigned long long now = pipe_now();
+        if (!t0) { t0 = now; return false; }
+        return now - t0 > limit_ns;
+    }
+    __device__ __forceinline__ bool expired() { return expired(c_pipe_wait_ns); }
+};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -51,9 +73,14 @@ __device__ __forceinline__ int status_peek(const int* status) { return *reinterp
 /* Wait for phase `parity` of an mbarrier; false (and status set) on time-out or when
  * another wait already failed. */
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, int* status) {
+    PipeDeadline dl;
+    const unsigned every = c_pipe_wait_ns < 1000ull ? 0u : 63u; /* a sub-microsecond deadline (tests) is looked at on every poll */
     for (unsigned i = 0; i < PIPE_MBAR_TRIES; i++) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && status_peek(status) != PIPE_OK) return false;
+        if ((i & every) == every) {
+            if (status_peek(status) != PIPE_OK) return false;
+            if (dl.expired()) break;
+        }
     }
     atomicCAS(status, PIPE_OK, PIPE_ERR_TMA_WAIT);
     return false;
@@ -67,7 +94,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
  * and no separate flag are involved.  Tags count stage instances modulo 65536; every
  * cell is rewritten at least once per frame (a few hundred stage instances), so a
  * stale word can never carry the expected tag. */
-constexpr unsigned PIPE_FLAG_SPINS = 1u << 23; /* a few seconds of polling: long enough for a peer GPU whose host was descheduled */
+constexpr unsigned PIPE_FLAG_SPINS = 1u << 26; /* backstop in polls; the limit is the deadline above */
 
 __device__ __forceinline__ uint32_t flag_word(__nv_bfloat16 v, unsigned tag) {
     return (uint32_t)__bfloat16_as_ushort(v) | (tag << 16);
@@ -83,20 +110,27 @@ __device__ __forceinline__ uint4 flag_ld4(const uint4* p) {
     return q;
 }
 /* wait for one word / four consecutive words to carry `tag`; false (status set) on time-out */
+/* one poll of a flag wait that did not find its words: true when the wait has to give up (status set) */
+__device__ __forceinline__ bool flag_wait_over(unsigned i, PipeDeadline& dl, int* status) {
+    if ((i & 63u) != 63u) return false;
+    if (status_peek(status) != PIPE_OK) return true;
+    if (i > PIPE_FLAG_SPINS || dl.expired()) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); return true; }
+    return false;
+}
 __device__ __forceinline__ bool flag_wait1(const uint32_t* p, unsigned tag, int* status, uint32_t& w) {
+    PipeDeadline dl;
     for (unsigned i = 0;; i++) {
         w = flag_ld1(p);
         if ((w >> 16) == tag) return true;
-        if (i > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); return false; }
-        if ((i & 63u) == 63u && status_peek(status) != PIPE_OK) return false;
+        if (flag_wait_over(i, dl, status)) return false;
     }
 }
 __device__ __forceinline__ bool flag_wait4(const uint4* p, unsigned tag, int* status, uint4& q) {
+    PipeDeadline dl;
     for (unsigned i = 0;; i++) {
         q = flag_ld4(p);
         if (((q.x >> 16) == tag) & ((q.y >> 16) == tag) & ((q.z >> 16) == tag) & ((q.w >> 16) == tag)) return true;
-        if (i > PIPE_FLAG_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_FLAG_WAIT); return false; }
-        if ((i & 63u) == 63u && status_peek(status) != PIPE_OK) return false;
+        if (flag_wait_over(i, dl, status)) return false;
     }
 }
 __device__ __forceinline__ bool flag_tags4(const uint4& q, unsigned tag) {
@@ -127,12 +161,15 @@ __device__ __forceinline__ bool grid_barrier_tp(unsigned* counter, const long lo
             asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(counter) : "memory");
         }
         unsigned spins = 0, seen;
+        PipeDeadline dl;
         for (;;) {
             if (n_peers > 0) asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
             else asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
             if ((int)(seen - target) >= 0) break;
-            if (++spins > PIPE_GRID_SPINS) { atomicCAS(status, PIPE_OK, PIPE_ERR_GRID_BARRIER); ok = 0; break; }
-            if ((spins & 255u) == 0u && status_peek(status) != PIPE_OK) { ok = 0; break; }
+            if ((++spins & 63u) == 0u) {
+                if (status_peek(status) != PIPE_OK) { ok = 0; break; }
+                if (spins > PIPE_GRID_SPINS || dl.expired()) { atomicCAS(status, PIPE_OK, PIPE_ERR_GRID_BARRIER); ok = 0; break; }
+            }
         }
         ok_tp = ok && status_peek(status) == PIPE_OK;
     }

@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         const uint32_t idesc = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(SK_BM >> 4) << 24);
         const uint64_t desc_a0 = sk_smem_desc(smem_u32(smem), SK_BM * 16, 128);
         const uint64_t desc_b0 = sk_smem_desc(smem_u32(stage_b0), (uint32_t)NB * 16, 128);
-        int s = 0;
+        int s = 0, issued = 0;
         unsigned full_parity = 0;
         for (int it = 0; it < nk; it++) {
             ok = mbar_wait_bounded(full + s, full_parity, status);
@@ -375,7 +375,18 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(done + s)) : "memory");
             }
             __syncwarp();
+            issued = it + 1;
             if (++s == NST) { s = 0; full_parity ^= 1u; }
+        }
+        if (!ok && issued > 0) {
+            /* giving up with MMAs in flight: they complete by themselves (nothing but the tensor core is
+             * waited for), and TMEM must not be freed under them.  Wait for the last commit with a fixed,
+             * generous limit, whatever deadline the other waits have. */
+            uint64_t* bar = done + ((issued - 1) % NST);
+            const unsigned parity = (unsigned)((issued - 1) / NST) & 1u;
+            PipeDeadline dl;
+            for (unsigned i = 0; i < PIPE_MBAR_TRIES && !mbar_try_wait(bar, parity); i++)
+                if ((i & 63u) == 63u && dl.expired(2000000000ull)) break;
         }
     }
     /* the last commit covers every MMA before it */
@@ -511,24 +522,40 @@ static float* g_partial[64];
 static unsigned* g_arrivals[64];
 static int g_partial_rows[64];
 
-/* once per device, outside stream capture: room for split-K launches with up to `max_rows` batch rows */
+/* Once per device, outside stream capture: room for split-K launches.  The scratch is sized for the largest batch
+ * the kernel serves and never freed or moved: captured graphs of any model hold its address.  All models and
+ * streams of a device share it (and the arrival counters), so batched ticks of two models must not overlap on
+ * the GPU - the library issues every tick of a process from one host thread, as the reference's scheduler does. */
 extern "C" cudaError_t skinny_setup(int max_rows) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64 || max_rows < 1) return cudaErrorInvalidValue;
-    if (g_partial_rows[dev] >= max_rows) return cudaSuccess;
-    if (g_partial[dev]) cudaFree(g_partial[dev]);
-    g_partial[dev] = nullptr;
-    g_partial_rows[dev] = 0;
-    if ((e = cudaMalloc((void**)&g_partial[dev], (size_t)SK_SCRATCH_FLOATS_PER_ROW * max_rows * sizeof(float))) != cudaSuccess) return e;
+    if (g_partial[dev]) return cudaSuccess;
+    const int rows = 256;
+    if ((e = cudaMalloc((void**)&g_partial[dev], (size_t)SK_SCRATCH_FLOATS_PER_ROW * rows * sizeof(float))) != cudaSuccess) return e;
     if (!g_arrivals[dev]) {
-        if ((e = cudaMalloc((void**)&g_arrivals[dev], 256 * sizeof(unsigned))) != cudaSuccess) return e;
-        if ((e = cudaMemset(g_arrivals[dev], 0, 256 * sizeof(unsigned))) != cudaSuccess) return e;
+        if ((e = cudaMalloc((void**)&g_arrivals[dev], SK_MAX_SPLIT_TILES * sizeof(unsigned))) != cudaSuccess) return e;
+        if ((e = cudaMemset(g_arrivals[dev], 0, SK_MAX_SPLIT_TILES * sizeof(unsigned))) != cudaSuccess) return e;
     }
-    g_partial_rows[dev] = max_rows;
+    g_partial_rows[dev] = rows;
     return cudaSuccess;
 }
+
+/* After a launch left a status code: clear it and the arrival counters (a CTA that gave up did not count itself in),
+ * in stream order, so that later launches start clean. */
+extern "C" cudaError_t skinny_reset(cudaStream_t st) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    void* sp = nullptr;
+    if ((e = cudaGetSymbolAddress(&sp, g_sk_status)) != cudaSuccess) return e;
+    if ((e = cudaMemsetAsync(sp, 0, sizeof(int), st)) != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && g_arrivals[dev])
+        e = cudaMemsetAsync(g_arrivals[dev], 0, SK_MAX_SPLIT_TILES * sizeof(unsigned), st);
+    return e;
+}
+extern "C" cudaError_t skinny_set_wait_ns(unsigned long long ns) { return cudaMemcpyToSymbol(c_pipe_wait_ns, &ns, sizeof(ns)); }
 
 /* shared memory of a launch: the converted stages, D slabs of raw activations, DW copy rounds of raw weights, barriers */
 template <int WK, int NT, int KCP> static size_t sk_fixed_bytes(int NB) {
@@ -613,11 +640,15 @@ template <int WK> static bool sk_plan(int N, int K, int M, int scratch_rows, int
 template <int WK, int NT, int KCP>
 static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, const SkPlan& p, int ffn, void* y, const void* resid,
                                 float* partial, unsigned* arrivals, cudaStream_t st) {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static bool attr_set[64] = {false}; /* the attribute belongs to the function on one device */
+    int dev = 0;
+    cudaError_t ed = cudaGetDevice(&dev);
+    if (ed != cudaSuccess) return ed;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_set[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
         if (e != cudaSuccess) return e;
-        attr_set = true;
+        attr_set[dev] = true;
     }
     k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)p.grid), NT + 32, (size_t)p.smem, st>>>(
         lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, p.lgNB, p.D, p.DW, p.S, p.KS, ffn, (__nv_bfloat16*)y,

@@ -224,8 +224,14 @@ static int tc_scales_ok(const s2p_linear* lin) {
     return g >= (lin->q_packed ? 32 : 16) && g <= 128 && !(g & (g - 1));
 }
 
+/* set once a launch of the tensor-core kernel gave up on a wait: batched linears take the exact-order
+ * kernel from then on, as with S2P_NO_TC=1 */
+static int g_tc_disabled = 0;
+void s2p_linear_tc_disable(void) { g_tc_disabled = 1; }
+
 /* 1 when M decode rows of this linear go to the tensor-core kernel */
 int s2p_linear_rows_on_tc(const s2p_linear* lin, int M) {
+    if (g_tc_disabled) return 0;
     const int K = lin->in_features;
     static int tc_min_rows = 0;
     if (!tc_min_rows) {

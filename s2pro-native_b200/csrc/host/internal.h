@@ -14,6 +14,10 @@
 int s2p_env_is_one(const char* name);
 s2p_status s2p_linear_gemv_rows(const s2p_linear* lin, const void* x_bf16, void* y_bf16, int M, cudaStream_t stream);
 int s2p_linear_rows_on_tc(const s2p_linear* lin, int M);
+void s2p_linear_tc_disable(void);
+/* what a tensor-parallel model may do (session.c) */
+s2p_status s2p_tp_guard_tick(int tp_world, int decoding_rows, int persistent_path);
+s2p_status s2p_tp_guard_kv_save(int tp_world);
 s2p_status s2p_linear_tc_add(const s2p_linear* lin, const void* x_bf16, void* y_inout_bf16, int M, cudaStream_t stream);
 s2p_status s2p_linear_tc_swiglu(const s2p_linear* lin, const void* x_bf16, void* h_bf16, int M, cudaStream_t stream);
 

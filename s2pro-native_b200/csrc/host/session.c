@@ -351,8 +351,22 @@ static s2p_status kv_blob_copy(s2p_session* s, void* blob, int n_tokens, int sav
     return S2P_OK;
 }
 
+/* What a tensor-parallel model may do.  Each kv head's cache is current only on the rank that attends
+ * over it, so a tick with decoding rows is served by the persistent kernel or not at all (the
+ * single-GPU paths would attend over heads this rank never wrote), and a cache blob saved here would
+ * be incomplete.  Returns S2P_OK or the status the caller hands back. */
+s2p_status s2p_tp_guard_tick(int tp_world, int decoding_rows, int persistent_path) {
+    if (tp_world > 1 && decoding_rows >= 1 && !persistent_path) return S2P_ERR_UNSUPPORTED;
+    return S2P_OK;
+}
+s2p_status s2p_tp_guard_kv_save(int tp_world) { return tp_world > 1 ? S2P_ERR_UNSUPPORTED : S2P_OK; }
+
 s2p_status s2p_session_kv_save(s2p_session* s, int n_tokens, void* blob_dev) {
     if (!s || !blob_dev || n_tokens <= 0 || n_tokens > s->kv_len) return S2P_ERR_INVALID;
+    if (s2p_tp_guard_kv_save(s->m->tp_world) != S2P_OK) {
+        fprintf(stderr, "[s2pro] kv_save: a tensor-parallel session's cache is spread over the ranks; not saved\n");
+        return S2P_ERR_UNSUPPORTED;
+    }
     return kv_blob_copy(s, blob_dev, n_tokens, 1);
 }
 
@@ -975,6 +989,11 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
     if (fused && bd == 1 && m->mega_ok && !m->mega_built && dump_dir() == NULL) S2P_TRY(mega_build(m));
     const int mega = fused && bd == 1 && m->mega_ok && m->mega_built && dump_dir() == NULL;
     const int steady = bd == nact && graphs && !mega; /* every row decoding: the launch sequence is frame-invariant */
+    if (s2p_tp_guard_tick(m->tp_world, bd, mega) != S2P_OK) {
+        fprintf(stderr, "[s2pro] tensor-parallel model: this tick (%d decoding rows%s) cannot run as the persistent kernel, and no "
+                        "other path sees the whole KV cache; not served\n", bd, m->mega_ok ? "" : ", persistent path disabled");
+        return S2P_ERR_UNSUPPORTED;
+    }
     m->tick_kernels = 0;
     if (mega) {
         S2P_CUDA_TRY(cudaEventRecord(m->ev0, st));
@@ -1014,8 +1033,13 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
     S2P_CUDA_TRY(cudaStreamSynchronize(st));
     if (mega && *m->h_mega_status != 0) {
         fprintf(stderr, "[s2pro] persistent tick kernel gave up on a bounded wait (code %d); the frame is lost and later "
-                        "ticks use per-stage launches\n", *m->h_mega_status);
+                        "ticks %s\n", *m->h_mega_status,
+                m->tp_world > 1 ? "of this tensor-parallel model are refused" : "use per-stage launches");
         m->mega_ok = 0; /* its barrier counters and tags are no longer in step */
+        /* CTAs that left the kernel early did not take part in the arrival counting of its last attention
+         * stage: the per-stage kernels that take over expect the counters at zero */
+        if (m->attn_ctr)
+            S2P_CUDA_TRY(cudaMemsetAsync(m->attn_ctr, 0, (size_t)m->max_sessions * S2P_SLOW_KV_HEADS * sizeof(unsigned int), st));
         return S2P_ERR_INTERNAL;
     }
     if (!mega && m->n_slow > 0 && m->mode == S2P_GEMM_INT8 && m->slow[0].wqkv.int8_ready &&
@@ -1024,7 +1048,16 @@ s2p_status s2p_model_batch_next_frame(s2p_model* m, s2p_session** sess, int n, i
         int sk = 0;
         S2P_CUDA_TRY(skinny_status(&sk));
         if (sk != 0) {
-            fprintf(stderr, "[s2pro] batched tensor-core linear gave up on a bounded wait (code %d); the frame is lost\n", sk);
+            fprintf(stderr, "[s2pro] batched tensor-core linear gave up on a bounded wait (code %d); the frame is lost and later "
+                            "batched ticks use the exact-order kernel\n", sk);
+            S2P_CUDA_TRY(skinny_reset(st));
+            s2p_linear_tc_disable();
+            for (int b = 0; b <= S2P_MAX_BATCH; b++) /* captured ticks hold launches of the kernel that is now off */
+                if (m->gready[b]) {
+                    cudaGraphExecDestroy(m->gexec[b]);
+                    m->gexec[b] = NULL;
+                    m->gready[b] = 0;
+                }
             return S2P_ERR_INTERNAL;
         }
     }

@@ -83,7 +83,19 @@ def main():
               "fused": (mine, load(mine, True, persistent=False)), "general": (mine, load(mine, False))}
     paths = ("persistent", "fused", "general")
     result = {"mode": mode, "n_slow": n_slow, "frames": frames, "runs": {}}
-    for temp, seed, tag in ((0.0, 0, "greedy"), (0.8, 42, "sampled")):
+    for temp, seed0, tag in ((0.0, 0, "greedy"), (0.8, 42, "sampled")):
+        # A random-weight model samples EOS now and then (one of 4097 candidates), which ends the session:
+        # take the first prompt / seed with which the reference produces every requested frame.
+        Lr, mr = models["ref"]
+        for attempt in range(8):
+            ids = synth.random_prompt(prompt_len, 7 + attempt)
+            seed = seed0 + attempt
+            s = session(Lr, mr, temp, seed)
+            prefill(Lr, s, ids)
+            probe, _ = run(Lr, s, frames)
+            Lr.s2p_session_destroy(s)
+            if probe[-1] is not None:
+                break
         res = {}
         for name, (L, m) in models.items():
             s = session(L, m, temp, seed)
@@ -97,7 +109,8 @@ def main():
                 assert L.s2p_b200_model_stats(m, C.byref(st)) == 0
                 res[name] += ((st.last_tick_persistent, st.last_tick_fused, st.last_tick_kernels, st.last_tick_device_ms),)
             L.s2p_session_destroy(s)
-        entry = {"frames_ref": len(res["ref"][0]), "eos": res["ref"][0][-1] is None}
+        entry = {"frames_ref": len([o for o in res["ref"][0] if o is not None]), "eos": res["ref"][0][-1] is None,
+                 "prompt_seed": 7 + attempt, "sampling_seed": seed}
         for name in paths:
             n_same = sum(1 for a, b in zip(res[name][0], res["ref"][0]) if a == b)
             entry[name] = {"kv_prefill_identical": bool(torch.equal(res[name][1], res["ref"][1])),

@@ -193,6 +193,12 @@ def test_split_k_decode_attention_batch_of_32(libs, kv8):
     _split_k_decode_attention(libs, kv8, lens, 3136, (8,))
 
 
+def test_split_k_decode_attention_8192_positions(libs):
+    """The long-context end of the data-parallel configuration: two rows with 8192 and 8000 cached
+    positions in an INT8 cache of 8256 slots (129 splits), with the worker counts the tick uses."""
+    _split_k_decode_attention(libs, 1, [8192, 8000], 8256, (8, 18))
+
+
 def _split_k_decode_attention(libs, kv8, lens, max_seq, workers_list):
     _, tl, ref = libs
     rows = len(lens)
@@ -458,3 +464,43 @@ def test_tick_begin_matches_reference_glue(libs):
     assert tl.tick_begin(C.byref(a), rows, None) == 0
     assert_same(x, x_ref, "tick_begin rows")
     assert int(keys.abs().sum()) == 0
+
+
+# the shapes of the decode tick's linears (N x K): wqkv, wo, gate_up, w2, the fast head, the tied-head slice, the EOS row
+MODEL_SHAPES = [(6144, 2560), (2560, 4096), (19456, 2560), (2560, 9728), (4096, 2560), (4097, 2560), (1, 2560)]
+
+
+@pytest.mark.parametrize("N,K", MODEL_SHAPES)
+def test_quantisers_pack_and_dequant_equal_reference(libs, N, K):
+    """Load-time conversion, bit for bit: per-channel INT8, g32 INT4 with and without the MSE clip search,
+    nibble packing, and the three dequantisers, against the reference's own kernels."""
+    mine, _, ref = libs
+    w = rnd(N, K, scale=0.02, seed=900 + N % 97)
+    w[0, : min(K, 64)] = 0  # an all-zero group (and, for N == 1, a partly zero row)
+    # per-channel INT8
+    q1 = torch.empty(N, K, dtype=torch.int8, device="cuda"); q2 = torch.empty_like(q1)
+    s1 = torch.empty(N, dtype=torch.float32, device="cuda"); s2 = torch.empty_like(s1)
+    assert mine.s2p_int8_quant(p(q1), p(s1), p(w), N, K, None) == 0
+    assert ref.s2p_int8_quant(p(q2), p(s2), p(w), N, K, None) == 0
+    assert_same(q1, q2, "int8 codes"); assert_same(s1, s2, "int8 row scales")
+    d1 = torch.empty(N, K, dtype=torch.bfloat16, device="cuda"); d2 = torch.empty_like(d1)
+    assert mine.s2p_int8_dequant(p(d1), p(q1), p(s1), N, K, None) == 0
+    assert ref.s2p_int8_dequant(p(d2), p(q2), p(s2), N, K, None) == 0
+    assert_same(d1, d2, "int8 dequant")
+    # g32 INT4, plain absmax and MSE clip search
+    for mse in (0, 1):
+        g1 = torch.empty(N, K, dtype=torch.int8, device="cuda"); g2 = torch.empty_like(g1)
+        h1 = torch.empty(N, K // 32, dtype=torch.float16, device="cuda"); h2 = torch.empty_like(h1)
+        assert mine.s2p_intq_quant(p(g1), p(h1), p(w), N, K, 32, 7, mse, None) == 0
+        assert ref.s2p_intq_quant(p(g2), p(h2), p(w), N, K, 32, 7, mse, None) == 0
+        assert_same(g1, g2, f"int4 codes mse={mse}"); assert_same(h1, h2, f"int4 group scales mse={mse}")
+    assert mine.s2p_intq_dequant(p(d1), p(g1), p(h1), N, K, 32, None) == 0
+    assert ref.s2p_intq_dequant(p(d2), p(g2), p(h2), N, K, 32, None) == 0
+    assert_same(d1, d2, "int4 container dequant")
+    k1 = torch.empty(N, K // 2, dtype=torch.uint8, device="cuda"); k2 = torch.empty_like(k1)
+    assert mine.s2p_int4_pack(p(k1), p(g1), N, K, None) == 0
+    assert ref.s2p_int4_pack(p(k2), p(g2), N, K, None) == 0
+    assert_same(k1, k2, "packed nibbles")
+    assert mine.s2p_int4p_dequant(p(d1), p(k1), p(h1), N, K, 32, None) == 0
+    assert ref.s2p_int4p_dequant(p(d2), p(k2), p(h2), N, K, 32, None) == 0
+    assert_same(d1, d2, "packed int4 dequant")

@@ -30,8 +30,8 @@ def check(res):
         for path in ("persistent", "fused", "general"):
             r = run[path]
             assert r["kv_prefill_identical"], f"{tag}/{path}: KV cache after prefill differs from the reference"
-            assert r["frames"] == run["frames_ref"], f"{tag}/{path}: frame count {r['frames']} vs {run['frames_ref']}"
-            assert r["frames_identical"] == run["frames_ref"], f"{tag}/{path}: {r['frames_identical']}/{run['frames_ref']} frames identical"
+            assert r["frames_identical"] == r["frames"] == run["frames_ref"] + int(run["eos"]), \
+                f"{tag}/{path}: {r['frames_identical']} of {r['frames']} frames identical, reference ran {run['frames_ref']}"
             assert r["kv_after_identical"], f"{tag}/{path}: KV cache after decode differs"
         if run["frames_ref"] > 1:
             # the three ways this library runs a batch-1 tick were really three ways
@@ -52,10 +52,12 @@ def test_two_layer_parity_config(mode):
 
 @pytest.mark.parametrize("mode", ["int4", "int8"])
 def test_full_model_200_frames(mode):
-    """BASELINE configurations 2 and 3: 36-layer backbone + 4-layer fast-AR, 512-token prompt,
+    """The full dual-AR model (INT8 and all-INT4): 36-layer backbone + 4-layer fast-AR, 512-token prompt,
     200 frames greedy and 200 frames seeded T=0.8/top-p=0.8; every code of every frame and the
-    KV cache bytes must equal the reference's."""
+    KV cache bytes must equal the reference's.  The prompt / seed is the first with which the reference
+    itself reaches frame 200 (a random-init model samples EOS now and then)."""
     res = run_worker(mode, 36, 200, prompt=512)
     check(res)
     for tag, run in res["runs"].items():
-        assert run["frames_ref"] >= 1
+        print(f"{mode}/{tag}: reference produced {run['frames_ref']} frames (prompt seed {run['prompt_seed']}, sampling seed {run['sampling_seed']})")
+        assert run["frames_ref"] == 200 and not run["eos"], f"{tag}: the reference stopped at frame {run['frames_ref']}"

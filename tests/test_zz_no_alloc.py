@@ -64,6 +64,56 @@ def test_noalloc_attention_twice_in_a_row(mine, testlib):
         assert diff <= 2e-2 and cos >= 0.9999, (call, diff, cos)
 
 
+def _regular(tl, q, k, v, pos, max_seq):
+    """The library's regular split-K decode attention with caller-allocated scratch, K and V as two bases."""
+    n_slots = (max_seq + 63) // 64
+    part = torch.empty(QH * n_slots * 130, dtype=torch.float32, device="cuda")
+    ctr = torch.zeros(KVH, dtype=torch.int32, device="cuda")
+    out = torch.zeros_like(q)
+    lo = min(k.data_ptr(), v.data_ptr())
+    a = AttnArgs()
+    a.q = q.data_ptr(); a.out = out.data_ptr(); a.q_heads = QH; a.kv_heads = KVH; a.max_seq = max_seq; a.kv8 = 0
+    a.head_dim = HD; a.pos0 = pos; a.pos_row_step = 0
+    a.kv.base0 = lo; a.kv.k_off = k.data_ptr() - lo; a.kv.v_off = v.data_ptr() - lo
+    a.part = part.data_ptr(); a.counters = ctr.data_ptr(); a.n_split_slots = n_slots; a.workers = 16
+    assert tl.attn_decode(C.byref(a), 1, None) == 0
+    torch.cuda.synchronize()
+    return out
+
+
+def test_noalloc_attention_separate_allocations_either_order(mine, testlib):
+    """K and V are two independent pointers of the entry point: separate allocations, V above K and V below K."""
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    tl = bind_internal(testlib)
+    max_seq, pos = 512, 300
+    a = rnd(KVH, max_seq, HD, seed=31); b = rnd(KVH, max_seq, HD, seed=32)
+    q = rnd(1, QH * HD, seed=33)
+    for k, v in ((a, b), (b, a)):  # one of the two orders has the value plane at the lower address
+        out = torch.zeros_like(q)
+        assert mine.s2p_b200_attention_decode_noalloc(p(q), p(k), p(v), p(out), QH, KVH, HD, pos, max_seq, None) == 0
+        torch.cuda.synchronize()
+        want = _regular(tl, q, k, v, pos, max_seq)
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16)), ("V below K" if v.data_ptr() < k.data_ptr() else "V above K")
+
+
+def test_noalloc_attention_at_the_size_limit(mine, testlib):
+    """The largest accepted call (8192 cached positions: the top split slot sits directly below the arrival
+    counters in the built-in array), then a short call that would see counters left non-zero."""
+    if not torch.cuda.is_available():
+        pytest.fail("CUDA device required for -m gpu tests")
+    tl = bind_internal(testlib)
+    max_seq = 8192
+    k = rnd(KVH, max_seq, HD, seed=41); v = rnd(KVH, max_seq, HD, seed=42)
+    q = rnd(1, QH * HD, seed=43)
+    for pos in (8191, 70):
+        out = torch.zeros_like(q)
+        assert mine.s2p_b200_attention_decode_noalloc(p(q), p(k), p(v), p(out), QH, KVH, HD, pos, max_seq, None) == 0
+        torch.cuda.synchronize()
+        want = _regular(tl, q, k, v, pos, max_seq)
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16)), f"pos {pos}"
+
+
 def test_noalloc_attention_rejects_oversize(mine):
     if not torch.cuda.is_available():
         pytest.fail("CUDA device required for -m gpu tests")
