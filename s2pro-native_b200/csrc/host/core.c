@@ -1,85 +1,120 @@
-/* Status strings and the device/pinned buffer helpers of the C ABI
- * (reference contracts: include/s2pro/status.h:23, include/s2pro/tensor.h:23-43;
- * reference behaviour: src/core/tensor.c:60-127 — host buffers are pinned so
- * stream copies are asynchronous, device buffers are plain cudaMalloc). */
+/* Status strings and the buffer helpers of the C ABI.
+ *
+ * Contract (include/s2pro/status.h:23, include/s2pro/tensor.h:23-43 of the reference): an
+ * s2p_tensor describes up to four dimensions of one element type and owns either device memory
+ * or pinned host memory; a freed or never-allocated descriptor is all zero.  Host buffers are
+ * pinned so that copies on a stream are asynchronous (the reference's choice too,
+ * src/core/tensor.c:60-127).
+ */
 #include <string.h>
 #include "s2p_b200_abi.h"
 
+/* ---- status --------------------------------------------------------------------------- */
+
 const char* s2p_status_str(s2p_status s) {
-    static const char* const names[] = {
-        "ok", "invalid argument", "cuda error", "i/o error", "out of memory",
-        "format/parse error", "invalid state", "unsupported",
-        "internal invariant violated", "capacity exhausted"};
-    const int i = -(int)s;
-    return (i >= 0 && i < 10) ? names[i] : "unknown status";
+    switch (s) {
+    case S2P_OK: return "ok";
+    case S2P_ERR_INVALID: return "invalid argument";
+    case S2P_ERR_CUDA: return "cuda error";
+    case S2P_ERR_IO: return "i/o error";
+    case S2P_ERR_OOM: return "out of memory";
+    case S2P_ERR_FORMAT: return "format/parse error";
+    case S2P_ERR_STATE: return "invalid state";
+    case S2P_ERR_UNSUPPORTED: return "unsupported";
+    case S2P_ERR_INTERNAL: return "internal invariant violated";
+    case S2P_ERR_FULL: return "capacity exhausted";
+    }
+    return "unknown status";
 }
 
+/* ---- element types ---------------------------------------------------------------------- */
+
 size_t s2p_dtype_size(s2p_dtype dt) {
-    static const unsigned char sz[] = {2, 4, 2, 1, 4, 8, 1};
-    return ((unsigned)dt < sizeof(sz)) ? sz[dt] : 0;
+    switch (dt) {
+    case S2P_DT_BF16: case S2P_DT_F16: return 2;
+    case S2P_DT_F32: case S2P_DT_I32: return 4;
+    case S2P_DT_I64: return 8;
+    case S2P_DT_I8: case S2P_DT_U8: return 1;
+    }
+    return 0;
 }
 
 int64_t s2p_tensor_numel(const s2p_tensor* t) {
     if (!t || t->ndim < 0 || t->ndim > 4) return 0;
     int64_t n = 1;
-    for (int i = 0; i < t->ndim; i++) n *= t->shape[i];
+    for (int d = 0; d < t->ndim; d++) n *= t->shape[d];
     return n;
 }
 
-static s2p_status describe(s2p_tensor* t, s2p_dtype dt, int ndim, const int64_t* shape) {
-    if (!t || !shape || ndim < 1 || ndim > 4) return S2P_ERR_INVALID;
-    const size_t esz = s2p_dtype_size(dt);
-    if (!esz) return S2P_ERR_INVALID;
-    int64_t numel = 1;
-    for (int i = 0; i < ndim; i++) {
-        if (shape[i] <= 0 || numel > INT64_MAX / shape[i]) return S2P_ERR_INVALID;
-        numel *= shape[i];
+/* ---- allocation --------------------------------------------------------------------------
+ * Both kinds of buffer go through one routine: the byte count is formed with checked
+ * multiplications (a shape that overflows is an invalid argument, not a small allocation), the
+ * memory is obtained, and only then is the caller's descriptor written - so a failed call
+ * leaves whatever the caller had there untouched except for the documented zeroing. */
+
+static int shape_bytes(s2p_dtype dt, int ndim, const int64_t* shape, size_t* bytes_out) {
+    size_t bytes = s2p_dtype_size(dt);
+    if (!bytes || !shape || ndim < 1 || ndim > 4) return 0;
+    for (int d = 0; d < ndim; d++) {
+        if (shape[d] <= 0) return 0;
+        if (__builtin_mul_overflow(bytes, (size_t)shape[d], &bytes)) return 0;
     }
-    if ((uint64_t)numel > SIZE_MAX / esz) return S2P_ERR_INVALID;
-    memset(t, 0, sizeof(*t));
-    t->dtype = dt;
-    t->ndim = ndim;
-    for (int i = 0; i < 4; i++) t->shape[i] = i < ndim ? shape[i] : 1;
-    t->bytes = (size_t)numel * esz;
-    return S2P_OK;
+    if (bytes > (size_t)INT64_MAX) return 0; /* the element count must fit the signed count the ABI reports */
+    *bytes_out = bytes;
+    return 1;
 }
 
-static s2p_status alloc_common(s2p_tensor* t, s2p_dtype dt, int ndim, const int64_t* shape, int dev) {
-    S2P_TRY(describe(t, dt, ndim, shape));
-    const cudaError_t e = dev ? cudaMalloc(&t->data, t->bytes) : cudaMallocHost(&t->data, t->bytes);
+static s2p_status tensor_alloc(s2p_tensor* t, s2p_dtype dt, int ndim, const int64_t* shape, int on_device) {
+    size_t bytes = 0;
+    if (!t || !shape_bytes(dt, ndim, shape, &bytes)) return S2P_ERR_INVALID;
+    void* mem = NULL;
+    const cudaError_t e = on_device ? cudaMalloc(&mem, bytes) : cudaMallocHost(&mem, bytes);
+    memset(t, 0, sizeof(*t));
     if (e != cudaSuccess) {
-        fprintf(stderr, "[s2pro] %s(%zu) failed: %s\n", dev ? "cudaMalloc" : "cudaMallocHost", t->bytes,
-                cudaGetErrorString(e));
-        t->data = NULL;
+        fprintf(stderr, "[s2pro] %s(%zu) failed: %s\n", on_device ? "cudaMalloc" : "cudaMallocHost", bytes, cudaGetErrorString(e));
         return e == cudaErrorMemoryAllocation ? S2P_ERR_OOM : S2P_ERR_CUDA;
     }
-    t->on_device = dev;
+    t->data = mem;
+    t->dtype = dt;
+    t->ndim = ndim;
+    t->bytes = bytes;
+    t->on_device = on_device;
+    for (int d = 0; d < 4; d++) t->shape[d] = d < ndim ? shape[d] : 1;
     return S2P_OK;
 }
 
 s2p_status s2p_tensor_device_alloc(s2p_tensor* t, s2p_dtype dt, int ndim, const int64_t* shape) {
-    return alloc_common(t, dt, ndim, shape, 1);
+    return tensor_alloc(t, dt, ndim, shape, 1);
 }
 s2p_status s2p_tensor_host_alloc(s2p_tensor* t, s2p_dtype dt, int ndim, const int64_t* shape) {
-    return alloc_common(t, dt, ndim, shape, 0);
-}
-
-s2p_status s2p_tensor_upload(s2p_tensor* dst, const void* src, size_t bytes, cudaStream_t stream) {
-    if (!dst || !dst->data || !dst->on_device || bytes > dst->bytes || (!src && bytes)) return S2P_ERR_INVALID;
-    if (bytes) S2P_CUDA_TRY(cudaMemcpyAsync(dst->data, src, bytes, cudaMemcpyHostToDevice, stream));
-    return S2P_OK;
-}
-s2p_status s2p_tensor_download(void* dst, const s2p_tensor* src, size_t bytes, cudaStream_t stream) {
-    if (!src || !src->data || !src->on_device || bytes > src->bytes || (!dst && bytes)) return S2P_ERR_INVALID;
-    if (bytes) S2P_CUDA_TRY(cudaMemcpyAsync(dst, src->data, bytes, cudaMemcpyDeviceToHost, stream));
-    return S2P_OK;
+    return tensor_alloc(t, dt, ndim, shape, 0);
 }
 
 void s2p_tensor_free(s2p_tensor* t) {
     if (!t) return;
-    if (t->data) {
-        const cudaError_t e = t->on_device ? cudaFree(t->data) : cudaFreeHost(t->data);
-        if (e != cudaSuccess) fprintf(stderr, "[s2pro] tensor free failed: %s\n", cudaGetErrorString(e));
-    }
+    void* mem = t->data;
+    const int on_device = t->on_device;
     memset(t, 0, sizeof(*t));
+    if (!mem) return;
+    const cudaError_t e = on_device ? cudaFree(mem) : cudaFreeHost(mem);
+    if (e != cudaSuccess) fprintf(stderr, "[s2pro] tensor free failed: %s\n", cudaGetErrorString(e));
+}
+
+/* ---- copies: a device tensor on one side, caller memory on the other, in stream order ------ */
+
+static s2p_status device_copy(const s2p_tensor* dev, void* dev_ptr_side, const void* other, size_t bytes, int to_device,
+                              cudaStream_t stream) {
+    if (!dev || !dev->data || !dev->on_device || bytes > dev->bytes) return S2P_ERR_INVALID;
+    if (!bytes) return S2P_OK;
+    if (!other) return S2P_ERR_INVALID;
+    if (to_device) S2P_CUDA_TRY(cudaMemcpyAsync(dev->data, other, bytes, cudaMemcpyHostToDevice, stream));
+    else S2P_CUDA_TRY(cudaMemcpyAsync(dev_ptr_side, dev->data, bytes, cudaMemcpyDeviceToHost, stream));
+    return S2P_OK;
+}
+
+s2p_status s2p_tensor_upload(s2p_tensor* dst, const void* src, size_t bytes, cudaStream_t stream) {
+    return device_copy(dst, NULL, src, bytes, 1, stream);
+}
+s2p_status s2p_tensor_download(void* dst, const s2p_tensor* src, size_t bytes, cudaStream_t stream) {
+    return device_copy(src, dst, dst, bytes, 0, stream);
 }
