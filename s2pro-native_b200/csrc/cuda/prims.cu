@@ -3,7 +3,7 @@
  * round-to-nearest steps where the reference forbids fma contraction, and the
  * reduction pairings its kernels fix (see common.cuh).
  *
- * Exported launchers: the eleven s2pk_* of the primitive contract
+ * Exported launchers: the ten s2pk_* of the primitive contract
  * (include/s2pro/kernels.h:20-70 of the reference).  The internal launchers in
  * namespace s2p serve the unfused decode tick and prefill (ops.h).
  */

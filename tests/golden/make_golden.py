@@ -18,7 +18,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("S2P_REFERENCE", "/root/reference")
+REF = os.environ.get("S2P_REFERENCE") or os.path.abspath(os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference"))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, HERE)
 from oracle import oracle_api  # noqa: E402
