@@ -35,13 +35,26 @@ s2p_status s2p_b200_model_stats(const s2p_model* m, s2p_b200_stats* out);
 
 /* Stage trace of the persistent tick kernel (no counterpart in the reference).  With
  * S2P_TICK_TRACE=1 in the environment at model load, CTA 0 of every persistent tick
- * stamps the SM clock at four points of each stage: stage entered, activation staged
- * (GEMV stages; 0 otherwise), own work done, grid barrier passed.  This call copies the
- * stamps of the most recent tick: out[4 * stage + point], types[stage] = stage kind
- * (0 frame start, 1 GEMV, 2 backbone attention, 3 fast-AR attention, 4 sampler, 5 frame
- * end).  *n_stages receives the stage count; at most max_stages are written.
- * S2P_ERR_STATE if tracing is off or no persistent tick has run. */
+ * records sixteen 64-bit words per stage; this call copies those of the most recent tick:
+ * out[16 * stage + w].  Words 0..3 are SM-clock stamps: stage entered, activation staged
+ * (GEMV stages; 0 otherwise), own work done, grid barrier passed (or stage left where
+ * the stage ends without one).  Words 4..7 are SM-clock sums of thread 0's streaming
+ * role (waiting for weight chunks, multiplying) and of fold warp 0 (waiting for
+ * partial sums, folding); words 8..15 are the SM clock at which each of the eight
+ * streaming warps was through.  types[stage] = stage kind (0 frame start, 1 GEMV,
+ * 2 backbone attention, 3 fast-AR attention, 4 sampler, 5 frame end).  *n_stages
+ * receives the stage count; at most max_stages stages are written.  S2P_ERR_STATE if
+ * tracing is off or no persistent tick has run. */
 s2p_status s2p_b200_model_tick_trace(s2p_model* m, uint64_t* out, int32_t* types, int max_stages, int* n_stages);
+/* Per-CTA stamps of the same tick, in nanoseconds of the GPU's global timer:
+ * fold_done_ns[stage * n_ctas + cta] = the CTA's last output of the stage was published
+ * (for stages without a GEMV: the stage body returned), staged_ns[...] = its
+ * activation vector of a GEMV stage was staged in shared memory (0 elsewhere).  The
+ * difference between the latest fold_done of stage s and a CTA's staged stamp of stage
+ * s+1 is the hand-off latency between two GEMV stages.  Both arrays must hold
+ * n_stages * n_ctas words (S2P_ERR_INVALID with the two counts filled in otherwise). */
+s2p_status s2p_b200_model_tick_trace_ctas(s2p_model* m, uint64_t* fold_done_ns, uint64_t* staged_ns, int max_stages, int max_ctas,
+                                          int* n_stages, int* n_ctas);
 /* The stream every tick of this model is issued on (for external event timing). */
 cudaStream_t s2p_b200_model_stream(s2p_model* m);
 

@@ -127,6 +127,7 @@ EXT_PROTOTYPES = {
     "s2p_b200_model_stats": (_I, [_P, C.POINTER(Stats)]),
     "s2p_b200_model_stream": (C.c_void_p, [_P]),
     "s2p_b200_model_tick_trace": (_I, [_P, _P, _P, _I, C.POINTER(C.c_int)]),
+    "s2p_b200_model_tick_trace_ctas": (_I, [_P, _P, _P, _I, _I, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "s2p_b200_model_tp_export": (_I, [_P, _P]),
     "s2p_b200_model_tp_attach": (_I, [_P, _I, _I, _P]),
     "s2p_b200_attention_decode_noalloc": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _S]),

@@ -1122,10 +1122,21 @@ s2p_status s2p_b200_model_tick_trace(s2p_model* m, uint64_t* out, int32_t* types
     const int n = m->mega_n_stages < max_stages ? m->mega_n_stages : max_stages;
     *n_stages = m->mega_n_stages;
     S2P_CUDA_TRY(cudaMemcpy(out, m->d_mega_trace, (size_t)n * 16 * sizeof(uint64_t), cudaMemcpyDeviceToHost));
-    if (getenv("S2P_TICK_TRACE_ALL") && max_stages >= m->mega_n_stages) /* probe: per-CTA finish stamps follow */
-        S2P_CUDA_TRY(cudaMemcpy(out + (size_t)m->mega_n_stages * 16, m->d_mega_trace + (size_t)m->mega_n_stages * 16,
-                                (size_t)m->mega_n_stages * 2 * m->mega_ctas * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     if (types && m->mega_types) memcpy(types, m->mega_types, (size_t)n * sizeof(int32_t));
+    return S2P_OK;
+}
+
+s2p_status s2p_b200_model_tick_trace_ctas(s2p_model* m, uint64_t* fold_done_ns, uint64_t* staged_ns, int max_stages, int max_ctas,
+                                          int* n_stages, int* n_ctas) {
+    if (!m || !fold_done_ns || !staged_ns || !n_stages || !n_ctas || max_stages < 0 || max_ctas < 0) return S2P_ERR_INVALID;
+    if (!m->d_mega_trace || !m->last_mega) return S2P_ERR_STATE;
+    *n_stages = m->mega_n_stages;
+    *n_ctas = m->mega_ctas;
+    if (max_stages < m->mega_n_stages || max_ctas < m->mega_ctas) return S2P_ERR_INVALID;
+    const size_t words = (size_t)m->mega_n_stages * m->mega_ctas;
+    const uint64_t* base = m->d_mega_trace + (size_t)m->mega_n_stages * 16;
+    S2P_CUDA_TRY(cudaMemcpy(fold_done_ns, base, words * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    S2P_CUDA_TRY(cudaMemcpy(staged_ns, base + words, words * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     return S2P_OK;
 }
 
