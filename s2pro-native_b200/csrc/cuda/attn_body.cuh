@@ -217,9 +217,9 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
                     for (int h = 0; h < HPT; h++) pp[h] = 0.f;
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
-                        const uint32_t w = kw[gi * 8 + e];
-                        const float k0 = (float)(int8_t)(w & 0xFFu), k1 = (float)(int8_t)((w >> 8) & 0xFFu);
-                        const float k2 = (float)(int8_t)((w >> 16) & 0xFFu), k3 = (float)(int8_t)(w >> 24);
+                        const uint32_t w = s8x4_bias(kw[gi * 8 + e]);
+                        const float k0 = s8_biased_to_f32<0>(w), k1 = s8_biased_to_f32<1>(w);
+                        const float k2 = s8_biased_to_f32<2>(w), k3 = s8_biased_to_f32<3>(w);
 #pragma unroll
                         for (int h = 0; h < HPT; h++) {
                             const float4 qv = reinterpret_cast<const float4*>(sq[gq + h])[gi * 8 + e];
@@ -270,7 +270,7 @@ __device__ void attn_decode_cta(const AttnArgs& a, const AttnPrep& pz, int row, 
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll 4
             for (int j = 0; j < cnt; j++) {
-                const float vf = KV8 ? (float)reinterpret_cast<const int8_t*>(vtile + j * TS)[dd]
+                const float vf = KV8 ? s8_to_f32(reinterpret_cast<const int8_t*>(vtile + j * TS)[dd])
                                      : bf2f(reinterpret_cast<const __nv_bfloat16*>(vtile + j * TS)[dd]);
                 const float4 wj = wv[j * 4];
                 a0 = __fmaf_rn(wj.x, vf, a0);

@@ -26,6 +26,15 @@ __device__ __forceinline__ float bf_bits_to_f32(uint32_t hi16) { return __uint_a
 /* the two bf16 of a 32-bit word (lower address first) */
 __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+/* Signed bytes to float without the conversion unit (which runs at a quarter of the arithmetic rate):
+ * the byte, offset to unsigned, is placed in the low mantissa bits of 2^23 and the offset subtracted;
+ * both steps are exact, so the value equals (float)(int8_t)b. */
+__device__ __forceinline__ uint32_t s8x4_bias(uint32_t w) { return w ^ 0x80808080u; }
+template <int I> __device__ __forceinline__ float s8_biased_to_f32(uint32_t biased_word) {
+    return __fsub_rn(__uint_as_float(__byte_perm(biased_word, 0x4B000000u, 0x7440 + I)), 8388736.0f);
+}
+/* one sign-extended byte: added to the bit pattern of 2^23 + 2^22, whose mantissa absorbs either sign */
+__device__ __forceinline__ float s8_to_f32(int v) { return __fsub_rn(__int_as_float(0x4B400000 + v), 12582912.0f); }
 __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ __nv_bfloat16 f2bf(float v) { return __float2bfloat16(v); } /* RNE */
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
