@@ -19,7 +19,7 @@
  * fused tick needs no separate launches for them.
  */
 #include "attn_body.cuh"
-#include "attn_warp.cuh"
+#include "attn_team.cuh"
 
 namespace s2p {
 
@@ -30,32 +30,33 @@ __global__ void __launch_bounds__(512) k_attn_decode(AttnArgs a, AttnPrep pz) {
     attn_decode_cta<KV8, PREP, HPT>(a, pz, blockIdx.x, blockIdx.y, blockIdx.z, gridDim.z, sm);
 }
 
-/* The warp-per-split kernel (attn_warp.cuh): lockstep batches on one GPU, no fused prologue. */
-template <bool KV8, int NW>
-static cudaError_t launch_attn_warp(const AttnArgs& a, dim3 grid, cudaStream_t st) {
+/* The kernel for lockstep batches on one GPU, no fused prologue: a team of two warps per split
+ * (attn_team.cuh). */
+template <bool KV8, int NT>
+static cudaError_t launch_attn_team(const AttnArgs& a, dim3 grid, cudaStream_t st) {
     static bool attr_set[64] = {false};
-    constexpr size_t smem = sizeof(AttnWarpSmem<KV8, NW>);
+    constexpr size_t smem = sizeof(AttnTeamSmem<KV8, NT>);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
-        e = cudaFuncSetAttribute(k_attn_decode_warp<KV8, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        e = cudaFuncSetAttribute(k_attn_decode_team<KV8, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    k_attn_decode_warp<KV8, NW><<<grid, NW * 32, smem, st>>>(a);
+    k_attn_decode_team<KV8, NT><<<grid, NT * 64, smem, st>>>(a);
     return cudaGetLastError();
 }
-constexpr int ATTN_WARPS_KV8 = 4, ATTN_WARPS_BF16 = 6;
-static bool attn_warp_serves(const AttnArgs& a, int rows) {
+constexpr int ATTN_TEAMS_KV8 = 4, ATTN_TEAMS_BF16 = 3; /* two CTAs per SM either way */
+static bool attn_team_serves(const AttnArgs& a, int rows) {
     if (rows < 2 || a.out_ll || a.n_out_peers > 0 || (a.max_seq & 1)) return false;
     if ((a.kv.k_off | a.kv.v_off) & 15u) return false;
     if (a.kv8 && ((a.kv.ks_off | a.kv.vs_off) & 15u)) return false;
     if (!a.kv.bases && (a.kv.row_stride & 15u)) return false;
     if (a.kv8 && !a.kv.sbases && (a.kv.srow_stride & 15u)) return false;
     /* the merge keeps two floats per (head, split) in the idle tiles */
-    const size_t tiles = a.kv8 ? sizeof(AttnWarpTile<true>) * ATTN_WARPS_KV8 : sizeof(AttnWarpTile<false>) * ATTN_WARPS_BF16;
+    const size_t tiles = a.kv8 ? sizeof(AttnTeamTile<true>) * ATTN_TEAMS_KV8 : sizeof(AttnTeamTile<false>) * ATTN_TEAMS_BF16;
     return (size_t)a.n_split_slots * 32 + 16 <= tiles;
 }
 
@@ -63,8 +64,8 @@ cudaError_t launch_attn_decode(const AttnArgs& a, const AttnPrep* prep, int rows
     if (rows <= 0) return cudaSuccess;
     if (a.q_heads != a.kv_heads * 4 || !a.part || !a.counters || a.workers < 1) return cudaErrorInvalidValue;
     dim3 grid((unsigned)rows, (unsigned)a.kv_heads, (unsigned)a.workers);
-    if (!prep && attn_warp_serves(a, rows))
-        return a.kv8 ? launch_attn_warp<true, ATTN_WARPS_KV8>(a, grid, st) : launch_attn_warp<false, ATTN_WARPS_BF16>(a, grid, st);
+    if (!prep && attn_team_serves(a, rows))
+        return a.kv8 ? launch_attn_team<true, ATTN_TEAMS_KV8>(a, grid, st) : launch_attn_team<false, ATTN_TEAMS_BF16>(a, grid, st);
     AttnPrep pz = {};
     /* one score chain per thread (HPT 1): sharing a key's conversion between the heads of a position
      * (HPT 2 or 4) measured slower on a lockstep batch of 32, fewer warps being busy in the score phase */
