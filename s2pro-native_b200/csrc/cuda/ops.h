@@ -132,6 +132,8 @@ cudaError_t gemv_setup_all(void); /* once per device, before any stream capture 
 cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, void* y, const void* resid, cudaStream_t st);
 /* h[M, N / 2] = silu(x · Wg^T) * (x · Wu^T) for W = [Wg | Wu] stacked along N (gate/up linear + SwiGLU in one launch) */
 cudaError_t skinny_gemm_tc_swiglu(const LinRef* lin, const void* x, int M, void* h, cudaStream_t st);
+/* any M >= 1: prompt slices in blocks of 256 rows, activations pre-tiled (not under stream capture) */
+cudaError_t skinny_prefill_tc(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st);
 cudaError_t skinny_status(int* out);
 cudaError_t skinny_reset(cudaStream_t st);            /* clears the status code and the arrival counters */
 cudaError_t skinny_set_wait_ns(unsigned long long ns); /* test hook: deadline of the kernel's bounded waits */

@@ -172,7 +172,11 @@ __device__ __forceinline__ void sk_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) 
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-template <int WK, int NT, int KCP>
+/* XT (prompt-sized inputs): the grid's y dimension walks blocks of 256 input rows, and the activations arrive
+ * already converted and tiled (k_xt_tile below: f16 units in the order a stage's B tile wants them, one contiguous
+ * block per (row block, slab)), so a stage's B tile is ONE bulk copy issued by one thread and the converting threads
+ * touch weights only: a weight slab is converted once per 256 input rows instead of once per launch of <= 128. */
+template <int WK, int NT, int KCP, bool XT>
 __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
                                                           int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
                                                           int lgNB, int D, int DW, int n_split_tiles, int KS, int ffn,
@@ -202,10 +206,20 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
     const int x_bytes = x_units * 16;
     unsigned char* stage_b0 = smem + NST * G::A_BYTES;
     unsigned char* xring = stage_b0 + NST * b_bytes;
-    unsigned char* wring = xring + D * x_bytes;
+    unsigned char* wring = xring + (XT ? 0 : D * x_bytes); /* XT: no ring of raw activations, B tiles land in the stages */
     uint64_t* full = reinterpret_cast<uint64_t*>(wring + DW * G::SUP_BYTES);
     uint64_t* done = full + NST;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + NST);
+    uint64_t* bx = done + NST; /* XT: the bulk copy of a stage's B tile has landed */
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bx + NST);
+    if (XT) { /* this CTA's block of 256 input rows */
+        const int tb = (int)blockIdx.y;
+        x = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const unsigned char*>(x) + (size_t)tb * (size_t)(K / KC) * (size_t)b_bytes);
+        y += (size_t)tb * 256 * (size_t)(ffn ? ffn : N);
+        if (resid) resid += (size_t)tb * 256 * (size_t)N;
+        if (partial) partial += (size_t)tb * (size_t)n_split_tiles * KS * 256 * SK_BM;
+        if (arrivals) arrivals += (size_t)tb * n_split_tiles;
+        M = min(256, M - tb * 256);
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool mma_warp = warp == NT / 32;
     const int n_tiles = ffn ? (ffn + 63) / 64 : (N + SK_BM - 1) / SK_BM, n_pieces = n_split_tiles * KS;
@@ -226,6 +240,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         for (int i = 0; i < NST; i++) {
             mbar_init(full + i, NT / 32);
             mbar_init(done + i, 1);
+            mbar_init(bx + i, 1);
         }
         mbar_init_fence();
     }
@@ -270,9 +285,10 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         };
         /* activations, slab by slab: unit c = [k / 8][batch row] sits in the slot where the B tile wants it;
          * c = tid + NT u; rows beyond the batch repeat row M - 1 (their columns are never stored) */
-        const int x_mine = tid < x_units ? (x_units + NT - 1 - tid) / NT : 0; /* units of this thread */
+        const int x_mine = (!XT && tid < x_units) ? (x_units + NT - 1 - tid) / NT : 0; /* units of this thread */
         const int x_step = (NT >> lgNB) * 8;                                   /* elements between them (NB <= NT) */
-        const __nv_bfloat16* xsrc = x + (size_t)min(tid & (NB - 1), M - 1) * K + (size_t)it_first * KC + (tid >> lgNB) * 8;
+        const __nv_bfloat16* xsrc = XT ? x : x + (size_t)min(tid & (NB - 1), M - 1) * K + (size_t)it_first * KC + (tid >> lgNB) * 8;
+        int b_issued = 0; /* XT, thread 0: bulk copies of B tiles issued */
         int x_wslot = 0, x_issued = 0;
         auto issue_x = [&]() {
             unsigned char* slot = xring + x_wslot + tid * 16;
@@ -310,6 +326,11 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
             const unsigned char* sup = wring + w_rslot;
             unsigned char* A = smem + s * G::A_BYTES;
             unsigned char* B = stage_b0 + s * b_bytes;
+            if (XT && tid == 0) { /* the stage is free (its MMAs have completed): its B tile travels while the weights are converted */
+                mbar_expect_tx(bx + s, (unsigned)b_bytes);
+                tma_load_1d(B, reinterpret_cast<const unsigned char*>(x) + (size_t)(it_first + it) * (size_t)b_bytes, (unsigned)b_bytes, bx + s);
+                b_issued++;
+            }
             /* weights: A[k / 8][row] */
 #pragma unroll
             for (int i = 0; i < G::NLD; i++) {
@@ -345,6 +366,15 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
           if (w_rslot == DW * G::SUP_BYTES) w_rslot = 0;
         }
         asm volatile("cp.async.wait_all;" ::: "memory"); /* nothing of this thread's is in flight past here */
+        if (XT && tid == 0 && b_issued > 0) {
+            /* nor a bulk copy: the last one issued has landed (at once on the normal path, where the MMA warp waited
+             * for it; after a give-up, with a fixed generous limit of its own) */
+            uint64_t* bar = bx + ((b_issued - 1) % NST);
+            const unsigned parity = (unsigned)((b_issued - 1) / NST) & 1u;
+            PipeDeadline dl;
+            for (unsigned i = 0; i < PIPE_MBAR_TRIES && !mbar_try_wait(bar, parity); i++)
+                if ((i & 63u) == 63u && dl.expired(2000000000ull)) break;
+        }
     } else {
         /* ---- the MMA warp (its lane 0 issues) */
         /* instruction descriptor: D f32, A and B f16, both K-major, N = NB, M = 128 */
@@ -355,6 +385,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         unsigned full_parity = 0;
         for (int it = 0; it < nk; it++) {
             ok = mbar_wait_bounded(full + s, full_parity, status);
+            if (ok && XT) ok = mbar_wait_bounded(bx + s, full_parity, status);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (lane == 0) {
@@ -559,7 +590,7 @@ extern "C" cudaError_t skinny_set_wait_ns(unsigned long long ns) { return cudaMe
 
 /* shared memory of a launch: the converted stages, D slabs of raw activations, DW copy rounds of raw weights, barriers */
 template <int WK, int NT, int KCP> static size_t sk_fixed_bytes(int NB) {
-    return SK_STAGES * ((size_t)SkGeom<WK, NT, KCP>::A_BYTES + (size_t)NB * SkGeom<WK, NT, KCP>::KC * 2) + 64;
+    return SK_STAGES * ((size_t)SkGeom<WK, NT, KCP>::A_BYTES + (size_t)NB * SkGeom<WK, NT, KCP>::KC * 2) + 128;
 }
 /* ring depths that fit `budget` bytes; false if not even the shallowest does */
 template <int WK, int NT, int KCP> static bool sk_depths(int NB, size_t budget, int min_d, int* D, int* DW) {
@@ -646,11 +677,11 @@ static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, const S
     if (ed != cudaSuccess) return ed;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    k_skinny_tc<WK, NT, KCP><<<dim3((unsigned)p.grid), NT + 32, (size_t)p.smem, st>>>(
+    k_skinny_tc<WK, NT, KCP, false><<<dim3((unsigned)p.grid), NT + 32, (size_t)p.smem, st>>>(
         lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, p.lgNB, p.D, p.DW, p.S, p.KS, ffn, (__nv_bfloat16*)y,
         (const __nv_bfloat16*)resid, partial, arrivals);
     return cudaGetLastError();
@@ -722,6 +753,102 @@ extern "C" cudaError_t skinny_gemm_tc(const LinRef* lin, const void* x, int M, v
 extern "C" cudaError_t skinny_gemm_tc_swiglu(const LinRef* lin, const void* x, int M, void* h, cudaStream_t st) {
     if (!lin || (lin->N & 1)) return cudaErrorInvalidValue;
     return sk_entry(lin, x, M, lin->N / 2, h, nullptr, st);
+}
+
+/* ---- prompt-sized inputs (prefill): M rows in blocks of 256 ------------------------------------------------
+ * What this replaces: the reference dequantises the whole layer to bf16 and calls cuBLAS for M > 16
+ * (src/sched/gemm.c:467-490; its own S2P_PREFILL_TC path, :458-466, serves M <= 128 only).  Here the packed
+ * weights go to the tensor cores directly: a CTA owns 128 weight rows x 256 input rows (one 256-column f32
+ * accumulator in TMEM), converts each weight slab once for the 256 rows, and receives the activations as
+ * bulk copies of pre-tiled f16 blocks written by k_xt_tile. */
+constexpr int XT_ROWS = 256;   /* input rows per CTA: the MMA's N */
+constexpr int XT_NT = 256, XT_KC = 64; /* kernel shape: three stages of 16 KB (A) + 32 KB (B) fit beside the weight ring */
+
+/* x [M, K] bf16 -> f16 units of 8 in the order stage B wants them: [row block][slab][k / 8 within the slab][row][8],
+ * each unit in the within-8 element order of the weight conversion (sk_x_unit); rows beyond M are zero */
+template <int WK>
+__global__ void k_xt_tile(const __nv_bfloat16* __restrict__ x, int M, int K, uint4* __restrict__ xt) {
+    const int k8n = K >> 3;
+    const size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; /* (row, k8): consecutive threads read one row */
+    const size_t rows_padded = (size_t)((M + XT_ROWS - 1) / XT_ROWS) * XT_ROWS;
+    if (u >= rows_padded * k8n) return;
+    const int row = (int)(u / k8n), k8 = (int)(u - (size_t)row * k8n);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (row < M) v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)row * K) + k8);
+    const int tb = row / XT_ROWS, r = row - tb * XT_ROWS;
+    const int slab = (k8 * 8) / XT_KC, k8_in = k8 - slab * (XT_KC / 8);
+    xt[(((size_t)tb * (K / XT_KC) + slab) * (XT_KC / 8) + k8_in) * XT_ROWS + r] = sk_x_unit<WK>(v);
+}
+
+static void* g_xt[64];
+static size_t g_xt_bytes[64];
+
+template <int WK>
+static cudaError_t xt_launch(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st) {
+    typedef SkGeom<WK, XT_NT, XT_KC> G;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    const int N = lin->N, K = lin->K;
+    const int tbs = (M + XT_ROWS - 1) / XT_ROWS, tiles = (N + SK_BM - 1) / SK_BM;
+    /* workspace for the tiled activations: grown on demand, never shrunk (not under stream capture: prefill is not captured) */
+    const size_t need = (size_t)tbs * XT_ROWS * K * 2;
+    if (need > g_xt_bytes[dev]) {
+        if ((e = cudaStreamSynchronize(st)) != cudaSuccess) return e;
+        if (g_xt[dev]) cudaFree(g_xt[dev]);
+        g_xt[dev] = nullptr; g_xt_bytes[dev] = 0;
+        if ((e = cudaMalloc(&g_xt[dev], need)) != cudaSuccess) return e;
+        g_xt_bytes[dev] = need;
+    }
+    /* split K where tiles x row blocks leave most SMs idle (short prompts, matrices of few rows) */
+    int S = 0, KS = 1;
+    if (g_partial_rows[dev] >= XT_ROWS && tiles * tbs * 2 <= 148) {
+        int max_ks = K / SK_SUPER_K;
+        if (max_ks > SK_MAX_SPLIT) max_ks = SK_MAX_SPLIT;
+        KS = 148 / (tiles * tbs) < max_ks ? 148 / (tiles * tbs) : max_ks;
+        const size_t cap = (size_t)SK_SCRATCH_FLOATS_PER_ROW * g_partial_rows[dev];
+        while (KS > 1 && (size_t)tiles * KS * XT_ROWS * SK_BM * tbs > cap) KS--;
+        if (KS > 1 && tiles * tbs <= SK_MAX_SPLIT_TILES) S = tiles; else KS = 1;
+    }
+    const int grid_x = tiles - S + S * KS;
+    int DW = 3;
+    size_t smem = 0;
+    for (; DW >= 2; DW--) {
+        smem = sk_fixed_bytes<WK, XT_NT, XT_KC>(XT_ROWS) + (size_t)DW * G::SUP_BYTES;
+        if (smem <= SK_SMEM_ONE) break;
+    }
+    if (DW < 2) return cudaErrorInvalidValue;
+    int D = G::SPS * (DW - 1) + 1;
+    if (D > SK_MAX_DEPTH) D = SK_MAX_DEPTH;
+    static bool attr_set[64] = {false};
+    if (!attr_set[dev]) {
+        if ((e = cudaFuncSetAttribute(k_skinny_tc<WK, XT_NT, XT_KC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE)) != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    const size_t units = (size_t)tbs * XT_ROWS * (K >> 3);
+    k_xt_tile<WK><<<(unsigned)((units + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, M, K, (uint4*)g_xt[dev]);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    k_skinny_tc<WK, XT_NT, XT_KC, true><<<dim3((unsigned)grid_x, (unsigned)tbs), XT_NT + 32, smem, st>>>(
+        lin->w, lin->scales, N, K, lin->gshift, (const __nv_bfloat16*)g_xt[dev], M, 8, D, DW, S, KS, 0, (__nv_bfloat16*)y, nullptr,
+        S ? g_partial[dev] : nullptr, S ? g_arrivals[dev] : nullptr);
+    return cudaGetLastError();
+}
+
+/* y[M, N] (bf16) = x[M, K] (bf16) · W^T for any M >= 1 (prompt slices).  Same constraints on the weights as
+ * skinny_gemm_tc.  Not for use under stream capture (the workspace may be allocated here). */
+extern "C" cudaError_t skinny_prefill_tc(const LinRef* lin, const void* x, int M, void* y, cudaStream_t st) {
+    if (!lin || !x || !y || M < 1 || lin->K % SK_SUPER_K) return cudaErrorInvalidValue;
+    if (((uintptr_t)x | (uintptr_t)lin->w) & 15) return cudaErrorInvalidValue;
+    if (lin->kind != WK_INT8_CH)
+        if (lin->gshift < 4 || lin->gshift > 7 || ((uintptr_t)lin->scales & 15)) return cudaErrorInvalidValue;
+    if (lin->kind == WK_INT4_PACK && lin->gshift < 5) return cudaErrorInvalidValue;
+    switch (lin->kind) {
+    case WK_INT8_CH: return xt_launch<WK_INT8_CH>(lin, x, M, y, st);
+    case WK_INT8_GRP: return xt_launch<WK_INT8_GRP>(lin, x, M, y, st);
+    case WK_INT4_PACK: return xt_launch<WK_INT4_PACK>(lin, x, M, y, st);
+    }
+    return cudaErrorInvalidValue;
 }
 
 /* status word of the launches so far on the current device (0 = no wait ever gave up); synchronises */

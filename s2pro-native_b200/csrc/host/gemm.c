@@ -307,6 +307,19 @@ s2p_status s2p_linear_forward(const s2p_linear* lin, const void* x_bf16, void* y
     const int N = lin->out_features, K = lin->in_features;
     if (mode == S2P_GEMM_INT8 && lin->int8_ready) {
         if (M <= S2P_INT8_GEMV_MAX_M) return s2p_linear_gemv_rows(lin, x_bf16, y_bf16, M, stream);
+        /* S2P_PREFILL_TC=1 (the reference's switch, src/sched/gemm.c:458-466, off by default there and here
+         * because the summation order differs from cuBLAS): prompt slices of any length go to the tensor
+         * cores straight from the quantised weights, no bf16 copy of the layer is written or read. */
+        if (s2p_env_is_one("S2P_PREFILL_TC") && !g_tc_disabled && K % 256 == 0 && tc_scales_ok(lin)) {
+            LinRef lr;
+            s2p_lin_ref(lin, &lr);
+            const cudaError_t ce = skinny_prefill_tc(&lr, x_bf16, M, y_bf16, stream);
+            if (ce != cudaSuccess) {
+                fprintf(stderr, "[s2pro] tensor-core prefill linear (M=%d,N=%d,K=%d): %s\n", M, N, K, cudaGetErrorString(ce));
+                return S2P_ERR_CUDA;
+            }
+            return S2P_OK;
+        }
         /* prefill-sized M: dequantise the whole layer, then the library GEMM; the lock
          * spans both so a concurrent caller cannot resize the scratch underneath */
         pthread_mutex_lock(&G.mu);

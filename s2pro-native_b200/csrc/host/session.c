@@ -316,6 +316,18 @@ s2p_status s2p_session_prefill(s2p_session* s, const int64_t* ids, const uint8_t
                           S2P_DIM, S2P_NORM_EPS, st));
     dump_bf16("backbone_final_norm", s->pending_hidden.data, S2P_DIM, st);
     S2P_CUDA_TRY(cudaStreamSynchronize(st));
+    if (n_ids > S2P_INT8_GEMV_MAX_M && m->mode == S2P_GEMM_INT8 && s2p_env_is_one("S2P_PREFILL_TC")) {
+        /* the slice's linears ran on the tensor-core kernel: a bounded wait that gave up inside it left a code */
+        int sk = 0;
+        S2P_CUDA_TRY(skinny_status(&sk));
+        if (sk != 0) {
+            fprintf(stderr, "[s2pro] tensor-core prefill linear gave up on a bounded wait (code %d); the slice is lost and later "
+                            "linears use the other kernels\n", sk);
+            S2P_CUDA_TRY(skinny_reset(st));
+            s2p_linear_tc_disable();
+            return S2P_ERR_INTERNAL;
+        }
+    }
     s->kv_len = pos0 + n_ids;
     s->state = SESS_PREFILLED;
     return S2P_OK;
@@ -1134,7 +1146,7 @@ s2p_status s2p_b200_model_tick_trace_ctas(s2p_model* m, uint64_t* fold_done_ns, 
     *n_ctas = m->mega_ctas;
     if (max_stages < m->mega_n_stages || max_ctas < m->mega_ctas) return S2P_ERR_INVALID;
     const size_t words = (size_t)m->mega_n_stages * m->mega_ctas;
-    const uint64_t* base = m->d_mega_trace + (size_t)m->mega_n_stages * 16;
+    const uint64_t* base = (const uint64_t*)m->d_mega_trace + (size_t)m->mega_n_stages * 16;
     S2P_CUDA_TRY(cudaMemcpy(fold_done_ns, base, words * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     S2P_CUDA_TRY(cudaMemcpy(staged_ns, base + words, words * sizeof(uint64_t), cudaMemcpyDeviceToHost));
     return S2P_OK;

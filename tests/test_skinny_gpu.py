@@ -118,3 +118,40 @@ def test_fused_swiglu_equals_linear_then_swiglu(mine, testlib, kind, M, ffn, K):
         assert testlib.skinny_gemm_tc_swiglu(C.byref(lin), p(x), M, p(got2), None) == 0
         torch.cuda.synchronize()
         assert torch.equal(got2.view(torch.int16), got.view(torch.int16))
+
+
+@pytest.mark.parametrize("kind", [2, 0, 1])
+@pytest.mark.parametrize("M,N,K", [(300, 6144, 2560), (512, 2560, 4096), (1000, 19456, 2560), (40, 4097, 2560), (257, 2560, 9728), (2048, 384, 512)])
+def test_prompt_sized_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
+    """The prefill form of the tensor-core linear: any number of rows in blocks of 256, activations
+    pre-tiled in f16 and brought in by bulk copies, a weight slab converted once per block."""
+    dev()
+    testlib.skinny_prefill_tc.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    testlib.skinny_status.argtypes = [C.POINTER(C.c_int)]
+    testlib.skinny_setup.argtypes = [C.c_int]
+    w, s = _quantised(mine, N, K, kind, seed=21 + kind)
+    x = rnd(M, K, seed=6)
+    y_exact = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    exact(mine, kind, y_exact, x, w, s, M, N, K)
+    lin = LinRef(kind, w.data_ptr(), s.data_ptr(), N, K, 0 if kind == 0 else 5)
+    assert testlib.skinny_setup(256) == 0  # split-K scratch: short prompts on matrices of few rows use it
+    y = torch.full((M + 1, N), float("nan"), dtype=torch.bfloat16, device="cuda")  # one guard row behind the output
+    assert testlib.skinny_prefill_tc(C.byref(lin), p(x), M, p(y), None) == 0
+    torch.cuda.synchronize()
+    st = C.c_int(-1)
+    assert testlib.skinny_status(C.byref(st)) == 0 and st.value == 0, "a bounded wait inside the kernel gave up"
+    assert bool(torch.isnan(y[M].float()).all()), "wrote behind the last row"
+    a, b = y[:M].float(), y_exact.float()
+    assert torch.isfinite(a).all()
+    scale = float(b.abs().max())
+    diff = (a - b).abs()
+    mag = torch.maximum(a.abs(), b.abs()).clamp_min(2.0 ** -20)
+    step = torch.exp2(torch.floor(torch.log2(mag)) - 7)
+    assert bool((diff <= step + 2e-3 * scale).all()), f"max diff {float(diff.max())} at scale {scale}"
+    assert float((diff == 0).float().mean()) >= 0.8
+    cos = torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0)
+    assert float(cos) >= 0.99999
+    y2 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    assert testlib.skinny_prefill_tc(C.byref(lin), p(x), M, p(y2), None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y2.view(torch.int16), y[:M].view(torch.int16)), "not reproducible run to run"

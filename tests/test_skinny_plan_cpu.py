@@ -41,7 +41,7 @@ def stage_and_ring_bytes(kind, p):
     nld = upr * 128 // nt
     ncp = nld * (256 // kc)
     sup = ncp * nt * 16 + (0 if kind == 0 else ncp * nt * 4)
-    return 3 * (128 * kc * 2 + NB * kc * 2) + 64 + p["D"] * NB * kc * 2 + p["DW"] * sup
+    return 3 * (128 * kc * 2 + NB * kc * 2) + 128 + p["D"] * NB * kc * 2 + p["DW"] * sup
 
 
 @pytest.mark.parametrize("shape", [1, 0, 2])
