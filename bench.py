@@ -18,7 +18,10 @@ prompt, temperature 0.8 / top-p 0.8 with a fixed seed.  The same JSON line also
 carries the two other parts of the metric: `lockstep_b32` (32 sessions per GPU
 with 8192-token contexts, frames/s summed over the GPUs) and, with N >= 2 ranks,
 `tp` (one batch-1 session sharded over the N GPUs, with a frame-by-frame check
-against the single-GPU run of the same seed).
+against the single-GPU run of the same seed).  At N = 1 a `prefill` block times
+s2p_session_prefill of the headline prompt through both routes of its linears
+(dequantise + cuBLAS, the default; tensor cores from the quantised weights,
+S2P_PREFILL_TC=1); the reference arm reports its own.
 """
 import argparse
 import ctypes as C
@@ -398,6 +401,32 @@ def lockstep_block(args, lib, capi, synth, ckpt, rank, world, peak):
     return out
 
 
+def prefill_block(lib, capi, synth, ckpt, tokens, routes):
+    """Wall time of s2p_session_prefill (it returns after a stream sync) for one `tokens`-token prompt, best of
+    three fresh sessions per route.  routes: {"name": value of S2P_PREFILL_TC}."""
+    import torch
+    eng = Engine(lib, capi, ckpt, 4096, 1)
+    ids = synth.random_prompt(tokens, 31)
+    out = {"tokens": tokens, "unit": "ms", "note": "host wall time of the call, pageable ids in, KV cache and first-frame state out"}
+    for name, tc in routes.items():
+        os.environ["S2P_PREFILL_TC"] = tc
+        best = None
+        for _ in range(3):
+            cfg = lib.s2p_sampling_defaults()
+            sess = C.c_void_p()
+            capi.check(lib.s2p_session_create(eng.m, C.byref(cfg), C.byref(sess)), "s2p_session_create")
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            capi.check(lib.s2p_session_prefill(sess, ids.ctypes.data_as(C.c_void_p), None, tokens, None, 0), "s2p_session_prefill")
+            ms = (time.perf_counter() - t0) * 1e3
+            lib.s2p_session_destroy(sess)
+            best = ms if best is None else min(best, ms)
+        out[name] = round(best, 2)
+    os.environ["S2P_PREFILL_TC"] = "0"
+    eng.close()
+    return out
+
+
 def tp_block(args, lib, capi, synth, ckpt, rank, world, seed_used, ref_frames, n1_value):
     """ONE batch-1 session sharded over the `world` GPUs (tensor parallel, strong scaling): same checkpoint,
     prompt, seed and call sequence as rank 0's single-GPU engine of the headline measurement, whose frames
@@ -536,6 +565,9 @@ def run_ours(args, rank, world):
     if world == 1:  # bounded host-side legs only where no other GPU waits for them
         if not args.no_kernel_roofline:
             line["roofline_kernels"] = isolated_gemv_roofline(lib, torch, args.mode, peak)
+        if not args.no_prefill_block and args.batch == 1:
+            line["prefill"] = prefill_block(lib, capi, synth, ckpt, args.prompt,
+                                            {"ms_dequant_cublas": "0", "ms_tensor_core": "1"})
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args.mode, layers=args.layers)
     return line
@@ -585,6 +617,8 @@ def run_reference(args, rank, world):
         torch.cuda.synchronize()
         step = (time.perf_counter() - t0) * 1e3 / args.steps
         eng.close()
+        if not args.no_prefill_block and args.batch == 1:
+            base["prefill"] = prefill_block(ref, capi, synth, ckpt, args.prompt, {"ms_dequant_cublas": "0"})
         base.update({"value": round(step, 4), "ms_per_step": round(step, 4),
                      "config": config_block(args, seed_used, world, 1, 4096, False,
                                             "reference CUDA path rebuilt unchanged for sm_100a (oracle/_ref), same GPU, same API calls"),
@@ -622,6 +656,7 @@ def main():
     ap.add_argument("--stage-trace", action="store_true",
                     help="batch 1: add the persistent kernel's per-stage clock stamps (CTA 0) of the last frame, summed per stage kind")
     ap.add_argument("--no-lockstep", action="store_true", help="skip the lockstep_b32 block")
+    ap.add_argument("--no-prefill-block", action="store_true", help="skip the prefill timing block (N = 1)")
     ap.add_argument("--no-tp-block", action="store_true", help="N > 1: skip the tp block")
     ap.add_argument("--lockstep-sessions", type=int, default=32)
     ap.add_argument("--lockstep-context", type=int, default=8192)
