@@ -56,8 +56,10 @@ def algorithmic_bytes_per_frame(mode, n_slow=36):
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_tick_mega launch (36+4 layers, all-INT4, batch 1,
 # ~540 cached positions) from an ncu capture; the capture is named beside the figure because the figure
 # does not follow later kernel changes by itself
-NCU_TRAFFIC_TICK_MEGA_INT4 = 4426394112
-NCU_TRAFFIC_SOURCE = "ncu capture of k_tick_mega (dram__bytes_read.sum + dram__bytes_write.sum, one launch), kernel as of the capture's commit; see the k_tick_mega profile summary"
+NCU_TRAFFIC_TICK_MEGA_INT4 = 4425153280
+NCU_TRAFFIC_SOURCE = ("ncu capture of k_tick_mega (dram__bytes_read.sum + dram__bytes_write.sum, fourth of seven launches of "
+                      "`bench.py --steps 4 --warmup 3`), kernel source as of commit 09a83d5 (two-group GEMV stages); "
+                      "profiles/k_tick_mega_int4_b1.md holds the launch list")
 
 
 def ncu_traffic_per_launch(mode, layers, batch, stats):
