@@ -14,7 +14,8 @@
  * the cache at a fifth of the HBM rate.  Here two warps own a split from the copy to the partial:
  *   scores   warp 0 carries positions 0..31, warp 1 positions 32..63: one position per lane with the
  *            four heads' chains side by side, so a key word is converted once for the four heads;
- *   softmax  each warp reduces its half by shuffles; the halves meet through eight floats in shared
+ *   softmax  each warp reduces its half by shuffles (the four heads' trees packed into one: 6 shuffles
+ *            instead of 20); the halves meet through eight floats in shared
  *            memory.  The exp-sum starts with the pairs (t, t+32), i.e. one value of either warp:
  *            the probabilities go through a 1 KB buffer and every lane adds its pair itself;
  *   values   warp 0 carries dimensions 0..63, warp 1 dimensions 64..127 (two per lane, four heads):
@@ -275,10 +276,10 @@ __global__ void __launch_bounds__(NT * 64) k_attn_decode_team(AttnArgs a) {
         }
         const bool in = j_own < cnt;
 #pragma unroll
-        for (int h = 0; h < 4; h++) {
-            d[h] = in ? d[h] : -INFINITY;
-            const float mx = warp_tree_max(d[h]);
-            if (lane == 0) TT.xm[half][h] = mx;
+        for (int h = 0; h < 4; h++) d[h] = in ? d[h] : -INFINITY;
+        {   /* the four heads' maxima over this warp's 32 positions in one packed tree: lane 8 h holds head h's */
+            const float mx = warp_tree4<true>(d[0], d[1], d[2], d[3], lane);
+            if ((lane & 7) == 0) TT.xm[half][lane >> 3] = mx;
         }
         cp_async_wait<0>(); /* own requests for this split's values are through */
         team_sync(team);    /* the halves' maxima are out, nobody reads the key tile any more, the value tile is complete */
@@ -303,12 +304,16 @@ __global__ void __launch_bounds__(NT * 64) k_attn_decode_team(AttnArgs a) {
         }
         team_sync(team);
 
-        /* exp-sum: the pair (lane, lane + 32), then the 16..1 tree (either warp, same result) */
-        float l[4];
-        {
+        /* exp-sum: the pair (lane, lane + 32), then the 16..1 tree of the four heads packed into one; the first
+         * warp does it and its lane 8 h stores head h's (max, sum) */
+        if (half == 0) {
             const float4 pa = reinterpret_cast<const float4*>(TT.p)[lane], pb = reinterpret_cast<const float4*>(TT.p)[lane + 32];
-            l[0] = warp_tree_sum(pa.x + pb.x); l[1] = warp_tree_sum(pa.y + pb.y);
-            l[2] = warp_tree_sum(pa.z + pb.z); l[3] = warp_tree_sum(pa.w + pb.w);
+            const float lsum = warp_tree4<false>(pa.x + pb.x, pa.y + pb.y, pa.z + pb.z, pa.w + pb.w, lane);
+            if ((lane & 7) == 0) {
+                const int h = lane >> 3;
+                const float mh = h == 0 ? m[0] : h == 1 ? m[1] : h == 2 ? m[2] : m[3];
+                *reinterpret_cast<float2*>(a.part + (((size_t)row * QH + kvh * 4 + h) * a.n_split_slots + spl) * 130) = make_float2(mh, lsum);
+            }
         }
 
         /* ---- value sum: two dimensions, four heads ---- */
@@ -338,7 +343,6 @@ __global__ void __launch_bounds__(NT * 64) k_attn_decode_team(AttnArgs a) {
 #pragma unroll
         for (int h = 0; h < 4; h++) {
             float* ph = a.part + (((size_t)row * QH + kvh * 4 + h) * a.n_split_slots + spl) * 130;
-            if (t64 == 0) *reinterpret_cast<float2*>(ph) = make_float2(m[h], l[h]);
             *reinterpret_cast<float2*>(ph + 2 + d_own) = make_float2(acc[h][0], acc[h][1]);
         }
     }

@@ -51,6 +51,28 @@ __device__ __forceinline__ float warp_tree_max(float v) {
     return v;
 }
 
+/* Four independent warp trees in the shuffles of one and a bit: the same pairs per level as four calls of the
+ * helpers above (value l with l^16, then ^8, ^4, ^2, ^1), but at the first level each lane keeps two of the
+ * four values and hands the other two to its partner, at the second it keeps one.  Lane l ends up with the
+ * result of value index (l >> 3) & 3, the same in the eight lanes of a group.  6 shuffles instead of 20. */
+template <bool IS_MAX>
+__device__ __forceinline__ float warp_tree4(float v0, float v1, float v2, float v3, int lane) {
+    const bool hi16 = (lane & 16) != 0, hi8 = (lane & 8) != 0;
+    float k0 = hi16 ? v2 : v0, k1 = hi16 ? v3 : v1;
+    const float g0 = __shfl_xor_sync(S2P_FULL_MASK, hi16 ? v0 : v2, 16), g1 = __shfl_xor_sync(S2P_FULL_MASK, hi16 ? v1 : v3, 16);
+    k0 = IS_MAX ? fmaxf(k0, g0) : k0 + g0;
+    k1 = IS_MAX ? fmaxf(k1, g1) : k1 + g1;
+    float k = hi8 ? k1 : k0;
+    const float g = __shfl_xor_sync(S2P_FULL_MASK, hi8 ? k0 : k1, 8);
+    k = IS_MAX ? fmaxf(k, g) : k + g;
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) {
+        const float o = __shfl_xor_sync(S2P_FULL_MASK, k, off);
+        k = IS_MAX ? fmaxf(k, o) : k + o;
+    }
+    return k;
+}
+
 /* Halving tree over T values (thread t < T contributes v; T a power of two,
  * T >= 32, T <= blockDim.x).  Levels off >= 32 go through shared memory, the
  * last five through shuffles in warp 0.  `red` needs T floats.  Returns the

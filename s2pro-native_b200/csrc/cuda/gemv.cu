@@ -199,6 +199,11 @@ __global__ void __launch_bounds__(256) k_gemv_batch_i4(__nv_bfloat16* __restrict
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const size_t row_bytes = (size_t)(K >> 1);
     const int T = K >> 9, spr = K >> gshift;
+    /* the grid's y dimension walks groups of MM activation rows: a matrix of few rows gets enough warps that way
+     * while every warp still carries R weight rows per activation load (each (m, n) chain is untouched by it) */
+    x += (size_t)blockIdx.y * MM * K;
+    y += (size_t)blockIdx.y * MM * N;
+    M = min(MM, M - (int)blockIdx.y * MM);
     for (int n0 = ((blockIdx.x * blockDim.x + threadIdx.x) >> 5) * R; n0 < N; n0 += warps * R) {
         const unsigned char* wrow[R];
         const __half* srow[R];
@@ -289,16 +294,24 @@ cudaError_t launch_gemv_batch(void* y, const void* x, const void* w, const void*
     do {                                                                                                   \
         int g4 = (N + 8 * R - 1) / (8 * R);                                                                \
         if (g4 > cap) g4 = cap;                                                                            \
-        k_gemv_batch_i4<MM, R><<<g4, 256, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x,          \
-                                                       (const unsigned char*)w, (const __half*)scales, M, N, K, gshift); \
+        k_gemv_batch_i4<MM, R><<<dim3((unsigned)g4, (unsigned)((M + MM - 1) / MM)), 256, 0, stream>>>(     \
+            (__nv_bfloat16*)y, (const __nv_bfloat16*)x, (const unsigned char*)w, (const __half*)scales, M, N, K, gshift); \
     } while (0)
-        /* rows per warp: as many as leave about two CTAs per SM (a 2560-row matrix keeps one row per warp) */
+        /* A warp carries R weight rows and a group of MM activation rows: R x MM x 16 fmas per tile against MM
+         * 32-byte activation loads per lane, so R is what keeps the kernel off the L1 bandwidth bound (R = 1: two
+         * cycles of L1 per cycle of fma issue).  Large matrices take R = 4 and up to 8 activation rows per warp;
+         * a matrix of few rows keeps R = 4 (or 2) and splits the batch into groups of 4 instead, which doubles the
+         * warps without giving up the reuse.  Per-row results do not depend on the choice. */
         const int sms = device_sm_count();
-        const int R = (N >= 8 * 4 * 2 * sms && M <= 8) ? 4 : (N >= 8 * 2 * 2 * sms ? 2 : 1);
-        if (M <= 2) { if (R == 4) S2P_GB4(2, 4); else if (R == 2) S2P_GB4(2, 2); else S2P_GB4(2, 1); }
-        else if (M <= 4) { if (R == 4) S2P_GB4(4, 4); else if (R == 2) S2P_GB4(4, 2); else S2P_GB4(4, 1); }
-        else if (M <= 8) { if (R == 4) S2P_GB4(8, 4); else if (R == 2) S2P_GB4(8, 2); else S2P_GB4(8, 1); }
-        else S2P_GB4(16, 2); /* 9..16 rows: the activation reloads weigh more than the smaller grid */
+        const int ctas4 = (N + 31) / 32, ctas2 = (N + 15) / 16; /* CTAs of 8 warps at R = 4 / R = 2 */
+        if (M <= 4) { /* few activation rows: latency, not L1 bandwidth, bounds the kernel, so warps count for more than reuse */
+            const int R = ctas4 >= 2 * sms ? 4 : (ctas2 >= 2 * sms ? 2 : 1);
+            if (M <= 2) { if (R == 4) S2P_GB4(2, 4); else if (R == 2) S2P_GB4(2, 2); else S2P_GB4(2, 1); }
+            else { if (R == 4) S2P_GB4(4, 4); else if (R == 2) S2P_GB4(4, 2); else S2P_GB4(4, 1); }
+        }
+        else if (ctas4 >= 2 * sms) S2P_GB4(8, 4);                       /* groups of 8 rows */
+        else if (ctas4 * ((M + 3) / 4) >= sms) S2P_GB4(4, 4);          /* few weight rows: groups of 4 */
+        else S2P_GB4(4, 2);
 #undef S2P_GB4
         return cudaGetLastError();
     }
