@@ -299,18 +299,20 @@ cudaError_t launch_gemv_batch(void* y, const void* x, const void* w, const void*
     } while (0)
         /* A warp carries R weight rows and a group of MM activation rows: R x MM x 16 fmas per tile against MM
          * 32-byte activation loads per lane, so R is what keeps the kernel off the L1 bandwidth bound (R = 1: two
-         * cycles of L1 per cycle of fma issue).  Large matrices take R = 4 and up to 8 activation rows per warp;
-         * a matrix of few rows keeps R = 4 (or 2) and splits the batch into groups of 4 instead, which doubles the
-         * warps without giving up the reuse.  Per-row results do not depend on the choice. */
+         * cycles of L1 per cycle of fma issue), and the accumulators (R x MM) are what decides how many warps an SM
+         * holds: 8 rows x 4 rows is 158 registers (8 warps per SM), 4 x 4 is 128 (16 warps), 4 x 2 is 80.  Measured on
+         * the lockstep tick: beyond 4 activation rows, groups of 4 over the grid's y dimension with R = 4 on the large
+         * matrices and R = 2 on those of few rows (2560: twice the warps) beat 8-row groups by a quarter (batch 8:
+         * 13.9 -> 10.6 ms per tick, batch 16: 23.0 -> 17.5).  With 4 rows or fewer the kernel is bound by latency and
+         * warps count for more than reuse.  Per-row results do not depend on any of this. */
         const int sms = device_sm_count();
         const int ctas4 = (N + 31) / 32, ctas2 = (N + 15) / 16; /* CTAs of 8 warps at R = 4 / R = 2 */
-        if (M <= 4) { /* few activation rows: latency, not L1 bandwidth, bounds the kernel, so warps count for more than reuse */
+        if (M <= 4) {
             const int R = ctas4 >= 2 * sms ? 4 : (ctas2 >= 2 * sms ? 2 : 1);
             if (M <= 2) { if (R == 4) S2P_GB4(2, 4); else if (R == 2) S2P_GB4(2, 2); else S2P_GB4(2, 1); }
             else { if (R == 4) S2P_GB4(4, 4); else if (R == 2) S2P_GB4(4, 2); else S2P_GB4(4, 1); }
         }
-        else if (ctas4 >= 2 * sms) S2P_GB4(8, 4);                       /* groups of 8 rows */
-        else if (ctas4 * ((M + 3) / 4) >= sms) S2P_GB4(4, 4);          /* few weight rows: groups of 4 */
+        else if (ctas4 >= sms) S2P_GB4(4, 4);
         else S2P_GB4(4, 2);
 #undef S2P_GB4
         return cudaGetLastError();
