@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "headops.cuh"
 #include "ops.h"
+#include "attn_prefill.cuh"
 #include "s2p_b200_abi.h"
 
 namespace s2p {
@@ -248,9 +249,32 @@ __global__ void __launch_bounds__(512) k_attn_single(AttnArgs a) {
     a.out[((size_t)row * QH + h) * 128 + t] = f2bf(__fdiv_rn(acc, l));
 }
 
+/* prompt slices: consecutive rows of one session go to the row-block kernel (attn_prefill.cuh) */
+constexpr int ATTN_PREFILL_ROWS = 8;
+template <bool KV8>
+static cudaError_t launch_attn_prefill(const AttnArgs* a, int rows, cudaStream_t st) {
+    static bool attr_set[64] = {false};
+    constexpr size_t smem = sizeof(AttnPrefillSmem<KV8, ATTN_PREFILL_ROWS>);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(k_attn_prefill<KV8, ATTN_PREFILL_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    dim3 grid((unsigned)((rows + ATTN_PREFILL_ROWS - 1) / ATTN_PREFILL_ROWS), (unsigned)a->kv_heads);
+    k_attn_prefill<KV8, ATTN_PREFILL_ROWS><<<grid, 512, smem, st>>>(*a, rows);
+    return cudaGetLastError();
+}
+
 cudaError_t attn_single(const AttnArgs* a, int rows, cudaStream_t st) {
     if (rows <= 0) return cudaSuccess;
     if (a->q_heads != a->kv_heads * 4 || a->head_dim != 128) return cudaErrorInvalidValue;
+    if (rows >= 2 && !a->pos_arr && a->pos_row_step == 1 && !a->kv.bases && a->kv.row_stride == 0 &&
+        (!a->kv8 || (!a->kv.sbases && a->kv.srow_stride == 0)))
+        return a->kv8 ? launch_attn_prefill<true>(a, rows, st) : launch_attn_prefill<false>(a, rows, st);
     dim3 grid((unsigned)rows, (unsigned)a->kv_heads);
     if (a->kv8) k_attn_single<true><<<grid, 512, 0, st>>>(*a);
     else k_attn_single<false><<<grid, 512, 0, st>>>(*a);
