@@ -29,10 +29,13 @@ template <bool KV8, int RB> struct AttnPrefillSmem {
     static constexpr int VB = KV8 ? 128 : 256; /* payload bytes per cached vector */
     static constexpr int TS = VB + 4;          /* staged row stride: word reads of 32 different rows hit 32 banks */
     alignas(16) unsigned char tile[128 * TS];  /* K rows of the tile, then its V rows */
-    alignas(16) __half ssc[128 * 4];           /* their group scales (INT8 cache) */
+    alignas(16) __half ssc[128 * 4];           /* group scales of the keys (INT8 cache) */
+    alignas(16) __half vssc[128 * 4];          /* ... and of the values, staged with the keys */
     alignas(16) float sq[RB][4][128];          /* pre-scaled queries */
     alignas(16) float red[RB][4][128];         /* tree scratch */
-    alignas(16) float sp[RB][4][128];          /* probabilities of the tile */
+    /* weights of the value sum: [row][head][value group][position] = probability x the group's scale (INT8 cache),
+     * or [row][head][0][position] = probability (bf16 cache) */
+    alignas(16) float spv[RB][4][KV8 ? 4 : 1][128];
 };
 
 template <bool KV8, int RB>
@@ -70,7 +73,10 @@ __global__ void __launch_bounds__(512) k_attn_prefill(AttnArgs a, int rows) {
                 __ldg(reinterpret_cast<const uint32_t*>(kc + (plane + t0 + rr) * VB + cw * 4));
         }
         if (KV8)
-            for (int i = threadIdx.x; i < lim_max * 4; i += 512) sm.ssc[i] = ks[(plane + t0) * 4 + i];
+            for (int i = threadIdx.x; i < lim_max * 4; i += 512) {
+                sm.ssc[i] = ks[(plane + t0) * 4 + i];
+                sm.vssc[i] = vs[(plane + t0) * 4 + i];
+            }
         __syncthreads();
 
         /* ---- scores: the key of position t, converted once, against the RB rows' queries ---- */
@@ -145,11 +151,24 @@ __global__ void __launch_bounds__(512) k_attn_prefill(AttnArgs a, int rows) {
             corr[i] = (m[i] == -INFINITY) ? 0.f : expf(m[i] - mn[i]);
         }
         __syncthreads();
+        {
+            float vsf[4] = {1.f, 1.f, 1.f, 1.f};
+            if (KV8 && t < lim_max) {
+                const uint2 sv = *reinterpret_cast<const uint2*>(sm.vssc + t * 4);
+                const __half2 sva = *reinterpret_cast<const __half2*>(&sv.x), svb = *reinterpret_cast<const __half2*>(&sv.y);
+                vsf[0] = __low2float(sva); vsf[1] = __high2float(sva); vsf[2] = __low2float(svb); vsf[3] = __high2float(svb);
+            }
 #pragma unroll
-        for (int i = 0; i < RB; i++) {
-            const float p = (s[i] == -INFINITY) ? 0.f : expf(s[i] - mn[i]);
-            sm.sp[i][g][t] = p;
-            sm.red[i][g][t] = p;
+            for (int i = 0; i < RB; i++) {
+                const float p = (s[i] == -INFINITY) ? 0.f : expf(s[i] - mn[i]);
+                sm.red[i][g][t] = p;
+                if (KV8) {
+#pragma unroll
+                    for (int grp = 0; grp < 4; grp++) sm.spv[i][g][grp][t] = __fmul_rn(p, vsf[grp]);
+                } else {
+                    sm.spv[i][g][0][t] = p;
+                }
+            }
         }
         __syncthreads();
         if (t < 64) {
@@ -177,41 +196,33 @@ __global__ void __launch_bounds__(512) k_attn_prefill(AttnArgs a, int rows) {
             *reinterpret_cast<uint32_t*>(sm.tile + rr * TS + cw * 4) =
                 __ldg(reinterpret_cast<const uint32_t*>(vc + (plane + t0 + rr) * VB + cw * 4));
         }
-        if (KV8)
-            for (int i = threadIdx.x; i < lim_max * 4; i += 512) sm.ssc[i] = vs[(plane + t0) * 4 + i];
         __syncthreads();
 
-        /* ---- value sums: the value of (position j, dimension t), converted once, into the RB rows' chains ---- */
+        /* ---- value sums: the value of (position j, dimension t), converted once, into the RB rows' chains; the
+         * weights of four positions come with one 16-byte read per row ---- */
         const int full = min(lim_max, max(0, len0 - t0)); /* positions every row of the block sees */
-        for (int j = 0; j < full; j++) {
-            float vf, vsj = 1.f;
-            if (KV8) {
-                vf = s8_to_f32(reinterpret_cast<const int8_t*>(sm.tile + j * TS)[t]);
-                vsj = __half2float(sm.ssc[j * 4 + (t >> 5)]);
-            } else {
-                vf = bf2f(reinterpret_cast<const __nv_bfloat16*>(sm.tile + j * TS)[t]);
-            }
+        const int grp = KV8 ? (t >> 5) : 0;
+        auto value_at = [&](int j) -> float {
+            return KV8 ? s8_to_f32(reinterpret_cast<const int8_t*>(sm.tile + j * TS)[t])
+                       : bf2f(reinterpret_cast<const __nv_bfloat16*>(sm.tile + j * TS)[t]);
+        };
+        int j = 0;
+        for (; j + 4 <= full; j += 4) {
+            const float v0 = value_at(j), v1 = value_at(j + 1), v2 = value_at(j + 2), v3 = value_at(j + 3);
 #pragma unroll
             for (int i = 0; i < RB; i++) {
-                const float p = sm.sp[i][g][j];
-                acc[i] = __fmaf_rn(KV8 ? __fmul_rn(p, vsj) : p, vf, acc[i]);
+                const float4 w = *reinterpret_cast<const float4*>(&sm.spv[i][g][grp][j]);
+                acc[i] = __fmaf_rn(w.x, v0, acc[i]);
+                acc[i] = __fmaf_rn(w.y, v1, acc[i]);
+                acc[i] = __fmaf_rn(w.z, v2, acc[i]);
+                acc[i] = __fmaf_rn(w.w, v3, acc[i]);
             }
         }
-        for (int j = full; j < lim_max; j++) { /* the diagonal: row i sees position t0 + j only if it lies below len0 + i */
-            float vf, vsj = 1.f;
-            if (KV8) {
-                vf = s8_to_f32(reinterpret_cast<const int8_t*>(sm.tile + j * TS)[t]);
-                vsj = __half2float(sm.ssc[j * 4 + (t >> 5)]);
-            } else {
-                vf = bf2f(reinterpret_cast<const __nv_bfloat16*>(sm.tile + j * TS)[t]);
-            }
+        for (; j < lim_max; j++) { /* the rest, and the diagonal: row i sees position t0 + j only if it lies below len0 + i */
+            const float vf = value_at(j);
 #pragma unroll
-            for (int i = 0; i < RB; i++) {
-                if (i < rb && t0 + j < len0 + i) {
-                    const float p = sm.sp[i][g][j];
-                    acc[i] = __fmaf_rn(KV8 ? __fmul_rn(p, vsj) : p, vf, acc[i]);
-                }
-            }
+            for (int i = 0; i < RB; i++)
+                if (i < rb && t0 + j < len0 + i) acc[i] = __fmaf_rn(sm.spv[i][g][grp][j], vf, acc[i]);
         }
     }
 #pragma unroll
