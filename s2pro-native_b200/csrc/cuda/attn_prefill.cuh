@@ -43,7 +43,8 @@ __global__ void __launch_bounds__(512) k_attn_prefill(AttnArgs a, int rows) {
     extern __shared__ __align__(16) unsigned char attn_prefill_smem[];
     AttnPrefillSmem<KV8, RB>& sm = *reinterpret_cast<AttnPrefillSmem<KV8, RB>*>(attn_prefill_smem);
     constexpr int VB = AttnPrefillSmem<KV8, RB>::VB, TS = AttnPrefillSmem<KV8, RB>::TS;
-    const int r0 = blockIdx.x * RB, kvh = blockIdx.y;
+    /* the last rows of the slice look furthest back: their blocks start first, the short ones fill in behind them */
+    const int r0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * RB, kvh = blockIdx.y;
     const int rb = min(RB, rows - r0);
     const int g = threadIdx.x >> 7, t = threadIdx.x & 127;
     const int QH = a.q_heads, h = kvh * 4 + g;
