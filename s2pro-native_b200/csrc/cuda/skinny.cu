@@ -175,8 +175,11 @@ __device__ __forceinline__ void sk_tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) 
 /* XT (prompt-sized inputs): the grid's y dimension walks blocks of 256 input rows, and the activations arrive
  * already converted and tiled (k_xt_tile below: f16 units in the order a stage's B tile wants them, one contiguous
  * block per (row block, slab)), so a stage's B tile is ONE bulk copy issued by one thread and the converting threads
- * touch weights only: a weight slab is converted once per 256 input rows instead of once per launch of <= 128. */
-template <int WK, int NT, int KCP, bool XT>
+ * touch weights only: a weight slab is converted once per 256 input rows instead of once per launch of <= 128.
+ * XT == 2: the CTA takes two such blocks (512 rows): two B tiles per stage, two 256-column accumulators side by
+ * side in TMEM (all 512 columns), two MMAs per K step on the one converted A tile, and two stages instead of three
+ * to make room - a weight slab is converted once per 512 rows. */
+template <int WK, int NT, int KCP, int XT>
 __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict__ w, const void* __restrict__ scales, int N,
                                                           int K, int gshift, const __nv_bfloat16* __restrict__ x, int M,
                                                           int lgNB, int D, int DW, int n_split_tiles, int KS, int ffn,
@@ -197,7 +200,8 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
      *  - The MMA warp waits for full[stage], issues the stage's MMAs and commits them to done[stage].
      * Copies, conversion and MMAs of different slabs overlap; nothing in the loop is a CTA-wide barrier. */
     typedef SkGeom<WK, NT, KCP> G;
-    constexpr int KC = G::KC, NST = SK_STAGES;
+    constexpr int KC = G::KC, NST = (XT == 2) ? 2 : SK_STAGES;
+    constexpr int NBLK = (XT == 2) ? 2 : 1; /* blocks of NB input rows per CTA */
     int* status = &g_sk_status;
     extern __shared__ __align__(1024) unsigned char smem[];
     const int NB = 1 << lgNB;
@@ -205,20 +209,20 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
     const int x_units = NB * (KC / 8);
     const int x_bytes = x_units * 16;
     unsigned char* stage_b0 = smem + NST * G::A_BYTES;
-    unsigned char* xring = stage_b0 + NST * b_bytes;
+    unsigned char* xring = stage_b0 + NST * NBLK * b_bytes;
     unsigned char* wring = xring + (XT ? 0 : D * x_bytes); /* XT: no ring of raw activations, B tiles land in the stages */
     uint64_t* full = reinterpret_cast<uint64_t*>(wring + DW * G::SUP_BYTES);
     uint64_t* done = full + NST;
     uint64_t* bx = done + NST; /* XT: the bulk copy of a stage's B tile has landed */
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bx + NST);
-    if (XT) { /* this CTA's block of 256 input rows */
-        const int tb = (int)blockIdx.y;
+    if (XT) { /* this CTA's block(s) of 256 input rows */
+        const int tb = (int)blockIdx.y * NBLK;
         x = reinterpret_cast<const __nv_bfloat16*>(reinterpret_cast<const unsigned char*>(x) + (size_t)tb * (size_t)(K / KC) * (size_t)b_bytes);
         y += (size_t)tb * 256 * (size_t)(ffn ? ffn : N);
         if (resid) resid += (size_t)tb * 256 * (size_t)N;
-        if (partial) partial += (size_t)tb * (size_t)n_split_tiles * KS * 256 * SK_BM;
-        if (arrivals) arrivals += (size_t)tb * n_split_tiles;
-        M = min(256, M - tb * 256);
+        if (partial) partial += (size_t)blockIdx.y * (size_t)n_split_tiles * KS * (256 * NBLK) * SK_BM;
+        if (arrivals) arrivals += (size_t)blockIdx.y * n_split_tiles;
+        M = min(256 * NBLK, M - tb * 256);
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool mma_warp = warp == NT / 32;
@@ -230,7 +234,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
     const int n0 = tile * SK_BM;
     const size_t row_bytes = (WK == WK_INT4_PACK) ? (size_t)(K >> 1) : (size_t)K;
     int ncols = 32;
-    while (ncols < NB) ncols <<= 1;
+    while (ncols < NB * NBLK) ncols <<= 1;
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(ncols) : "memory");
@@ -325,10 +329,14 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
             if (!ok) break;
             const unsigned char* sup = wring + w_rslot;
             unsigned char* A = smem + s * G::A_BYTES;
-            unsigned char* B = stage_b0 + s * b_bytes;
-            if (XT && tid == 0) { /* the stage is free (its MMAs have completed): its B tile travels while the weights are converted */
-                mbar_expect_tx(bx + s, (unsigned)b_bytes);
-                tma_load_1d(B, reinterpret_cast<const unsigned char*>(x) + (size_t)(it_first + it) * (size_t)b_bytes, (unsigned)b_bytes, bx + s);
+            unsigned char* B = stage_b0 + s * (NBLK * b_bytes);
+            if (XT && tid == 0) { /* the stage is free (its MMAs have completed): its B tile(s) travel while the weights are converted */
+                mbar_expect_tx(bx + s, (unsigned)(NBLK * b_bytes));
+#pragma unroll
+                for (int blk = 0; blk < NBLK; blk++) /* the same slab of the next row block lies K / KC tiles further on */
+                    tma_load_1d(B + blk * b_bytes,
+                                reinterpret_cast<const unsigned char*>(x) + ((size_t)blk * (size_t)(K / KC) + (size_t)(it_first + it)) * (size_t)b_bytes,
+                                (unsigned)b_bytes, bx + s);
                 b_issued++;
             }
             /* weights: A[k / 8][row] */
@@ -391,16 +399,18 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
             if (lane == 0) {
                 /* the start-address field counts 16-byte units: stage s and K step kk are plain additions */
                 const uint64_t da0 = desc_a0 + (uint64_t)((s * G::A_BYTES) >> 4);
-                const uint64_t db0 = desc_b0 + (uint64_t)((s * b_bytes) >> 4);
+                const uint64_t db0 = desc_b0 + (uint64_t)((s * NBLK * b_bytes) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < KC / 16; kk++) {
                     const uint64_t da = da0 + (uint64_t)(kk * 2 * SK_BM);
                     const uint64_t db = db0 + (uint64_t)(kk * 2 * NB);
                     const uint32_t accumulate = (it > 0 || kk > 0) ? 1u : 0u;
-                    asm volatile(
-                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                        ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(accumulate) : "memory");
+#pragma unroll
+                    for (int blk = 0; blk < NBLK; blk++) /* accumulator blk: TMEM columns blk NB .., B tile blk of the stage */
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                            ::"r"(tmem + (uint32_t)(blk * NB)), "l"(da), "l"(db + (uint64_t)((blk * b_bytes) >> 4)), "r"(idesc), "r"(accumulate) : "memory");
                 }
                 /* arrives on the barrier once every MMA issued so far has completed */
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(done + s)) : "memory");
@@ -431,7 +441,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
     float rs = 1.f;
     if (WK == WK_INT8_CH && row_live) rs = static_cast<const float*>(scales)[grow];
     if (all_ok && !mma_warp && (piece || !ffn)) {
-        for (int col0 = (warp >> 2) * 32; col0 < NB; col0 += (NT / 128) * 32) {
+        for (int col0 = (warp >> 2) * 32; col0 < NB * NBLK; col0 += (NT / 128) * 32) {
             uint32_t v[32];
             sk_tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0, v);
             if (row_live) {
@@ -456,7 +466,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
          * pair: both products rounded to bf16, sigmoid and silu in f32, silu rounded to bf16, times up, bf16. */
         float* ex = reinterpret_cast<float*>(smem); /* [64 rows][NB + 1] */
         if (!mma_warp && (warp & 3) >= 2) {
-            for (int col0 = (warp >> 2) * 32; col0 < NB; col0 += (NT / 128) * 32) {
+            for (int col0 = (warp >> 2) * 32; col0 < NB * NBLK; col0 += (NT / 128) * 32) {
                 uint32_t v[32];
                 sk_tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0, v);
 #pragma unroll
@@ -466,7 +476,7 @@ __global__ void __launch_bounds__(NT + 32, 1) k_skinny_tc(const void* __restrict
         __syncthreads();
         if (!mma_warp && (warp & 3) < 2) {
             const int gi = tile * 64 + lrow;
-            for (int col0 = (warp >> 2) * 32; col0 < NB; col0 += (NT / 128) * 32) {
+            for (int col0 = (warp >> 2) * 32; col0 < NB * NBLK; col0 += (NT / 128) * 32) {
                 uint32_t v[32];
                 sk_tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)col0, v);
                 if (row_live) {
@@ -677,11 +687,11 @@ static cudaError_t sk_launch_nt(const LinRef* lin, const void* x, int M, const S
     if (ed != cudaSuccess) return ed;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (!attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
+        cudaError_t e = cudaFuncSetAttribute(k_skinny_tc<WK, NT, KCP, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE);
         if (e != cudaSuccess) return e;
         attr_set[dev] = true;
     }
-    k_skinny_tc<WK, NT, KCP, false><<<dim3((unsigned)p.grid), NT + 32, (size_t)p.smem, st>>>(
+    k_skinny_tc<WK, NT, KCP, 0><<<dim3((unsigned)p.grid), NT + 32, (size_t)p.smem, st>>>(
         lin->w, lin->scales, lin->N, lin->K, lin->gshift, (const __nv_bfloat16*)x, M, p.lgNB, p.D, p.DW, p.S, p.KS, ffn, (__nv_bfloat16*)y,
         (const __nv_bfloat16*)resid, partial, arrivals);
     return cudaGetLastError();
@@ -761,16 +771,16 @@ extern "C" cudaError_t skinny_gemm_tc_swiglu(const LinRef* lin, const void* x, i
  * weights go to the tensor cores directly: a CTA owns 128 weight rows x 256 input rows (one 256-column f32
  * accumulator in TMEM), converts each weight slab once for the 256 rows, and receives the activations as
  * bulk copies of pre-tiled f16 blocks written by k_xt_tile. */
-constexpr int XT_ROWS = 256;   /* input rows per CTA: the MMA's N */
+constexpr int XT_ROWS = 256;   /* input rows per block: the MMA's N; a CTA takes one block or (packed INT4, longer prompts) two */
 constexpr int XT_NT = 256, XT_KC = 64; /* kernel shape: three stages of 16 KB (A) + 32 KB (B) fit beside the weight ring */
 
 /* x [M, K] bf16 -> f16 units of 8 in the order stage B wants them: [row block][slab][k / 8 within the slab][row][8],
  * each unit in the within-8 element order of the weight conversion (sk_x_unit); rows beyond M are zero */
 template <int WK>
-__global__ void k_xt_tile(const __nv_bfloat16* __restrict__ x, int M, int K, uint4* __restrict__ xt) {
+__global__ void k_xt_tile(const __nv_bfloat16* __restrict__ x, int M, int K, int rows_pad, uint4* __restrict__ xt) {
     const int k8n = K >> 3;
     const size_t u = (size_t)blockIdx.x * blockDim.x + threadIdx.x; /* (row, k8): consecutive threads read one row */
-    const size_t rows_padded = (size_t)((M + XT_ROWS - 1) / XT_ROWS) * XT_ROWS;
+    const size_t rows_padded = (size_t)rows_pad; /* whole row blocks (an even number of them where a CTA takes two) */
     if (u >= rows_padded * k8n) return;
     const int row = (int)(u / k8n), k8 = (int)(u - (size_t)row * k8n);
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -791,7 +801,13 @@ static cudaError_t xt_launch(const LinRef* lin, const void* x, int M, void* y, c
     if (e != cudaSuccess) return e;
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     const int N = lin->N, K = lin->K;
-    const int tbs = (M + XT_ROWS - 1) / XT_ROWS, tiles = (N + SK_BM - 1) / SK_BM;
+    /* two row blocks per CTA where the weight ring leaves room for 64 KB of B tiles per stage (packed INT4) and the
+     * slice is long enough that halving the CTAs costs less than converting every weight twice (measured: at 512 rows
+     * one block per CTA is 2.5x faster on the 6144-row matrix, at 2048 rows two blocks are 1.25x faster per layer) */
+    const bool two = WK == WK_INT4_PACK && M >= 4 * XT_ROWS;
+    const int nblk = two ? 2 : 1;
+    const int tbs = ((M + XT_ROWS * nblk - 1) / (XT_ROWS * nblk)) * nblk; /* row blocks, padded to whole CTAs */
+    const int tiles = (N + SK_BM - 1) / SK_BM, ctas_y = tbs / nblk;
     /* workspace for the tiled activations: grown on demand, never shrunk (not under stream capture: prefill is not captured) */
     const size_t need = (size_t)tbs * XT_ROWS * K * 2;
     if (need > g_xt_bytes[dev]) {
@@ -803,19 +819,20 @@ static cudaError_t xt_launch(const LinRef* lin, const void* x, int M, void* y, c
     }
     /* split K where tiles x row blocks leave most SMs idle (short prompts, matrices of few rows) */
     int S = 0, KS = 1;
-    if (g_partial_rows[dev] >= XT_ROWS && tiles * tbs * 2 <= 148) {
+    if (g_partial_rows[dev] >= XT_ROWS && tiles * ctas_y * 2 <= 148) {
         int max_ks = K / SK_SUPER_K;
         if (max_ks > SK_MAX_SPLIT) max_ks = SK_MAX_SPLIT;
-        KS = 148 / (tiles * tbs) < max_ks ? 148 / (tiles * tbs) : max_ks;
+        KS = 148 / (tiles * ctas_y) < max_ks ? 148 / (tiles * ctas_y) : max_ks;
         const size_t cap = (size_t)SK_SCRATCH_FLOATS_PER_ROW * g_partial_rows[dev];
         while (KS > 1 && (size_t)tiles * KS * XT_ROWS * SK_BM * tbs > cap) KS--;
-        if (KS > 1 && tiles * tbs <= SK_MAX_SPLIT_TILES) S = tiles; else KS = 1;
+        if (KS > 1 && tiles * ctas_y <= SK_MAX_SPLIT_TILES) S = tiles; else KS = 1;
     }
     const int grid_x = tiles - S + S * KS;
     int DW = 3;
     size_t smem = 0;
     for (; DW >= 2; DW--) {
-        smem = sk_fixed_bytes<WK, XT_NT, XT_KC>(XT_ROWS) + (size_t)DW * G::SUP_BYTES;
+        smem = (two ? 2 * ((size_t)G::A_BYTES + 2 * (size_t)XT_ROWS * XT_KC * 2) + 128 : sk_fixed_bytes<WK, XT_NT, XT_KC>(XT_ROWS)) +
+               (size_t)DW * G::SUP_BYTES;
         if (smem <= SK_SMEM_ONE) break;
     }
     if (DW < 2) return cudaErrorInvalidValue;
@@ -823,15 +840,22 @@ static cudaError_t xt_launch(const LinRef* lin, const void* x, int M, void* y, c
     if (D > SK_MAX_DEPTH) D = SK_MAX_DEPTH;
     static bool attr_set[64] = {false};
     if (!attr_set[dev]) {
-        if ((e = cudaFuncSetAttribute(k_skinny_tc<WK, XT_NT, XT_KC, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE)) != cudaSuccess) return e;
+        if ((e = cudaFuncSetAttribute(k_skinny_tc<WK, XT_NT, XT_KC, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE)) != cudaSuccess) return e;
+        if (WK == WK_INT4_PACK &&
+            (e = cudaFuncSetAttribute(k_skinny_tc<WK_INT4_PACK, XT_NT, XT_KC, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM_ONE)) != cudaSuccess) return e;
         attr_set[dev] = true;
     }
     const size_t units = (size_t)tbs * XT_ROWS * (K >> 3);
-    k_xt_tile<WK><<<(unsigned)((units + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, M, K, (uint4*)g_xt[dev]);
+    k_xt_tile<WK><<<(unsigned)((units + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, M, K, tbs * XT_ROWS, (uint4*)g_xt[dev]);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    k_skinny_tc<WK, XT_NT, XT_KC, true><<<dim3((unsigned)grid_x, (unsigned)tbs), XT_NT + 32, smem, st>>>(
-        lin->w, lin->scales, N, K, lin->gshift, (const __nv_bfloat16*)g_xt[dev], M, 8, D, DW, S, KS, 0, (__nv_bfloat16*)y, nullptr,
-        S ? g_partial[dev] : nullptr, S ? g_arrivals[dev] : nullptr);
+    if (two)
+        k_skinny_tc<WK_INT4_PACK, XT_NT, XT_KC, 2><<<dim3((unsigned)grid_x, (unsigned)ctas_y), XT_NT + 32, smem, st>>>(
+            lin->w, lin->scales, N, K, lin->gshift, (const __nv_bfloat16*)g_xt[dev], M, 8, D, DW, S, KS, 0, (__nv_bfloat16*)y, nullptr,
+            S ? g_partial[dev] : nullptr, S ? g_arrivals[dev] : nullptr);
+    else
+        k_skinny_tc<WK, XT_NT, XT_KC, 1><<<dim3((unsigned)grid_x, (unsigned)ctas_y), XT_NT + 32, smem, st>>>(
+            lin->w, lin->scales, N, K, lin->gshift, (const __nv_bfloat16*)g_xt[dev], M, 8, D, DW, S, KS, 0, (__nv_bfloat16*)y, nullptr,
+            S ? g_partial[dev] : nullptr, S ? g_arrivals[dev] : nullptr);
     return cudaGetLastError();
 }
 

@@ -121,10 +121,12 @@ def test_fused_swiglu_equals_linear_then_swiglu(mine, testlib, kind, M, ffn, K):
 
 
 @pytest.mark.parametrize("kind", [2, 0, 1])
-@pytest.mark.parametrize("M,N,K", [(300, 6144, 2560), (512, 2560, 4096), (1000, 19456, 2560), (40, 4097, 2560), (257, 2560, 9728), (2048, 384, 512)])
+@pytest.mark.parametrize("M,N,K", [(300, 6144, 2560), (512, 2560, 4096), (1000, 19456, 2560), (40, 4097, 2560), (257, 2560, 9728), (2048, 384, 512),
+                                   (1024, 2560, 4096), (1300, 6144, 2560)])
 def test_prompt_sized_linear_matches_exact_gemv(mine, testlib, kind, M, N, K):
     """The prefill form of the tensor-core linear: any number of rows in blocks of 256, activations
-    pre-tiled in f16 and brought in by bulk copies, a weight slab converted once per block."""
+    pre-tiled in f16 and brought in by bulk copies, a weight slab converted once per block; from 1024 rows on a CTA
+    of the packed-INT4 kind takes two blocks (two accumulators side by side in TMEM), ragged last pair included."""
     dev()
     testlib.skinny_prefill_tc.argtypes = [C.POINTER(LinRef), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
     testlib.skinny_status.argtypes = [C.POINTER(C.c_int)]
