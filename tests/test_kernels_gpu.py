@@ -201,7 +201,14 @@ def test_split_k_decode_attention_8192_positions(libs):
     _split_k_decode_attention(libs, 1, [8192, 8000], 8256, (8, 18))
 
 
-def _split_k_decode_attention(libs, kv8, lens, max_seq, workers_list):
+@pytest.mark.parametrize("kv8", [1, 0])
+def test_split_k_decode_attention_cache_not_16_byte_aligned(libs, kv8):
+    """Caches whose base addresses are only 8-byte aligned: the lockstep kernel must take its 4-byte copy path
+    (a 16-byte asynchronous copy from such an address would be illegal) and give the same bits."""
+    _split_k_decode_attention(libs, kv8, [130, 64, 700], 768, (4,), shift_bytes=8)
+
+
+def _split_k_decode_attention(libs, kv8, lens, max_seq, workers_list, shift_bytes=0):
     _, tl, ref = libs
     rows = len(lens)
     caches = []
@@ -226,6 +233,18 @@ def _split_k_decode_attention(libs, kv8, lens, max_seq, workers_list):
     else:
         assert ref.s2pk_attention_decode(p(q), p(kptr), p(vptr), p(o_ref), rows, QH, KVH, HD, p(pos), max_seq, max_len, p(part), None) == 0
     torch.cuda.synchronize()
+    v_off = caches[0][0][0].numel() * caches[0][0].element_size()
+    vs_off = caches[0][1][0].numel() * 2
+    keep = []
+    if shift_bytes:  # byte copies of every cache at an address shift_bytes past a 256-byte boundary
+        def shifted(t):
+            raw = torch.empty(t.numel() * t.element_size() + 256, dtype=torch.uint8, device="cuda")
+            view = raw[shift_bytes:shift_bytes + t.numel() * t.element_size()]
+            view.copy_(t.contiguous().view(torch.uint8).flatten())
+            keep.append(raw)
+            assert view.data_ptr() % 16 == shift_bytes % 16
+            return view
+        caches = [(shifted(c[0]), shifted(c[1])) for c in caches]
     for workers in workers_list:
         o = torch.zeros_like(q)
         ctr = torch.zeros(rows * KVH, dtype=torch.int32, device="cuda")
@@ -233,8 +252,8 @@ def _split_k_decode_attention(libs, kv8, lens, max_seq, workers_list):
         a = AttnArgs()
         a.q = q.data_ptr(); a.out = o.data_ptr(); a.q_heads = QH; a.kv_heads = KVH; a.max_seq = max_seq; a.kv8 = kv8; a.head_dim = HD
         a.pos_arr = pos.data_ptr()
-        a.kv.bases = base.data_ptr(); a.kv.k_off = 0; a.kv.v_off = caches[0][0][0].numel() * caches[0][0].element_size()
-        a.kv.sbases = sbase.data_ptr(); a.kv.ks_off = 0; a.kv.vs_off = caches[0][1][0].numel() * 2
+        a.kv.bases = base.data_ptr(); a.kv.k_off = 0; a.kv.v_off = v_off
+        a.kv.sbases = sbase.data_ptr(); a.kv.ks_off = 0; a.kv.vs_off = vs_off
         a.part = part.data_ptr(); a.counters = ctr.data_ptr(); a.n_split_slots = n_slots; a.workers = workers
         assert tl.attn_decode(C.byref(a), rows, None) == 0
         assert_same(o, o_ref, f"split-K decode attention kv8={kv8} workers={workers}")
