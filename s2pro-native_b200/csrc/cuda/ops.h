@@ -208,8 +208,15 @@ __host__ __device__
 static inline MegaGeom mega_stage_geom(int N, int swiglu, int rows_per_chunk, int cta, int n_cta) {
     MegaGeom g;
     const int units = swiglu ? (N >> 1) : N;
-    g.row0 = (int)((long long)units * cta / n_cta);
-    g.cnt = (int)((long long)units * (cta + 1) / n_cta) - g.row0;
+    if ((long long)units * (long long)n_cta <= 0x7fffffffLL) {
+        /* the products fit 32 bits for every matrix of the model: unsigned 32-bit divisions, a fraction of the
+         * instructions of the 64-bit ones, and this runs at the head of every stage on both warp groups */
+        g.row0 = (int)((unsigned)units * (unsigned)cta / (unsigned)n_cta);
+        g.cnt = (int)((unsigned)units * (unsigned)(cta + 1) / (unsigned)n_cta) - g.row0;
+    } else {
+        g.row0 = (int)((long long)units * cta / n_cta);
+        g.cnt = (int)((long long)units * (cta + 1) / n_cta) - g.row0;
+    }
     g.n_chunks = g.cnt > 0 ? (g.cnt + rows_per_chunk - 1) / rows_per_chunk : 0;
     g.rc = g.n_chunks ? (g.cnt + g.n_chunks - 1) / g.n_chunks : 0;
     return g;
