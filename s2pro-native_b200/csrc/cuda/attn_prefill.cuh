@@ -10,7 +10,7 @@
  * value for that one row and crosses ~20 CTA barriers per tile: a 512-token prompt spends 13 of its 29 ms there, an
  * 8192-token prompt 2.8 of 2.9 s.  Here a tile is staged once for RB rows, a cached key or value is read and
  * converted once and feeds RB chains held side by side in registers, and the trees of the RB rows share their
- * barriers.  Rows of a block differ only in how far they may look: row i of the block sees positions below
+ * barriers.  (RB = 4 in the product: 64 registers, two CTAs per SM.)  Rows of a block differ only in how far they may look: row i of the block sees positions below
  * len0 + i, which only matters in the block's last one or two tiles; there the chains of positions a row may not see
  * yield -inf / probability 0 and its value sum skips them, exactly as the single-row loop ends earlier.
  *

@@ -155,7 +155,7 @@ def _filled_cache(max_seq, kv8, seed):
 @pytest.mark.parametrize("pos0,rows", [(0, 1), (0, 40), (100, 30), (250, 6), (0, 300), (120, 9), (127, 2), (190, 130), (0, 1100), (1000, 50)])
 def test_single_pass_attention(libs, kv8, pos0, rows):
     """One row goes to the single-row kernel, several consecutive rows of one cache (a prompt slice) to the
-    row-block kernel: blocks of 8 rows, ragged last block, blocks that straddle a 128-position tile boundary."""
+    row-block kernel: blocks of 4 rows, ragged last block, blocks that straddle a 128-position tile boundary."""
     mine, tl, ref = libs
     max_seq = max(320, ((pos0 + rows + 63) // 64) * 64)
     kvbuf, kvs, kvref, k, v = _filled_cache(max_seq, kv8, 30)
