@@ -298,6 +298,32 @@ __global__ void __launch_bounds__(256) k_silu_mul(const __nv_bfloat16* __restric
     }
 }
 
+/* the same, eight columns per thread (ffn a multiple of 8, 16-byte aligned rows): two 16-byte loads, one
+ * 16-byte store, one division per eight elements instead of one 64-bit division per element */
+__global__ void __launch_bounds__(256) k_silu_mul8(const uint4* __restrict__ gu, uint4* __restrict__ h, unsigned n_units,
+                                                   unsigned f8) {
+    for (unsigned u = blockIdx.x * blockDim.x + threadIdx.x; u < n_units; u += gridDim.x * blockDim.x) {
+        const unsigned r = u / f8, c8 = u - r * f8;
+        const uint4 gv = gu[(size_t)r * 2 * f8 + c8], uv = gu[(size_t)r * 2 * f8 + f8 + c8];
+        const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float r2[2];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const float g = k ? bf_hi(gw[j]) : bf_lo(gw[j]), up = k ? bf_hi(uw[j]) : bf_lo(uw[j]);
+                const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+                const float sil = bf16_round(__fmul_rn(g, sig));
+                r2[k] = __fmul_rn(sil, up);
+            }
+            const __nv_bfloat162 pk = __halves2bfloat162(f2bf(r2[0]), f2bf(r2[1]));
+            o[j] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        h[u] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 /* ---- residual add (kernels.cu:1242-1247) ----------------------------------- */
 __global__ void __launch_bounds__(256) k_add(__nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ x, int64_t n) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
@@ -406,7 +432,10 @@ cudaError_t rms_norm(const void* x, const void* w, void* y, int rows, int width,
 cudaError_t silu_mul(const void* gu, void* h, int rows, int ffn, cudaStream_t st) {
     if (rows <= 0) return cudaSuccess;
     const int64_t total = (int64_t)rows * ffn;
-    k_silu_mul<<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, total, ffn);
+    if (ffn % 8 == 0 && (((uintptr_t)gu | (uintptr_t)h) & 15) == 0 && total / 8 < 0xFFFFFFFFll)
+        k_silu_mul8<<<grid_for(total / 8, 256), 256, 0, st>>>((const uint4*)gu, (uint4*)h, (unsigned)(total / 8), (unsigned)(ffn / 8));
+    else
+        k_silu_mul<<<grid_for(total, 256), 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, total, ffn);
     return cudaGetLastError();
 }
 cudaError_t add_inplace(void* y, const void* x, int64_t n, cudaStream_t st) {
