@@ -143,6 +143,10 @@ __global__ void __launch_bounds__(256) k_gemv_batch(__nv_bfloat16* __restrict__ 
     const int warps = (gridDim.x * blockDim.x) >> 5;
     const size_t row_bytes = (WK == WK_INT4_PACK) ? (size_t)(K >> 1) : (size_t)K;
     const int T = K >> 9;
+    /* the grid's y dimension walks groups of MM activation rows (see k_gemv_batch_i4) */
+    x += (size_t)blockIdx.y * MM * K;
+    y += (size_t)blockIdx.y * MM * N;
+    M = min(MM, M - (int)blockIdx.y * MM);
     for (int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; n < N; n += warps) {
         const unsigned char* wrow = static_cast<const unsigned char*>(w) + (size_t)n * row_bytes;
         float acc[MM];
@@ -320,12 +324,12 @@ cudaError_t launch_gemv_batch(void* y, const void* x, const void* w, const void*
     int grid = (N + 7) / 8;
     if (grid > cap) grid = cap;
 #define S2P_GB(MM)                                                                                      \
-    k_gemv_batch<WK, MM><<<grid, 256, 0, stream>>>((__nv_bfloat16*)y, (const __nv_bfloat16*)x, w, scales, \
-                                                   M, N, K, gshift)
+    k_gemv_batch<WK, MM><<<dim3((unsigned)grid, (unsigned)((M + MM - 1) / MM)), 256, 0, stream>>>(      \
+        (__nv_bfloat16*)y, (const __nv_bfloat16*)x, w, scales, M, N, K, gshift)
+    /* beyond four activation rows: groups of four over the grid's y dimension (twice to four times the warps at half
+     * the registers; INT8 lockstep tick at 16 rows 34.7 -> 22.9 ms, at 8 rows 15.4 -> 13.9) */
     if (M <= 2) S2P_GB(2);
-    else if (M <= 4) S2P_GB(4);
-    else if (M <= 8) S2P_GB(8);
-    else S2P_GB(16);
+    else S2P_GB(4);
 #undef S2P_GB
     return cudaGetLastError();
 }
