@@ -81,3 +81,13 @@ def test_kv_head_workers_share_a_rank(lib, world):
     # fast-AR heads: head h runs in CTA h % (8 / world) of rank h // (8 / world)
     per = 8 // world
     assert sorted((h // per, h % per) for h in range(8)) == [(r, c) for r in range(world) for c in range(per)]
+
+
+@pytest.mark.parametrize("N,n_cta", [(19456, 148), (155776, 1184), (1813000, 1184), (1814000, 1184), (4000000, 1184), (2**31 - 1, 148)])
+def test_partition_matches_the_exact_quotients_on_both_arithmetic_paths(lib, N, n_cta):
+    """The row partition uses 32-bit divisions where the products fit and 64-bit ones beyond (around 1.81 M rows
+    at 1184 CTAs): both must give floor(N * cta / n_cta)."""
+    for cta in (0, 1, n_cta // 3, n_cta - 2, n_cta - 1):
+        row0, cnt, rc, n_chunks = geom(lib, N, 0, 1 << 20, cta, n_cta)
+        assert row0 == N * cta // n_cta
+        assert cnt == N * (cta + 1) // n_cta - row0
